@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b2a|reference] [--workload NAME]
+
+Prints ONE JSON line (rank 0).  The headline workload is the Llama-3-8B-shaped causal bf16 prefill SDPA
+(B=4, Hq=32, Hkv=8, S=4096, D=128); the same line carries the paged-decode half of the metric (KV GB/s on the
+64-sequence u8-cache decode and on the 16 x 32768 long-context decode) under "decode".  With N > 1 the heads are
+sharded over the ranks (Hkv/N KV heads each, no K/V crosses NVLink) and the per-head outputs are all-gathered
+with NCCL inside the timed step.
+
+`--impl reference` times the CPU restatement of the reference's dense attention (oracle port, all host threads)
+on a bounded slice of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PREFILL = dict(B=4, Hq=32, Hkv=8, S=4096, D=128)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d["bf16_tflops"], tflops_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        for ts, line in self.rows:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                mx = float(f[1])
+                if t0 - 0.05 <= ts <= t1 + 0.05:
+                    mhz.append(float(f[0]))
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                        if v.lower().startswith("active"):
+                            reasons.add(name)
+            except ValueError:
+                continue
+        if not mhz:  # region shorter than the sampling period: take the nearest samples
+            for ts, line in self.rows[-3:]:
+                try:
+                    mhz.append(float(line.split(",")[0]))
+                except ValueError:
+                    pass
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def causal_flops(B, Hq, S, D):
+    return 4 * B * Hq * D * (S * (S + 1) // 2)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's dense attention (restating the reference's _dense_attention) on all host threads
+# ----------------------------------------------------------------------------------------------------------
+
+def cpu_prefill_sample(steps: int, warmup: int, budget_s: float = 20.0):
+    """Times softmax(QK^T*scale + causal)V in float32 on the CPU for a slice of the prefill workload:
+    one batch entry, the 4 query heads of one KV head, full S and D.  Returns (TFLOP/s, dict)."""
+    from oracle.torch_cpu import dense_attention_cpu
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    S, D, g = PREFILL["S"], PREFILL["D"], PREFILL["Hq"] // PREFILL["Hkv"]
+    gen = torch.Generator().manual_seed(1)
+    q = (torch.randn(1, g, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(1, 1, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(1, 1, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    fl = causal_flops(1, g, S, D)
+    times = []
+    t_begin = time.time()
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        dense_attention_cpu(q, k, v, causal=True)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+        if time.time() - t_begin > budget_s and len(times) >= 1:
+            break
+    ms = 1e3 * float(np.mean(times))
+    tf = fl / (ms * 1e-3) / 1e12
+    return tf, ms, dict(value=tf, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                        sample=f"B=1, Hq={g} (one KV head), S={S}, D={D} causal slice of the prefill workload, "
+                               f"f32 math on bf16 data, {len(times)} timed passes")
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    tf, ms, base = cpu_prefill_sample(args.steps, args.warmup, budget_s=60.0)
+    line = {"impl": "reference", "metric": "prefill attn TFLOP/s (causal bf16 SDPA, Llama-3-8B shape)",
+            "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32 on bf16 data", "data": "synthetic",
+            "config": {"workload": "prefill_llama3_8b: B=4 Hq=32 Hkv=8 S=4096 D=128 causal, scale=1/sqrt(128)",
+                       "step": base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "OpenVINO runtime not present; CPU restatement of the reference's dense attention "
+                    "(modules/genai_optimizations/genai_opt/sparse_attention.py:95-121) stands in"}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------------
+
+def timed(fn, steps, warmup, world, stream=None):
+    """W warm-up calls, then K calls between two events; barrier + synchronize on both sides; max over ranks."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps, t0, t1
+
+
+def bench_prefill(args, rank, world, local):
+    import torch.distributed as dist
+    import openvino_contrib_b200 as b2a
+    B, Hq, Hkv, S, D = (PREFILL[k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    assert Hkv % world == 0
+    hkv_l, hq_l = Hkv // world, Hq // world
+    gen = torch.Generator().manual_seed(1)
+    # the full problem is generated from one seed; each rank keeps its head shard
+    sl_q = slice(rank * hq_l, (rank + 1) * hq_l)
+    sl_k = slice(rank * hkv_l, (rank + 1) * hkv_l)
+    q_h = (torch.randn(B, Hq, S, D, generator=gen) * 0.5).to(torch.bfloat16)[:, sl_q].contiguous().pin_memory()
+    k_h = (torch.randn(B, Hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)[:, sl_k].contiguous().pin_memory()
+    v_h = (torch.randn(B, Hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)[:, sl_k].contiguous().pin_memory()
+    q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
+    out = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16, device="cuda")
+    gathered = torch.empty(world, B, hq_l, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    launches = [0]
+
+    def step():
+        b2a.sdpa(q, k, v, causal=True, out=out)
+        launches[0] += 1
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    sampler = ClockSampler(local)
+    ms, t0, t1 = timed(step, args.steps, args.warmup, world)
+    clocks = sampler.stop(t0, t1)
+    n_launch = args.steps
+    flops = causal_flops(B, Hq, S, D)
+    value = flops / (ms * 1e-3) / 1e12
+
+    # kernel-only duration (no collective) for the roofline of the dominant kernel
+    def kern():
+        b2a.sdpa(q, k, v, causal=True, out=out)
+    kms, _, _ = timed(kern, args.steps, 1, 1)
+    pk = peaks()
+    achieved = causal_flops(B, hq_l, S, D) / (kms * 1e-3) / 1e12
+    roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
+            "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"] + " burst bf16 GEMM",
+            "kernel_ms": kms}
+
+    # end to end through the public API with host buffers: H2D of q,k,v, kernel, D2H of the output
+    out_h = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        qd, kd, vd = q_h.cuda(non_blocking=True), k_h.cuda(non_blocking=True), v_h.cuda(non_blocking=True)
+        o = b2a.sdpa(qd, kd, vd, causal=True)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, o)
+        out_h.copy_(o, non_blocking=True)
+    ems, _, _ = timed(e2e_step, max(3, args.steps // 2), 2, world)
+    h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
+    e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": out_h.numel() * 2, "ms_per_step": ems}
+    return dict(ms=ms, value=value, roofline=roof, e2e=e2e, clocks=clocks, launches=n_launch)
+
+
+def build_decode_problem(n_seqs, ctx_lens, Hq, Hkv, D, seed, device="cuda"):
+    """u8 pools filled on the device through b2a_paged_kv_store from N(0,1) rows; seeded shuffled block table."""
+    import openvino_contrib_b200 as b2a
+    bs = 16
+    nblk = [(int(c) + bs - 1) // bs for c in ctx_lens]
+    total = sum(nblk)
+    perm = torch.randperm(total + 1, generator=torch.Generator().manual_seed(seed + 1))[:total].to(torch.int32)
+    bb = torch.zeros(n_seqs + 1, dtype=torch.int32)
+    bb[1:] = torch.cumsum(torch.tensor(nblk), 0)
+    cache = b2a.PagedKvCache.allocate(total + 1, Hkv, D, bs, torch.uint8, device=device, poison=0xFF)
+    bi, bbd = perm.to(device), bb.to(device)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    # fill in slices of at most 2048 positions per sequence
+    maxc = int(max(ctx_lens))
+    ctx_t = torch.tensor([int(c) for c in ctx_lens])
+    for p0 in range(0, maxc, 2048):
+        ql = torch.clamp(ctx_t - p0, 0, 2048).to(torch.int32)
+        ntok = int(ql.sum())
+        if ntok == 0:
+            break
+        sb = torch.zeros(n_seqs + 1, dtype=torch.int32)
+        sb[1:] = torch.cumsum(ql, 0)
+        past = torch.where(ql > 0, torch.full_like(ql, p0), ctx_t.to(torch.int32))
+        key = torch.randn(ntok, Hkv * D, generator=gen, device=device, dtype=torch.float16)
+        val = torch.randn(ntok, Hkv * D, generator=gen, device=device, dtype=torch.float16)
+        b2a.paged_kv_store(key, val, cache, past.to(device), sb.to(device), bi, bbd)
+    past = (ctx_t - 1).to(torch.int32).to(device)
+    sb = torch.arange(n_seqs + 1, dtype=torch.int32, device=device)
+    q = torch.randn(n_seqs, Hq * D, generator=gen, device=device, dtype=torch.float16)
+    return cache, q, past, sb, bi, bbd
+
+
+def bench_decode(name, steps, warmup, rank, world):
+    """Paged decode, u8 KV: 'cfg3' = 64 sequences with contexts U[512, 8192]; 'cfg5' = 16 x 32768, Hq 64."""
+    import torch.distributed as dist
+    import openvino_contrib_b200 as b2a
+    if name == "cfg3":
+        n, Hq, Hkv = 64, 32, 8
+        ctx = np.random.default_rng(2).integers(512, 8193, size=n)
+    else:
+        n, Hq, Hkv = 16, 64, 8
+        ctx = np.full(n, 32768)
+    D = 128
+    hkv_l, hq_l = Hkv // world, Hq // world
+    cache, q, past, sb, bi, bb = build_decode_problem(n, ctx, hq_l, hkv_l, D, seed=3 + rank)
+    maxc = int(ctx.max())
+    out = torch.empty(n, hq_l * D, dtype=torch.float16, device="cuda")
+    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, hq_l, n, n, maxc, 1)),
+                     dtype=torch.uint8, device="cuda")
+    gathered = torch.empty(world, n, hq_l * D, dtype=torch.float16, device="cuda") if world > 1 else None
+
+    def step():
+        b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1, out=out,
+                            workspace=ws)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+    ms, _, _ = timed(step, steps, warmup, world)
+    tokens = int(ctx.sum())
+    kv_bytes = tokens * Hkv * 2 * (D + 4)  # whole job: all ranks' heads
+    pk = peaks()
+    gbs = kv_bytes / (ms * 1e-3) / 1e9
+    return {"workload": name, "kv_gbs": gbs, "ms_per_step": ms, "kv_bytes_per_step": kv_bytes,
+            "frac_of_hbm_peak": gbs / (pk["hbm_gbs"] * world), "peak_gbs_per_gpu": pk["hbm_gbs"],
+            "peak_source": pk["source"], "cached_tokens": tokens, "launches_per_step": 2}
+
+
+def run_b2a(args):
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import openvino_contrib_b200  # noqa: F401  (fails loudly if libb2a.so is missing)
+
+    pre = bench_prefill(args, rank, world, local)
+    decode = {}
+    for name in ("cfg3", "cfg5"):
+        decode[name] = bench_decode(name, max(args.steps, 20), max(args.warmup, 3), rank, world)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        _, _, cpu = cpu_prefill_sample(3, 1, budget_s=20.0)
+    if rank == 0:
+        B, Hq, Hkv, S, D = (PREFILL[k] for k in ("B", "Hq", "Hkv", "S", "D"))
+        line = {
+            "metric": "prefill attn TFLOP/s (causal bf16 SDPA, Llama-3-8B shape)",
+            "value": pre["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": pre["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"prefill_llama3_8b: B={B} Hq={Hq} Hkv={Hkv} S={S} D={D} causal, scale=1/sqrt(128), "
+                                   f"Q,K,V ~ N(0,1)*0.5 seed 1",
+                       "sharding": f"KV heads over {world} GPU(s), NCCL all-gather of outputs in the step" if world > 1
+                       else "single GPU",
+                       "l2": "inputs + outputs (335 MB) exceed the 126 MB L2; no flush between steps"},
+            "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["launches"],
+            "clocks": pre["clocks"], "decode": decode,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b2a", choices=["b2a", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b2a" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b2a(args)
+
+
+if __name__ == "__main__":
+    main()

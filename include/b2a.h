@@ -1,0 +1,169 @@
+/*
+ * b2a.h — C ABI of the B200 attention library (libb2a.so).
+ *
+ * The library replaces, for the attention path only, what OpenVINO's nvidia_plugin builds
+ * out of a dozen elementary operations.  Each entry point names the reference interface
+ * it stands in for (paths relative to modules/nvidia_plugin/ of openvino_contrib).
+ *
+ * Conventions
+ *   - every pointer named q/k/v/o/..._cache/workspace/status and every i32 table is DEVICE memory
+ *     unless the comment says "host";
+ *   - every call only validates on the host and enqueues kernels on `stream`; none allocates,
+ *     synchronises or copies across the host/device boundary, so all are legal inside stream capture
+ *     (the plugin captures Execute() under cudaStreamCaptureModeThreadLocal, src/cuda/graph.cpp:76-78);
+ *   - the return value is a b2a_status from host-side validation (0 = launched);
+ *   - `status` (optional, may be NULL) is a device int32 the kernels OR error bits into when a bounded
+ *     wait expires or an index check fails; the caller reads it whenever it synchronises.
+ *
+ * No function here has a CPU fallback: without a CUDA device the compute entry points return
+ * B2A_ERR_CUDA.
+ */
+#ifndef B2A_H_
+#define B2A_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b2a_stream_t; /* == cudaStream_t */
+
+typedef enum b2a_dtype { B2A_F32 = 0, B2A_F16 = 1, B2A_BF16 = 2, B2A_U8 = 3 } b2a_dtype;
+typedef enum b2a_mask_kind { B2A_MASK_NONE = 0, B2A_MASK_BOOL = 1, B2A_MASK_ADD = 2 } b2a_mask_kind;
+
+typedef enum b2a_status {
+    B2A_OK = 0,
+    B2A_ERR_NULL = 1,        /* a required pointer is NULL */
+    B2A_ERR_DIM = 2,         /* a dimension is non-positive or inconsistent (Hq % Hkv, D limits, ...) */
+    B2A_ERR_DTYPE = 3,       /* unsupported element type combination */
+    B2A_ERR_ALIGN = 4,       /* a pointer or stride breaks the alignment the kernels need */
+    B2A_ERR_WORKSPACE = 5,   /* workspace missing or too small */
+    B2A_ERR_CUDA = 6,        /* a CUDA runtime call failed (no device, launch error) */
+    B2A_ERR_UNSUPPORTED = 7, /* valid request this build has no kernel for */
+    B2A_ERR_CAPACITY = 8,    /* block manager: pool exhausted / output array too small */
+    B2A_ERR_NOT_FOUND = 9    /* block manager: unknown sequence id */
+} b2a_status;
+
+/* bits OR-ed into the device status word */
+#define B2A_DEV_TIMEOUT 0x1u   /* a bounded wait (mbarrier / flag) gave up */
+#define B2A_DEV_BAD_BLOCK 0x2u /* a block-table entry was outside [0, num_blocks_total) */
+#define B2A_DEV_BAD_LEN 0x4u   /* a length/offset table was inconsistent */
+
+/* ---------------------------------------------------------------------------------------------
+ * ScaledDotProductAttention
+ *
+ * Replaces the chain the reference obtains from ov::pass::ScaledDotProductAttentionDecomposition
+ * (src/transformer/cuda_graph_transformer.cpp:151-156): Multiply (src/ops/multiply.cpp:16-43),
+ * Transpose (src/ops/transpose.cpp:58-135), MatMul via cublasGemmStridedBatchedEx
+ * (src/ops/matmul.cpp:185-227), the causal-mask subgraph (src/kernels/comparison.cu:17-49,
+ * src/kernels/select.cu:16-45, src/kernels/broadcast.cu:16-24), Add (src/ops/add.cpp:17-43),
+ * Softmax via cudnnSoftmaxForward (src/ops/softmax.cpp:178-193) and the second MatMul.
+ *
+ * Layout: q [B,Hq,Sq,D], k [B,Hkv,Skv,D], v [B,Hkv,Skv,Dv], o [B,Hq,Sq,Dv]; strides in ELEMENTS,
+ * innermost stride must be 1; an all-zero stride array means "contiguous".  Hq % Hkv == 0; query head h
+ * reads KV head h / (Hq/Hkv).  causal != 0: query i keeps keys 0..i (top-left aligned) and the mask is
+ * ignored.  mask: B2A_MASK_BOOL = u8, non-zero keeps; B2A_MASK_ADD = same dtype as q, added to the scaled
+ * scores; mask_strides address a logical [B,Hq,Sq,Skv] tensor (stride 0 on broadcast dimensions).
+ * scale == 0 selects 1/sqrt(D).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct b2a_sdpa_desc {
+    int32_t dtype; /* b2a_dtype of q, k, v and o */
+    int32_t B, Hq, Hkv, Sq, Skv, D, Dv;
+    int32_t causal;
+    float scale;
+    int64_t q_strides[4], k_strides[4], v_strides[4], o_strides[4];
+    int32_t mask_kind; /* b2a_mask_kind */
+    int32_t reserved;
+    int64_t mask_strides[4];
+} b2a_sdpa_desc;
+
+/* Scratch bytes b2a_sdpa_forward needs for `desc` (0 is a valid answer).  Plays the part of
+ * IOperationExec::GetWorkBufferRequest (src/cuda_operation_base.hpp:56, src/memory_manager/cuda_workbuffers.hpp:18-22). */
+int b2a_sdpa_workspace_bytes(const b2a_sdpa_desc* desc, int sm_count, size_t* out_bytes);
+
+/* Enqueue the fused attention.  Plays the part of the Execute() bodies listed above. */
+int b2a_sdpa_forward(const b2a_sdpa_desc* desc, const void* q, const void* k, const void* v, const void* mask,
+                     void* o, void* workspace, size_t workspace_bytes, int32_t* status, b2a_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * PagedAttentionExtension
+ *
+ * Replaces the reference's only KV-cache mechanism: ReadValueOp::Execute (src/ops/read_value.cpp:31-72),
+ * the Concat of past and new K/V (src/kernels/concat.cu:16-32), AssignOp::Execute (src/ops/assign.cpp:29-56)
+ * over CudaVariableState (src/cuda_variable_state.hpp:31-183), followed by the decomposed SDPA above.
+ *
+ * query [num_tokens, Hq*D], key [num_tokens, Hkv*D], value [num_tokens, Hkv*Dv], out [num_tokens, Hq*Dv],
+ * row-major, dense.  Caches are block pools [num_blocks_total, Hkv, chunk]:
+ *   kv_dtype == B2A_U8 : chunk = block_size*D u8 values (token-major), then block_size f16 scales, then
+ *                        block_size f16 zero-points (per token, asymmetric: x = (u8 - zp) * scale);
+ *                        chunk bytes = block_size*(D+4);
+ *   kv_dtype == B2A_F16/B2A_BF16 : chunk = [block_size, D] elements of that type.
+ * past_lens [num_seqs], subsequence_begins [num_seqs+1], block_indices [sum blocks],
+ * block_indices_begins [num_seqs+1]: int32, device.  Token t of sequence s sits at cache position
+ * past_lens[s] + (t - subsequence_begins[s]) and attends to positions 0..that, or only to the last
+ * `sliding_window` of them when sliding_window > 0.
+ * max_context_len bounds past_lens[s] + q_len[s] over all s; it sizes grids and the workspace so that the
+ * same launch is valid for any lengths below it (graph replay with changed lengths).
+ * max_q_len bounds q_len[s]; 1 selects the decode kernel.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct b2a_paged_desc {
+    int32_t q_dtype;  /* B2A_F16 | B2A_BF16 | B2A_F32: type of query, key, value and out */
+    int32_t kv_dtype; /* B2A_U8 | B2A_F16 | B2A_BF16 */
+    int32_t Hq, Hkv, D, Dv, block_size;
+    int32_t num_seqs, num_tokens, num_blocks_total;
+    int32_t max_context_len, max_q_len;
+    float scale; /* 0 selects 1/sqrt(D) */
+    int32_t sliding_window;
+} b2a_paged_desc;
+
+/* Bytes of one (block, KV head) chunk of a cache of `kv_dtype` with head size d. */
+size_t b2a_paged_chunk_bytes(int32_t kv_dtype, int32_t block_size, int32_t d);
+
+/* Scratch bytes b2a_paged_attention needs (split-K partials).  GetWorkBufferRequest counterpart. */
+int b2a_paged_workspace_bytes(const b2a_paged_desc* desc, int sm_count, size_t* out_bytes);
+
+/* Append this step's K/V rows to the pools through the block table, quantising to u8 when the cache is u8.
+ * Counterpart of the Concat + Assign pair (src/kernels/concat.cu:16-32, src/ops/assign.cpp:29-56). */
+int b2a_paged_kv_store(const b2a_paged_desc* desc, const void* key, const void* value, void* k_cache,
+                       void* v_cache, const int32_t* past_lens, const int32_t* subsequence_begins,
+                       const int32_t* block_indices, const int32_t* block_indices_begins, int32_t* status,
+                       b2a_stream_t stream);
+
+/* Attention of every query token over its sequence's cache (call after b2a_paged_kv_store of the same step).
+ * Counterpart of ReadValue + decomposed SDPA (src/ops/read_value.cpp:31-72 and the SDPA chain above). */
+int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const void* k_cache, const void* v_cache,
+                        const int32_t* past_lens, const int32_t* subsequence_begins, const int32_t* block_indices,
+                        const int32_t* block_indices_begins, void* out, void* workspace, size_t workspace_bytes,
+                        int32_t* status, b2a_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * KV block manager (host only; no CUDA calls).  Owns the free list of a pool of `num_blocks` physical
+ * blocks and the per-sequence block lists, and emits the four int32 tables of a step.  It takes the place
+ * CudaVariableState has for the contiguous cache (src/cuda_variable_state.hpp:31-183: reset / grow / hand
+ * out the buffer), for a paged pool.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct b2a_kvmgr b2a_kvmgr;
+
+int b2a_kvmgr_create(int32_t num_blocks, int32_t block_size, uint64_t shuffle_seed, b2a_kvmgr** out);
+void b2a_kvmgr_destroy(b2a_kvmgr* m);
+int b2a_kvmgr_add_sequence(b2a_kvmgr* m, int64_t seq_id);
+int b2a_kvmgr_free_sequence(b2a_kvmgr* m, int64_t seq_id);
+int32_t b2a_kvmgr_free_blocks(const b2a_kvmgr* m);
+int32_t b2a_kvmgr_sequence_len(const b2a_kvmgr* m, int64_t seq_id); /* -1 if unknown */
+/* Reserve blocks for q_lens[i] new tokens of seq_ids[i] (all or nothing), fill the step tables (host arrays:
+ * past_lens[n], subsequence_begins[n+1], block_indices[capacity], block_indices_begins[n+1]) and advance
+ * the sequences' lengths.  *num_block_indices and *max_context_len receive the totals. */
+int b2a_kvmgr_schedule_step(b2a_kvmgr* m, const int64_t* seq_ids, const int32_t* q_lens, int32_t n,
+                            int32_t* past_lens, int32_t* subsequence_begins, int32_t* block_indices,
+                            int32_t block_indices_capacity, int32_t* block_indices_begins,
+                            int32_t* num_block_indices, int32_t* max_context_len);
+
+const char* b2a_status_string(int status);
+int b2a_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2A_H_ */

@@ -1,0 +1,43 @@
+// Host-side launchers of the kernels, one per .cu file; api.cu validates descriptors and dispatches to these.
+#pragma once
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace b2a {
+
+// attn_generic.cu
+int sdpa_generic_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4],
+                        const int64_t (&vs)[4], const int64_t (&os)[4], const void* q, const void* k, const void* v,
+                        const void* mask, void* o, int32_t* status, cudaStream_t stream);
+int paged_generic_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
+                         const PagedTables& t, void* out, int32_t* status, cudaStream_t stream);
+
+// paged_kv_store.cu
+int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* value, void* k_cache, void* v_cache,
+                          const PagedTables& t, int32_t* status, cudaStream_t stream);
+
+// paged_decode.cu — split-K decode over a u8 cache (D = Dv = 128, block 16, one query token per sequence)
+struct DecodePlan {
+    int blocks_per_cta;  // logical KV blocks one CTA walks
+    int max_splits;      // CTAs per (sequence, KV head)
+    size_t workspace_bytes;
+};
+bool paged_decode_supported(const b2a_paged_desc& d);
+DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count);
+int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
+                        const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
+                        cudaStream_t stream);
+
+// sdpa_tcgen05.cu — TMA + tcgen05 flash prefill (f16 / bf16, D = Dv = 128)
+bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4],
+                       const int64_t (&vs)[4], const int64_t (&os)[4], const void* q, const void* k, const void* v,
+                       const void* o);
+int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
+                   const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
+                   cudaStream_t stream);
+
+int device_sm_count();
+
+}  // namespace b2a

@@ -1,0 +1,488 @@
+// Split-K paged decode over a u8 KV cache: one query token per sequence, D = Dv = 128, 16-token blocks.
+//
+// The step is bound by HBM: every cached token costs Hkv * 2 * (128 + 4) bytes and a handful of flops.  With
+// grouped-query attention the flops are not free, though: G query heads share each K/V byte, and at G = 8 plain
+// FP32 FMAs (2*G*128 per token and KV head for QK^T, as many for PV, plus the u8 conversions) need more issue
+// slots than the memory system leaves time for.  So the two small contractions run on the warp-level MMA
+// (m16n8k16, f16 in, f32 accumulate) with the u8 codes fed in UNSCALED:
+//     S[t][g]  = scale_k[t] * ( sum_d code_k[t][d] * Q[g][d]  -  zp_k[t] * sum_d Q[g][d] )
+//     O[g][d]  = sum_t P'[g][t] * code_v[t][d]  -  sum_t P'[g][t] * zp_v[t],      P'[g][t] = p[g][t] * scale_v[t]
+// Codes 0..255 are exact in f16, products are exact, accumulation is f32: no de-quantisation rounding at all on
+// the K side, one f16 rounding of P' on the V side.
+//
+// Grid = (split, KV head, sequence); a CTA of 4 warps walks `blocks_per_cta` logical blocks of one sequence and KV
+// head, warp w taking blocks w, w+4, ...  Each warp runs its own 4-stage cp.async pipeline: a stage holds the K chunk
+// and the V chunk of one block (2 x 2112 bytes), copied as 16-byte pieces, 512 contiguous bytes per warp
+// instruction, into shared memory with an XOR swizzle of the 16-byte column so that the MMA fragments are read
+// with conflict-free 128-bit loads.  Online softmax per warp (row max by warp shuffle), partials of the 4 warps
+// merged in shared memory, one (m, l, O[G][128]) partial per CTA into the workspace; a second kernel merges the
+// splits.  Lengths and tables are read on the device, the grid depends only on max_context_len, so a captured
+// launch stays valid when lengths change.
+#include "launch.cuh"
+
+namespace b2a {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kBS = 16;
+constexpr int kChunk = kBS * (kD + 4);   // 2112 bytes: 2048 codes, 16 f16 scales, 16 f16 zero-points
+constexpr int kStage = 2 * kChunk;       // K chunk then V chunk
+constexpr int kWarps = 4;
+constexpr int kStages = 4;
+constexpr int kSmemBytes = kWarps * kStages * kStage;
+constexpr float kNegBig = -1.0e30f;      // finite "minus infinity" for the running max (keeps exp2 arguments NaN-free)
+
+struct DecodeParams {
+    const void* query;
+    const uint8_t* k_cache;
+    const uint8_t* v_cache;
+    PagedTables t;
+    void* out;
+    float* ws_o;   // [num_seqs*Hq][max_splits][128]
+    float* ws_ml;  // [num_seqs*Hq][max_splits][2]
+    int Hq, Hkv, G;
+    int blocks_per_cta, max_splits;
+    int sliding_window;
+    float scale_log2;  // softmax scale * log2(e)
+    int32_t* status;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ float lds_h(uint32_t addr) {
+    unsigned short r;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(r) : "r"(addr));
+    return __half2float(__ushort_as_half(r));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// 0x64XX as f16 is 1024 + XX: insert the byte under the exponent pattern, subtract 1024 — exact for 0..255.
+__device__ __forceinline__ uint32_t sub1024(uint32_t h2bits) {
+    const __half2 v = *reinterpret_cast<const __half2*>(&h2bits);
+    const uint32_t kbits = 0x64006400u;
+    const __half2 r = __hsub2(v, *reinterpret_cast<const __half2*>(&kbits));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+// half2(float(byte 2*pair), float(byte 2*pair+1)) of one word
+template <int PAIR>
+__device__ __forceinline__ uint32_t bytes_to_h2(uint32_t w) {
+    return sub1024(__byte_perm(w, 0x64646464u, PAIR == 0 ? 0x4140 : 0x4342));
+}
+// half2(float(byte e of w0), float(byte e of w1))
+__device__ __forceinline__ uint32_t bytepair_to_h2(uint32_t w0, uint32_t w1, int e) {
+    const uint32_t r = __byte_perm(w0, w1, ((4 + e) << 8) | e);
+    return sub1024((r & 0x00FF00FFu) | 0x64006400u);
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float h2_lo(uint32_t v) { return __half2float(__ushort_as_half(v & 0xFFFFu)); }
+__device__ __forceinline__ float h2_hi(uint32_t v) { return __half2float(__ushort_as_half(v >> 16)); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t load_q_pair(const T* p);  // two consecutive query values as half2 bits
+template <>
+__device__ __forceinline__ uint32_t load_q_pair<__half>(const __half* p) {
+    return *reinterpret_cast<const uint32_t*>(p);
+}
+template <>
+__device__ __forceinline__ uint32_t load_q_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return pack_h2(__bfloat162float(p[0]), __bfloat162float(p[1]));
+}
+
+__device__ __forceinline__ int first_block_of(int ctx, int sliding_window) {
+    const int first_pos = sliding_window > 0 ? max(0, ctx - sliding_window) : 0;
+    return first_pos / kBS;
+}
+
+template <typename T, int NT>
+__global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tid4 = lane & 3;
+
+    const int tok = p.t.subsequence_begins[seq];
+    const int qlen = p.t.subsequence_begins[seq + 1] - tok;
+    if (qlen <= 0) return;
+    const int past = p.t.past_lens[seq];
+    const int ctx = past + 1;  // the query token sits at position `past` and sees 0..past
+    const int nblk = (ctx + kBS - 1) / kBS;
+    if (qlen != 1 || past < 0 || nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
+        if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
+        return;
+    }
+    const int first_pos = p.sliding_window > 0 ? max(0, ctx - p.sliding_window) : 0;
+    const int blk_lo = first_block_of(ctx, p.sliding_window);
+    if (nblk - blk_lo > p.max_splits * p.blocks_per_cta) {  // context longer than the max_context_len the grid was sized for
+        if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
+        return;
+    }
+    const int my_lo = blk_lo + split * p.blocks_per_cta;
+    const int my_hi = min(nblk, my_lo + p.blocks_per_cta);
+    if (my_lo >= my_hi) return;
+
+    // blocks of this warp: my_lo + warp + 4*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
+    const int n_w = (my_hi - my_lo - warp + kWarps - 1) / kWarps;
+    const int32_t* btab = p.t.block_indices + p.t.block_indices_begins[seq];
+    int my_phys = 0;
+    if (lane < n_w) {
+        my_phys = btab[my_lo + warp + kWarps * lane];
+        if (my_phys < 0 || my_phys >= p.t.num_blocks_total) {
+            report(p.status, B2A_DEV_BAD_BLOCK);
+            my_phys = -1;
+        }
+    }
+
+    const uint32_t smem_warp = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStage);
+    const size_t head_stride = kChunk;                         // chunks of one block: [Hkv][2112]
+    const size_t block_stride = static_cast<size_t>(p.Hkv) * kChunk;
+
+    auto issue = [&](int i) {
+        // stage i % kStages <- block i of this warp; an out-of-range physical index copies nothing
+        const int phys = __shfl_sync(0xffffffffu, my_phys, i & 31);
+        if (phys >= 0) {
+            const uint8_t* kc = p.k_cache + phys * block_stride + hk * head_stride;
+            const uint8_t* vc = p.v_cache + phys * block_stride + hk * head_stride;
+            const uint32_t st = smem_warp + (i % kStages) * kStage;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int piece = r * 32 + lane;          // 16-byte piece of the 2048 code bytes
+                const int row = piece >> 3, col = piece & 7;
+                const uint32_t off = row * 128 + ((col ^ (row & 7)) << 4);
+                cp_async16(st + off, kc + piece * 16);
+                cp_async16(st + kChunk + off, vc + piece * 16);
+            }
+            if (lane < 4) cp_async16(st + 2048 + lane * 16, kc + 2048 + lane * 16);
+            else if (lane < 8) cp_async16(st + kChunk + 2048 + (lane - 4) * 16, vc + 2048 + (lane - 4) * 16);
+        }
+    };
+
+    // ---- query fragments (B operand of QK^T) and per-head sums of Q
+    const T* qrow = reinterpret_cast<const T*>(p.query) + (static_cast<size_t>(tok) * p.Hq + hk * p.G) * kD;
+    uint32_t qf[NT][8][2];
+    float qsum_a[NT], qsum_b[NT];  // heads nt*8 + 2*tid4 and + 1
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int n = nt * 8 + gid;
+        float part = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t b0 = 0, b1 = 0;
+            if (n < p.G) {
+                const T* src = qrow + n * kD + tid4 * 32 + 4 * j;
+                b0 = load_q_pair<T>(src);
+                b1 = load_q_pair<T>(src + 2);
+            }
+            qf[nt][j][0] = b0;
+            qf[nt][j][1] = b1;
+            part += h2_lo(b0) + h2_hi(b0) + h2_lo(b1) + h2_hi(b1);
+        }
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);  // sum of Q[head nt*8+gid][:]
+        qsum_a[nt] = __shfl_sync(0xffffffffu, part, 8 * tid4);
+        qsum_b[nt] = __shfl_sync(0xffffffffu, part, 8 * tid4 + 4);
+    }
+
+    float acc[NT][8][4];
+    float m_a[NT], m_b[NT], l_a[NT], l_b[NT], corr_a[NT], corr_b[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        m_a[nt] = m_b[nt] = kNegBig;
+        l_a[nt] = l_b[nt] = corr_a[nt] = corr_b[nt] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[nt][j][0] = acc[nt][j][1] = acc[nt][j][2] = acc[nt][j][3] = 0.f;
+    }
+
+    // ---- pipeline prologue
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < n_w) issue(s);
+        cp_async_commit();
+    }
+
+    const int sw_k = (gid & 7);  // swizzle key of rows gid and gid+8
+    for (int i = 0; i < n_w; ++i) {
+        if (i + kStages - 1 < n_w) issue(i + kStages - 1);
+        cp_async_commit();
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+
+        const uint32_t sK = smem_warp + (i % kStages) * kStage;
+        const uint32_t sV = sK + kChunk;
+        const int lb = my_lo + warp + kWarps * i;
+        const bool blk_ok = __shfl_sync(0xffffffffu, my_phys, i & 31) >= 0;
+        const int pos0 = lb * kBS + gid, pos1 = pos0 + 8;
+        const bool ok0 = blk_ok && pos0 < ctx && pos0 >= first_pos;
+        const bool ok1 = blk_ok && pos1 < ctx && pos1 >= first_pos;
+
+        // ---- S^T = codes_K . Q^T  (rows = tokens gid, gid+8; columns = heads)
+        float sc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        {
+            const uint4 x0 = lds128(sK + gid * 128 + (((2 * tid4) ^ sw_k) << 4));
+            const uint4 x1 = lds128(sK + gid * 128 + (((2 * tid4 + 1) ^ sw_k) << 4));
+            const uint4 y0 = lds128(sK + (gid + 8) * 128 + (((2 * tid4) ^ sw_k) << 4));
+            const uint4 y1 = lds128(sK + (gid + 8) * 128 + (((2 * tid4 + 1) ^ sw_k) << 4));
+            const uint32_t wl[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            const uint32_t wh[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t a0 = bytes_to_h2<0>(wl[j]), a1 = bytes_to_h2<0>(wh[j]);
+                const uint32_t a2 = bytes_to_h2<1>(wl[j]), a3 = bytes_to_h2<1>(wh[j]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma16816(sc[nt], a0, a1, a2, a3, qf[nt][j][0], qf[nt][j][1]);
+            }
+        }
+        // per-token scale / zero-point (forced to 0 for tokens outside the context: unused slots may hold anything)
+        const float sk0 = ok0 ? lds_h(sK + 2048 + 2 * gid) * p.scale_log2 : 0.f;
+        const float sk1 = ok1 ? lds_h(sK + 2048 + 2 * (gid + 8)) * p.scale_log2 : 0.f;
+        const float zk0 = ok0 ? lds_h(sK + 2048 + 32 + 2 * gid) : 0.f;
+        const float zk1 = ok1 ? lds_h(sK + 2048 + 32 + 2 * (gid + 8)) : 0.f;
+        const float sv0 = ok0 ? lds_h(sV + 2048 + 2 * gid) : 0.f;
+        const float sv1 = ok1 ? lds_h(sV + 2048 + 2 * (gid + 8)) : 0.f;
+        const float zv0 = ok0 ? lds_h(sV + 2048 + 32 + 2 * gid) : 0.f;
+        const float zv1 = ok1 ? lds_h(sV + 2048 + 32 + 2 * (gid + 8)) : 0.f;
+
+        uint32_t pb0[NT], pb1[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const float s0 = ok0 ? (sc[nt][0] - zk0 * qsum_a[nt]) * sk0 : -INFINITY;
+            const float s1 = ok0 ? (sc[nt][1] - zk0 * qsum_b[nt]) * sk0 : -INFINITY;
+            const float s2 = ok1 ? (sc[nt][2] - zk1 * qsum_a[nt]) * sk1 : -INFINITY;
+            const float s3 = ok1 ? (sc[nt][3] - zk1 * qsum_b[nt]) * sk1 : -INFINITY;
+            float ta = fmaxf(s0, s2), tb = fmaxf(s1, s3);
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) {
+                ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, o));
+                tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, o));
+            }
+            const float na = fmaxf(m_a[nt], ta), nb = fmaxf(m_b[nt], tb);
+            const float alpha_a = ex2(m_a[nt] - na), alpha_b = ex2(m_b[nt] - nb);
+            m_a[nt] = na;
+            m_b[nt] = nb;
+            const float p0 = ex2(s0 - na), p1 = ex2(s1 - nb), p2 = ex2(s2 - na), p3 = ex2(s3 - nb);
+            l_a[nt] = l_a[nt] * alpha_a + p0 + p2;
+            l_b[nt] = l_b[nt] * alpha_b + p1 + p3;
+            const uint32_t x0 = pack_h2(p0 * sv0, p1 * sv0);  // token gid:   heads a, b
+            const uint32_t x1 = pack_h2(p2 * sv1, p3 * sv1);  // token gid+8: heads a, b
+            corr_a[nt] = corr_a[nt] * alpha_a + h2_lo(x0) * zv0 + h2_lo(x1) * zv1;
+            corr_b[nt] = corr_b[nt] * alpha_b + h2_hi(x0) * zv0 + h2_hi(x1) * zv1;
+            pb0[nt] = movmatrix_trans(x0);  // (P'[head gid][token 2*tid4], P'[head gid][token 2*tid4+1])
+            pb1[nt] = movmatrix_trans(x1);  // tokens 2*tid4+8, +9
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[nt][j][0] *= alpha_a;
+                acc[nt][j][1] *= alpha_b;
+                acc[nt][j][2] *= alpha_a;
+                acc[nt][j][3] *= alpha_b;
+            }
+        }
+
+        // ---- O^T += codes_V^T . P'^T  (rows = d, columns = heads, contraction over the 16 tokens)
+        {
+            const int t0 = 2 * tid4;
+            const uint4 v0 = lds128(sV + t0 * 128 + ((gid ^ (t0 & 7)) << 4));
+            const uint4 v1 = lds128(sV + (t0 + 1) * 128 + ((gid ^ ((t0 + 1) & 7)) << 4));
+            const uint4 v2 = lds128(sV + (t0 + 8) * 128 + ((gid ^ (t0 & 7)) << 4));
+            const uint4 v3 = lds128(sV + (t0 + 9) * 128 + ((gid ^ ((t0 + 1) & 7)) << 4));
+            const uint32_t w0[4] = {v0.x, v0.y, v0.z, v0.w}, w1[4] = {v1.x, v1.y, v1.z, v1.w};
+            const uint32_t w2[4] = {v2.x, v2.y, v2.z, v2.w}, w3[4] = {v3.x, v3.y, v3.z, v3.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int w = j >> 1, e = (j & 1) * 2;
+                const uint32_t a0 = bytepair_to_h2(w0[w], w1[w], e);      // d = gid*16+2j,   tokens t0, t0+1
+                const uint32_t a1 = bytepair_to_h2(w0[w], w1[w], e + 1);  // d = gid*16+2j+1
+                const uint32_t a2 = bytepair_to_h2(w2[w], w3[w], e);      // tokens t0+8, t0+9
+                const uint32_t a3 = bytepair_to_h2(w2[w], w3[w], e + 1);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma16816(acc[nt][j], a0, a1, a2, a3, pb0[nt], pb1[nt]);
+            }
+        }
+        __syncwarp();  // every lane is done with this stage before it is refilled
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // ---- warp partial: reduce l and corr over the 8 token rows, park (O - corr, m, l) in this warp's smem
+    float* wbuf = reinterpret_cast<float*>(smem + warp * (kStages * kStage));  // [NT*8][128] O, then [NT*8] m, [NT*8] l
+    constexpr int GP = NT * 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+            l_a[nt] += __shfl_xor_sync(0xffffffffu, l_a[nt], o);
+            l_b[nt] += __shfl_xor_sync(0xffffffffu, l_b[nt], o);
+            corr_a[nt] += __shfl_xor_sync(0xffffffffu, corr_a[nt], o);
+            corr_b[nt] += __shfl_xor_sync(0xffffffffu, corr_b[nt], o);
+        }
+        const int ga = nt * 8 + 2 * tid4, gb = ga + 1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int d = gid * 16 + 2 * j;
+            *reinterpret_cast<float2*>(wbuf + ga * kD + d) =
+                make_float2(acc[nt][j][0] - corr_a[nt], acc[nt][j][2] - corr_a[nt]);
+            *reinterpret_cast<float2*>(wbuf + gb * kD + d) =
+                make_float2(acc[nt][j][1] - corr_b[nt], acc[nt][j][3] - corr_b[nt]);
+        }
+        if (gid == 0) {
+            wbuf[GP * kD + ga] = m_a[nt];
+            wbuf[GP * kD + gb] = m_b[nt];
+            wbuf[GP * kD + GP + ga] = l_a[nt];
+            wbuf[GP * kD + GP + gb] = l_b[nt];
+        }
+    }
+    __syncthreads();
+
+    // ---- merge the 4 warps: thread = column d
+    const int d = tid;
+    for (int g = 0; g < p.G; ++g) {
+        float mw[kWarps], mc = kNegBig;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float* wb = reinterpret_cast<const float*>(smem + w * (kStages * kStage));
+            mw[w] = wb[GP * kD + g];
+            mc = fmaxf(mc, mw[w]);
+        }
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float* wb = reinterpret_cast<const float*>(smem + w * (kStages * kStage));
+            const float f = ex2(mw[w] - mc);
+            o += wb[g * kD + d] * f;
+            l += wb[GP * kD + GP + g] * f;
+        }
+        const size_t slot = (static_cast<size_t>(seq) * p.Hq + hk * p.G + g) * p.max_splits + split;
+        p.ws_o[slot * kD + d] = o;
+        if (d == 0) {
+            p.ws_ml[slot * 2] = mc;
+            p.ws_ml[slot * 2 + 1] = l;
+        }
+    }
+}
+
+// Merge the split partials of one (sequence, query head): out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
+template <typename T>
+__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodeParams p) {
+    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const int tok = p.t.subsequence_begins[seq];
+    const int qlen = p.t.subsequence_begins[seq + 1] - tok;
+    if (qlen != 1) return;
+    const int past = p.t.past_lens[seq];
+    if (past < 0) return;
+    const int ctx = past + 1;
+    const int nblk = (ctx + kBS - 1) / kBS;
+    if (nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) return;
+    const int blk_lo = first_block_of(ctx, p.sliding_window);
+    const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
+    const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
+    float mc = kNegBig;
+    for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, p.ws_ml[(base + s) * 2]);
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float f = ex2(p.ws_ml[(base + s) * 2] - mc);
+        o += p.ws_o[(base + s) * kD + d] * f;
+        l += p.ws_ml[(base + s) * 2 + 1] * f;
+    }
+    T* orow = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD;
+    orow[d] = from_f32<T>(l > 0.f ? o / l : 0.f);
+}
+
+template <typename T, int NT>
+int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
+    auto kern = paged_decode_kernel<T, NT>;
+    static bool configured[64] = {};  // per device; setting the attribute twice is harmless
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B2A_ERR_CUDA;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    dim3 grid(p.max_splits, p.Hkv, num_seqs);
+    kern<<<grid, kWarps * 32, kSmemBytes, stream>>>(p);
+    if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+    paged_decode_merge_kernel<T><<<dim3(p.Hq, num_seqs), kD, 0, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+}
+
+}  // namespace
+
+bool paged_decode_supported(const b2a_paged_desc& d) {
+    const int g = d.Hkv > 0 ? d.Hq / d.Hkv : 0;
+    return d.kv_dtype == B2A_U8 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) && d.D == kD && d.Dv == kD &&
+           d.block_size == kBS && d.max_q_len == 1 && g >= 1 && g <= 16 && d.num_tokens == d.num_seqs;
+}
+
+DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count) {
+    // Aim at ~4 CTAs per resident slot (3 CTAs fit per SM) so that the tail of the last wave is short, while a
+    // CTA still walks at least 16 blocks (4 per warp) to amortise its prologue and the merge.
+    const long long nblk_max = (static_cast<long long>(d.max_context_len) + kBS - 1) / kBS;
+    const long long total = nblk_max * d.Hkv * d.num_seqs;
+    const long long target_ctas = static_cast<long long>(sm_count) * 3 * 4;
+    long long bpc = (total + target_ctas - 1) / target_ctas;
+    bpc = ((bpc + 3) / 4) * 4;
+    if (bpc < 16) bpc = 16;
+    if (bpc > 128) bpc = 128;
+    DecodePlan plan;
+    plan.blocks_per_cta = static_cast<int>(bpc);
+    plan.max_splits = static_cast<int>((nblk_max + bpc - 1) / bpc);
+    if (plan.max_splits < 1) plan.max_splits = 1;
+    plan.workspace_bytes = static_cast<size_t>(d.num_seqs) * d.Hq * plan.max_splits * (kD + 2) * sizeof(float);
+    return plan;
+}
+
+int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
+                        const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
+                        cudaStream_t stream) {
+    DecodeParams p{};
+    p.query = query;
+    p.k_cache = static_cast<const uint8_t*>(k_cache);
+    p.v_cache = static_cast<const uint8_t*>(v_cache);
+    p.t = t;
+    p.out = out;
+    const size_t rows = static_cast<size_t>(d.num_seqs) * d.Hq * plan.max_splits;
+    p.ws_o = static_cast<float*>(workspace);
+    p.ws_ml = p.ws_o + rows * kD;
+    p.Hq = d.Hq;
+    p.Hkv = d.Hkv;
+    p.G = d.Hq / d.Hkv;
+    p.blocks_per_cta = plan.blocks_per_cta;
+    p.max_splits = plan.max_splits;
+    p.sliding_window = d.sliding_window;
+    p.scale_log2 = d.scale * kLog2e;
+    p.status = status;
+    const bool two = p.G > 8;
+    if (d.q_dtype == B2A_F16) return two ? launch_t<__half, 2>(p, d.num_seqs, stream) : launch_t<__half, 1>(p, d.num_seqs, stream);
+    return two ? launch_t<__nv_bfloat16, 2>(p, d.num_seqs, stream) : launch_t<__nv_bfloat16, 1>(p, d.num_seqs, stream);
+}
+
+}  // namespace b2a

@@ -1,0 +1,356 @@
+"""Host-side callers of the C ABI for Python users and for the parity tests.
+
+The operator classes mirror the interface every nvidia_plugin operation implements
+(``modules/nvidia_plugin/src/cuda_operation_base.hpp:33-60``): construct once from the node's static
+attributes, ask ``GetWorkBufferRequest()`` for scratch sizes, then ``Execute(inputs, outputs, workbuffers)``
+on device buffers, any number of times, on any stream.  ``torch`` is used for device memory and streams only;
+all arithmetic happens in libb2a.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import B2AError, PagedDesc, SdpaDesc, check
+
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.uint8: _lib.U8}
+
+
+def _dtype_code(t: torch.dtype) -> int:
+    if t not in _DTYPES:
+        raise TypeError(f"unsupported element type {t}")
+    return _DTYPES[t]
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream]) -> int:
+    return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("libb2a works on device memory only: pass CUDA tensors (there is no CPU path)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def sm_count() -> int:
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+# ------------------------------------------------------------------------------------------------------------
+# ScaledDotProductAttention
+# ------------------------------------------------------------------------------------------------------------
+
+def _as_bhsd(x: torch.Tensor) -> torch.Tensor:
+    """[..., S, E] -> a 4-D [B, H, S, E] view (rank 3 is [N, S, E]: batch N, one head)."""
+    if x.dim() < 3:
+        raise ValueError("SDPA operands need rank >= 3")
+    if x.dim() == 3:
+        return x.unsqueeze(1)
+    if x.dim() == 4:
+        return x
+    return x.reshape(-1, *x.shape[-3:])
+
+
+def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[torch.Tensor] = None,
+         scale: Optional[float] = None, causal: bool = False, out: Optional[torch.Tensor] = None,
+         stream: Optional[torch.cuda.Stream] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``ov::op::v13::ScaledDotProductAttention`` on device tensors: softmax(q k^T * scale + mask) v.
+
+    q [..., Hq, Sq, E], k [..., Hkv, Skv, E], v [..., Hkv, Skv, Ev]; Hq a multiple of Hkv.  ``causal`` ignores
+    ``attn_mask``.  A boolean mask keeps where true, a floating mask is added.  Strided views are passed
+    through as they are, provided the innermost stride is 1.
+    """
+    _require_cuda(q, k, v, attn_mask, out)
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q, k and v must share one element type")
+    q4, k4, v4 = _as_bhsd(q), _as_bhsd(k), _as_bhsd(v)
+    fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+    q4, k4, v4 = fix(q4), fix(k4), fix(v4)
+    B, Hq, Sq, D = q4.shape
+    Bk, Hkv, Skv, Dk = k4.shape
+    Dv = v4.shape[-1]
+    if Bk != B or v4.shape[:3] != k4.shape[:3] or Dk != D:
+        raise ValueError(f"inconsistent SDPA shapes q{tuple(q.shape)} k{tuple(k.shape)} v{tuple(v.shape)}")
+    out_shape = (*q.shape[:-1], Dv)
+    if out is None:
+        out = torch.empty(out_shape, dtype=q.dtype, device=q.device)
+    o4 = _as_bhsd(out)
+    if o4.stride(-1) != 1:
+        raise ValueError("the output needs a unit innermost stride")
+
+    d = SdpaDesc()
+    d.dtype = _dtype_code(q.dtype)
+    d.B, d.Hq, d.Hkv, d.Sq, d.Skv, d.D, d.Dv = B, Hq, Hkv, Sq, Skv, D, Dv
+    d.causal = int(bool(causal))
+    d.scale = 0.0 if scale is None else float(scale)
+    d.q_strides[:] = q4.stride()
+    d.k_strides[:] = k4.stride()
+    d.v_strides[:] = v4.stride()
+    d.o_strides[:] = o4.stride()
+    mask_t = None
+    d.mask_kind = _lib.MASK_NONE
+    if attn_mask is not None and not causal:
+        m = attn_mask
+        if m.dtype == torch.bool:
+            d.mask_kind = _lib.MASK_BOOL
+            m = m.view(torch.uint8) if m.is_contiguous() else m.to(torch.uint8)
+        else:
+            d.mask_kind = _lib.MASK_ADD
+            m = m.to(q.dtype)
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        if m.dim() > 4:
+            m = m.reshape(-1, *m.shape[-3:])
+        m = m.expand(B, Hq, Sq, Skv)  # broadcast dimensions get stride 0
+        d.mask_strides[:] = m.stride()
+        mask_t = m
+    lib = _lib.load()
+    ws = C.c_size_t(0)
+    check(lib.b2a_sdpa_workspace_bytes(C.byref(d), sm_count(), C.byref(ws)), "b2a_sdpa_workspace_bytes")
+    wbuf = torch.empty(ws.value, dtype=torch.uint8, device=q.device) if ws.value else None
+    check(lib.b2a_sdpa_forward(C.byref(d), q4.data_ptr(), k4.data_ptr(), v4.data_ptr(), _ptr(mask_t),
+                               o4.data_ptr(), _ptr(wbuf), ws.value, _ptr(status), _stream_ptr(stream)),
+          "b2a_sdpa_forward")
+    return out
+
+
+class SdpaOp:
+    """Operator-shaped wrapper: static attributes at construction, device buffers at ``Execute``.
+
+    Mirrors what a nvidia_plugin operation for ``ScaledDotProductAttention`` looks like
+    (``cuda_operation_base.hpp:80-149``); inputs are (q, k, v[, attention_mask[, scale]]).
+    """
+
+    type_name = "ScaledDotProductAttention"
+
+    def __init__(self, causal: bool = False):
+        self.causal = bool(causal)
+
+    def GetCudaGraphCompatibility(self) -> str:
+        return "FULL"  # launches only; no allocation, no synchronisation
+
+    def GetWorkBufferRequest(self):
+        return {"immutable_sizes": [], "mutable_sizes": []}
+
+    def Execute(self, inputs: Sequence[torch.Tensor], outputs: Sequence[torch.Tensor], workbuffers=None,
+                stream: Optional[torch.cuda.Stream] = None) -> None:
+        if not 3 <= len(inputs) <= 5 or len(outputs) != 1:
+            raise ValueError("ScaledDotProductAttention takes 3 to 5 inputs and 1 output")
+        mask = inputs[3] if len(inputs) > 3 else None
+        scale = None
+        if len(inputs) > 4 and inputs[4] is not None:
+            s = inputs[4]
+            scale = float(s.item()) if isinstance(s, torch.Tensor) else float(s)
+        sdpa(inputs[0], inputs[1], inputs[2], mask, scale, self.causal, out=outputs[0], stream=stream)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# PagedAttentionExtension
+# ------------------------------------------------------------------------------------------------------------
+
+@dataclass
+class PagedKvCache:
+    """Device-resident block pools [num_blocks, Hkv, chunk_bytes] (u8) or [num_blocks, Hkv, bs, D] (f16/bf16)."""
+    k: torch.Tensor
+    v: torch.Tensor
+    hkv: int
+    d: int
+    dv: int
+    block_size: int
+    kv_dtype: torch.dtype
+
+    @staticmethod
+    def allocate(num_blocks: int, hkv: int, d: int, block_size: int = 16, kv_dtype: torch.dtype = torch.uint8,
+                 device="cuda", dv: Optional[int] = None, poison: Optional[int] = 0xFF) -> "PagedKvCache":
+        dv = d if dv is None else dv
+        lib = _lib.load()
+        code = _dtype_code(kv_dtype)
+        ck, cv = lib.b2a_paged_chunk_bytes(code, block_size, d), lib.b2a_paged_chunk_bytes(code, block_size, dv)
+        if ck == 0 or cv == 0:
+            raise ValueError("unsupported cache geometry")
+        mk = lambda cb: (torch.full((num_blocks, hkv, cb), poison, dtype=torch.uint8, device=device)
+                         if poison is not None else torch.empty((num_blocks, hkv, cb), dtype=torch.uint8, device=device))
+        return PagedKvCache(mk(ck), mk(cv), hkv, d, dv, block_size, kv_dtype)
+
+    @property
+    def num_blocks(self) -> int:
+        return self.k.shape[0]
+
+
+def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int, max_context_len: int,
+                max_q_len: int, scale: Optional[float], sliding_window: int) -> PagedDesc:
+    d = PagedDesc()
+    d.q_dtype = _dtype_code(q_dtype)
+    d.kv_dtype = _dtype_code(cache.kv_dtype)
+    d.Hq, d.Hkv, d.D, d.Dv, d.block_size = hq, cache.hkv, cache.d, cache.dv, cache.block_size
+    d.num_seqs, d.num_tokens, d.num_blocks_total = num_seqs, num_tokens, cache.num_blocks
+    d.max_context_len, d.max_q_len = max_context_len, max_q_len
+    d.scale = 0.0 if scale is None else float(scale)
+    d.sliding_window = int(sliding_window)
+    return d
+
+
+def _i32(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise TypeError("step tables must be contiguous int32 device tensors")
+    return t
+
+
+def paged_kv_store(key: torch.Tensor, value: torch.Tensor, cache: PagedKvCache, past_lens, subsequence_begins,
+                   block_indices, block_indices_begins, stream=None, status: Optional[torch.Tensor] = None) -> None:
+    """Append key [tokens, Hkv*D] / value [tokens, Hkv*Dv] to the pools through the block table."""
+    _require_cuda(key, value, cache.k, cache.v, past_lens, subsequence_begins, block_indices, block_indices_begins)
+    if key.dtype != value.dtype or not key.is_contiguous() or not value.is_contiguous():
+        raise ValueError("key and value must be dense and share one element type")
+    num_tokens, num_seqs = key.shape[0], past_lens.shape[0]
+    if key.shape[1] != cache.hkv * cache.d or value.shape[1] != cache.hkv * cache.dv or value.shape[0] != num_tokens:
+        raise ValueError("key/value row width does not match the cache geometry")
+    d = _paged_desc(key.dtype, cache, cache.hkv, num_seqs, num_tokens, 0, 0, None, 0)
+    check(_lib.load().b2a_paged_kv_store(C.byref(d), key.data_ptr(), value.data_ptr(), cache.k.data_ptr(),
+                                         cache.v.data_ptr(), _i32(past_lens).data_ptr(),
+                                         _i32(subsequence_begins).data_ptr(), _i32(block_indices).data_ptr(),
+                                         _i32(block_indices_begins).data_ptr(), _ptr(status), _stream_ptr(stream)),
+          "b2a_paged_kv_store")
+
+
+def paged_workspace_bytes(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int,
+                          max_context_len: int, max_q_len: int) -> int:
+    d = _paged_desc(q_dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, None, 0)
+    ws = C.c_size_t(0)
+    check(_lib.load().b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
+    return ws.value
+
+
+def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequence_begins, block_indices,
+                    block_indices_begins, hq: int, max_context_len: int, max_q_len: int,
+                    scale: Optional[float] = None, sliding_window: int = 0, out: Optional[torch.Tensor] = None,
+                    workspace: Optional[torch.Tensor] = None, stream=None,
+                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of query [tokens, Hq*D] over the cache; returns [tokens, Hq*Dv]."""
+    _require_cuda(query, cache.k, cache.v, past_lens, subsequence_begins, block_indices, block_indices_begins, out)
+    if not query.is_contiguous() or query.shape[1] != hq * cache.d:
+        raise ValueError("query must be dense [tokens, Hq*D]")
+    num_tokens, num_seqs = query.shape[0], past_lens.shape[0]
+    if out is None:
+        out = torch.empty((num_tokens, hq * cache.dv), dtype=query.dtype, device=query.device)
+    d = _paged_desc(query.dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, scale, sliding_window)
+    lib = _lib.load()
+    ws = C.c_size_t(0)
+    check(lib.b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
+    if ws.value and (workspace is None or workspace.numel() * workspace.element_size() < ws.value):
+        workspace = torch.empty(ws.value, dtype=torch.uint8, device=query.device)
+    wbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    check(lib.b2a_paged_attention(C.byref(d), query.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                  _i32(past_lens).data_ptr(), _i32(subsequence_begins).data_ptr(),
+                                  _i32(block_indices).data_ptr(), _i32(block_indices_begins).data_ptr(),
+                                  out.data_ptr(), _ptr(workspace), wbytes, _ptr(status), _stream_ptr(stream)),
+          "b2a_paged_attention")
+    return out
+
+
+class PagedAttentionOp:
+    """Operator-shaped wrapper for ``PagedAttentionExtension``.
+
+    ``Execute`` takes the operands in the op's order: query, key, value, key_cache, value_cache, past_lens,
+    subsequence_begins, block_indices, block_indices_begins, scale, sliding_window[, alibi_slopes,
+    max_context_len].  It first appends key/value to the caches, then attends.  The constructor fixes what is
+    static for a compiled model (head counts, head size, block size, capacity maxima), so one instance serves
+    every step of a continuous-batching loop whatever its token and sequence counts.
+    """
+
+    type_name = "PagedAttentionExtension"
+
+    def __init__(self, hq: int, hkv: int, d: int, block_size: int = 16, kv_dtype: torch.dtype = torch.uint8,
+                 max_seqs: int = 256, max_context_len: int = 32768):
+        self.hq, self.hkv, self.d, self.block_size, self.kv_dtype = hq, hkv, d, block_size, kv_dtype
+        self.max_seqs, self.max_context_len = max_seqs, max_context_len
+
+    def GetCudaGraphCompatibility(self) -> str:
+        return "FULL"
+
+    def GetWorkBufferRequest(self, q_dtype=torch.float16):
+        cache = PagedKvCache(torch.empty(0), torch.empty(0), self.hkv, self.d, self.d, self.block_size, self.kv_dtype)
+        cache.k = torch.empty((0, self.hkv, 1), dtype=torch.uint8)
+        n = paged_workspace_bytes(q_dtype, cache, self.hq, self.max_seqs, self.max_seqs, self.max_context_len, 1)
+        return {"immutable_sizes": [], "mutable_sizes": [n] if n else []}
+
+    def Execute(self, inputs: Sequence, outputs: Sequence[torch.Tensor], workbuffers: Optional[dict] = None,
+                stream=None, status: Optional[torch.Tensor] = None) -> None:
+        if len(inputs) < 11 or len(outputs) < 1:
+            raise ValueError("PagedAttentionExtension takes at least 11 inputs and 1 output")
+        (query, key, value, k_cache, v_cache, past_lens, subsequence_begins, block_indices,
+         block_indices_begins, scale, sliding_window) = inputs[:11]
+        if len(inputs) > 11 and inputs[11] is not None and getattr(inputs[11], "numel", lambda: 0)() > 0:
+            raise B2AError(7, "PagedAttentionOp: alibi slopes")
+        max_ctx = int(inputs[12]) if len(inputs) > 12 and inputs[12] is not None else self.max_context_len
+        cache = PagedKvCache(k_cache, v_cache, self.hkv, self.d, self.d, self.block_size, self.kv_dtype)
+        num_tokens, num_seqs = query.shape[0], past_lens.shape[0]
+        max_q_len = 1 if num_tokens == num_seqs else max(1, num_tokens - (num_seqs - 1))
+        paged_kv_store(key, value, cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
+                       stream=stream, status=status)
+        ws = workbuffers["mutable"][0] if workbuffers and workbuffers.get("mutable") else None
+        sc = None if scale is None else (float(scale.item()) if isinstance(scale, torch.Tensor) else float(scale))
+        sw = int(sliding_window.item()) if isinstance(sliding_window, torch.Tensor) else int(sliding_window or 0)
+        paged_attention(query, cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
+                        self.hq, max_ctx, max_q_len, sc, sw, out=outputs[0], workspace=ws, stream=stream,
+                        status=status)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# KV block manager (host)
+# ------------------------------------------------------------------------------------------------------------
+
+class KvBlockManager:
+    """Python face of the C++ ``b2a::KvBlockManager`` (free list + per-sequence block lists + step tables)."""
+
+    def __init__(self, num_blocks: int, block_size: int = 16, shuffle_seed: int = 0):
+        self._lib = _lib.load()
+        self._h = C.c_void_p()
+        check(self._lib.b2a_kvmgr_create(num_blocks, block_size, shuffle_seed, C.byref(self._h)), "b2a_kvmgr_create")
+        self.num_blocks, self.block_size = num_blocks, block_size
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.b2a_kvmgr_destroy(self._h)
+            self._h = None
+
+    def add_sequence(self, seq_id: int) -> None:
+        check(self._lib.b2a_kvmgr_add_sequence(self._h, seq_id), "b2a_kvmgr_add_sequence")
+
+    def free_sequence(self, seq_id: int) -> None:
+        check(self._lib.b2a_kvmgr_free_sequence(self._h, seq_id), "b2a_kvmgr_free_sequence")
+
+    @property
+    def free_blocks(self) -> int:
+        return self._lib.b2a_kvmgr_free_blocks(self._h)
+
+    def sequence_len(self, seq_id: int) -> int:
+        return self._lib.b2a_kvmgr_sequence_len(self._h, seq_id)
+
+    def schedule_step(self, seq_ids: Sequence[int], q_lens: Sequence[int]):
+        """Reserve blocks for the new tokens and return the step tables as numpy int32 arrays:
+        (past_lens, subsequence_begins, block_indices, block_indices_begins, max_context_len)."""
+        n = len(seq_ids)
+        ids = (C.c_int64 * n)(*seq_ids)
+        ql = (C.c_int32 * n)(*q_lens)
+        cap = sum((max(self.sequence_len(s), 0) + q + self.block_size - 1) // self.block_size
+                  for s, q in zip(seq_ids, q_lens)) + 1
+        past = np.zeros(n, np.int32)
+        sb = np.zeros(n + 1, np.int32)
+        bi = np.zeros(cap, np.int32)
+        bb = np.zeros(n + 1, np.int32)
+        nbi, mctx = C.c_int32(0), C.c_int32(0)
+        p = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+        check(self._lib.b2a_kvmgr_schedule_step(self._h, ids, ql, n, p(past), p(sb), p(bi), cap, p(bb),
+                                                C.byref(nbi), C.byref(mctx)), "b2a_kvmgr_schedule_step")
+        return past, sb, bi[: nbi.value].copy(), bb, mctx.value

@@ -1,0 +1,270 @@
+"""PagedAttentionExtension on the GPU, through the C ABI, against the oracle: the u8 bytes and the indices
+bit for bit, the attention outputs within the half-precision bar."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import paged as opaged
+from oracle import quant as oquant
+from tests.helpers import PagedWorkload, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def b2a():
+    import openvino_contrib_b200 as m
+    assert torch.cuda.is_available()
+    return m
+
+
+def _round(x: np.ndarray, dtype) -> torch.Tensor:
+    return torch.from_numpy(x).to(dtype)
+
+
+# ---------------------------------------------------------------- KV store: bit-exact
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("d", [128, 64, 80])
+def test_kv_store_bit_exact(b2a, dtype, d):
+    hkv, bs = 4, 16
+    ctx = np.array([1, 15, 16, 17, 33, 250])
+    past = np.array([0, 3, 15, 16, 0, 200], dtype=np.int32)
+    qlen = (ctx - past).astype(np.int32)
+    bi, bb, nb = opaged.build_block_tables(ctx, bs, seed=5, spare_blocks=3)
+    sb = np.zeros(len(ctx) + 1, np.int32)
+    sb[1:] = np.cumsum(qlen)
+    g = torch.Generator().manual_seed(1)
+    key = (torch.randn(int(sb[-1]), hkv * d, generator=g) * 1.7).to(dtype)
+    val = (torch.randn(int(sb[-1]), hkv * d, generator=g) + 0.3).to(dtype)
+    val[0] = 0.75                      # constant rows: the scale guard
+    key[1, :d] = 0.0
+    cache = b2a.PagedKvCache.allocate(nb, hkv, d, bs, torch.uint8)
+    t = [torch.from_numpy(a).cuda() for a in (past, sb, bi, bb)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    b2a.paged_kv_store(key.cuda(), val.cuda(), cache, *t, status=status)
+    ref_k = np.full((nb, hkv, bs * (d + 4)), 0xFF, np.uint8)
+    ref_v = ref_k.copy()
+    wk = opaged.kv_store_ref(key, ref_k, past, sb, bi, bb, hkv, d, bs)
+    opaged.kv_store_ref(val, ref_v, past, sb, bi, bb, hkv, d, bs)
+    assert int(status.item()) == 0
+    assert np.array_equal(cache.k.cpu().numpy(), ref_k)   # codes, f16 scales, f16 zero-points, untouched poison
+    assert np.array_equal(cache.v.cpu().numpy(), ref_v)
+    assert len(wk) == int(sb[-1])
+
+
+def test_kv_store_into_f16_cache(b2a):
+    hkv, d, bs = 2, 64, 16
+    ctx = np.array([20, 5])
+    bi, bb, nb = opaged.build_block_tables(ctx, bs, seed=1)
+    past = np.zeros(2, np.int32)
+    sb = np.array([0, 20, 25], np.int32)
+    key = torch.randn(25, hkv * d, generator=torch.Generator().manual_seed(2)).to(torch.float16)
+    cache = b2a.PagedKvCache.allocate(nb, hkv, d, bs, torch.float16, poison=0)
+    t = [torch.from_numpy(a).cuda() for a in (past, sb, bi, bb)]
+    b2a.paged_kv_store(key.cuda(), key.cuda(), cache, *t)
+    kc = cache.k.cpu().view(torch.float16).reshape(nb, hkv, bs, d)
+    for s in range(2):
+        for i in range(int(ctx[s])):
+            blk = int(bi[bb[s] + i // bs])
+            assert torch.equal(kc[blk, :, i % bs], key[sb[s] + i].reshape(hkv, d))
+
+
+# ---------------------------------------------------------------- decode
+
+DECODE_CASES = [
+    # (context lens, Hq, Hkv)
+    ([1, 15, 16, 17, 33, 100, 1000, 4097], 32, 8),   # GQA 4
+    ([5, 64, 129, 2048], 64, 8),                     # GQA 8
+    ([7, 300], 8, 8),                                # no grouping
+    ([31, 32, 513], 32, 2),                          # GQA 16
+    ([40, 9000], 12, 4),                             # GQA 3
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("ctx,hq,hkv", DECODE_CASES)
+def test_decode_parity(b2a, dtype, ctx, hq, hkv):
+    w = PagedWorkload(ctx, [1] * len(ctx), hq, hkv, 128, seed=hq + len(ctx))
+    q = _round(w.query, dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=hq, max_context_len=max(ctx),
+                              max_q_len=1, status=status)
+    assert int(status.item()) == 0
+    assert_close(out, w.reference(q.float().numpy()), dtype)
+
+
+def test_decode_grid_sized_for_longer_contexts(b2a):
+    # a launch sized for max_context_len 8192 serves shorter contexts (graph replay with changing lengths)
+    ctx = [3, 700]
+    w = PagedWorkload(ctx, [1, 1], 32, 8, 128, seed=3)
+    q = _round(w.query, torch.float16)
+    out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=32, max_context_len=8192, max_q_len=1)
+    assert_close(out, w.reference(q.float().numpy()), torch.float16)
+
+
+def test_decode_sliding_window_and_scale(b2a):
+    ctx = [10, 100, 1000]
+    w = PagedWorkload(ctx, [1] * 3, 32, 8, 128, seed=4)
+    q = _round(w.query, torch.float16)
+    for win in (1, 16, 50, 4096):
+        out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=32, max_context_len=1000,
+                                  max_q_len=1, scale=0.05, sliding_window=win)
+        assert_close(out, w.reference(q.float().numpy(), scale=0.05, sliding_window=win), torch.float16, f"win={win}")
+
+
+def test_decode_constant_values_and_table_permutation(b2a):
+    # V rows constant per sequence -> the output is that constant whatever the scores are (up to the u8 step);
+    # re-shuffling the physical placement leaves the result bit-identical.
+    ctx = [4000, 777]
+    consts = [0.5, -1.25]
+    vf = lambda s, n: np.full((n, 8, 128), consts[s], np.float32)
+    w1 = PagedWorkload(ctx, [1, 1], 32, 8, 128, seed=6, table_seed=1, value_fn=vf)
+    w2 = PagedWorkload(ctx, [1, 1], 32, 8, 128, seed=6, table_seed=2, value_fn=vf)
+    assert not np.array_equal(w1.bi, w2.bi)
+    q = _round(w1.query, torch.float16).cuda()
+    o1 = b2a.paged_attention(q, w1.device_cache(), *w1.device_tables(), hq=32, max_context_len=4000, max_q_len=1)
+    o2 = b2a.paged_attention(q, w2.device_cache(), *w2.device_tables(), hq=32, max_context_len=4000, max_q_len=1)
+    assert torch.equal(o1, o2)
+    for s in range(2):
+        np.testing.assert_allclose(o1[s].float().cpu().numpy(), consts[s], atol=2e-3)
+
+
+def test_bad_block_index_is_reported_not_followed(b2a):
+    w = PagedWorkload([100, 50], [1, 1], 32, 8, 128, seed=8)
+    past, sb, bi, bb = w.device_tables()
+    bi = bi.clone()
+    bi[2] = w.nb + 1000  # far outside the pool
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q = _round(w.query, torch.float16).cuda()
+    out = b2a.paged_attention(q, w.device_cache(), past, sb, bi, bb, hq=32, max_context_len=100, max_q_len=1,
+                              status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 2
+    assert torch.isfinite(out.float()).all()
+    # the untouched sequence is still right
+    ref = w.reference(q.float().cpu().numpy())
+    assert_close(out[1], ref[1], torch.float16)
+
+
+def test_decode_graph_replay_with_new_lengths(b2a):
+    ctx = [900, 1500, 64]
+    w = PagedWorkload(ctx, [1] * 3, 32, 8, 128, seed=9)
+    cache = w.device_cache()
+    past, sb, bi, bb = w.device_tables()
+    q = _round(w.query, torch.float16).cuda()
+    out = torch.empty_like(q)
+    ws = torch.empty(b2a.ops.paged_workspace_bytes(torch.float16, cache, 32, 3, 3, 2048, 1), dtype=torch.uint8,
+                     device="cuda")
+    run = lambda stream=None: b2a.paged_attention(q, cache, past, sb, bi, bb, hq=32, max_context_len=2048,
+                                                  max_q_len=1, out=out, workspace=ws, stream=stream)
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            run(s)
+    # same pool, shorter histories: only past_lens changes on the device
+    new_past = np.array([500, 1499, 10], np.int32)
+    past.copy_(torch.from_numpy(new_past))
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    ref = opaged.paged_attention_ref(q.float().cpu().numpy(), w.k_cache, w.v_cache, new_past, w.sb, w.bi, w.bb,
+                                     32, 8, 128, 16)
+    assert_close(out, ref, torch.float16)
+
+
+# ---------------------------------------------------------------- multi-token rows (general kernel)
+
+def test_reference_golden_paged_vectors(b2a, golden_dir):
+    g = np.load(os.path.join(golden_dir, "paged_reference.npz"))
+    hq, hkv, d, bs = (int(x) for x in g["geom"])
+    cache = b2a.PagedKvCache(torch.from_numpy(g["k_cache"]).cuda(), torch.from_numpy(g["v_cache"]).cuda(),
+                             hkv, d, d, bs, torch.uint8)
+    t = [torch.from_numpy(g[n]).cuda() for n in ("past_lens", "subsequence_begins", "block_indices",
+                                                 "block_indices_begins")]
+    qlen = np.diff(g["subsequence_begins"])
+    ctx = int((g["past_lens"] + qlen).max())
+    out = b2a.paged_attention(torch.from_numpy(g["query"]).cuda(), cache, *t, hq=hq, max_context_len=ctx,
+                              max_q_len=int(qlen.max()))
+    assert_close(out, g["out"], torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_mixed_step_through_the_operator(b2a, dtype):
+    # two prefill sequences, one chunked-prefill continuation, three decode sequences, one idle sequence
+    hq, hkv, d, bs = 16, 4, 128, 16
+    past = np.array([0, 0, 40, 99, 16, 511, 30], np.int32)
+    qlen = np.array([70, 33, 25, 1, 1, 1, 0], np.int32)
+    ctx = past + qlen
+    w = PagedWorkload(ctx, qlen, hq, hkv, d, seed=12)
+    # pools holding only the past; this step's rows go in through the operator
+    rng = np.random.default_rng(5)
+    new_k = rng.standard_normal((int(w.sb[-1]), hkv * d), dtype=np.float32)
+    new_v = rng.standard_normal((int(w.sb[-1]), hkv * d), dtype=np.float32)
+    nk, nv = _round(new_k, dtype), _round(new_v, dtype)
+    ref_k, ref_v = w.k_cache.copy(), w.v_cache.copy()
+    opaged.kv_store_ref(nk, ref_k, w.past, w.sb, w.bi, w.bb, hkv, d, bs)
+    opaged.kv_store_ref(nv, ref_v, w.past, w.sb, w.bi, w.bb, hkv, d, bs)
+    q = _round(w.query, dtype)
+    ref = opaged.paged_attention_ref(q.float().numpy(), ref_k, ref_v, w.past, w.sb, w.bi, w.bb, hq, hkv, d, bs)
+
+    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=8, max_context_len=1024)
+    cache = w.device_cache()
+    out = torch.empty(int(w.sb[-1]), hq * d, dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    op.Execute([q.cuda(), nk.cuda(), nv.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, int(ctx.max())],
+               [out], status=status)
+    assert int(status.item()) == 0
+    assert np.array_equal(cache.k.cpu().numpy(), ref_k) and np.array_equal(cache.v.cpu().numpy(), ref_v)
+    assert_close(out, ref, dtype)
+
+
+# ---------------------------------------------------------------- benchmark-sized cases
+
+def test_config3_shape_against_oracle(b2a):
+    # 64 sequences, contexts uniform in [512, 8192] from seed 2, block table from seed 3, Hq 32 / Hkv 8 / D 128
+    rng = np.random.default_rng(2)
+    ctx = rng.integers(512, 8193, size=64)
+    w = PagedWorkload(ctx, [1] * 64, 32, 8, 128, seed=2, table_seed=3)
+    q = _round(w.query, torch.float16)
+    out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=32, max_context_len=8192, max_q_len=1)
+    assert_close(out, w.reference(q.float().numpy()), torch.float16)
+
+
+def test_config5_shape_properties(b2a):
+    # batch 16 x context 32768, Hq 64 / Hkv 8: too large for the numpy oracle in seconds, so check properties:
+    # (1) constant V per (sequence, head) is reproduced; (2) a window equal to the context changes nothing;
+    # (3) sequence 0 alone (oracle-checked) equals row 0 of the batch.
+    hq, hkv, d, bs, n, ctxlen = 64, 8, 128, 16, 16, 32768
+    nblk = ctxlen // bs
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    cache = b2a.PagedKvCache.allocate(n * nblk + 1, hkv, d, bs, torch.uint8, poison=0xFF)
+    perm = torch.randperm(n * nblk + 1, generator=torch.Generator().manual_seed(6))[: n * nblk].to(torch.int32)
+    bi = perm.cuda()
+    bb = (torch.arange(n + 1, dtype=torch.int32) * nblk).cuda()
+    sb = torch.arange(n + 1, dtype=torch.int32).cuda()
+    # fill through the library's own store path in slices (exercises kv_store at scale)
+    step = 4096
+    for p0 in range(0, ctxlen, step):
+        key = torch.randn(n * step, hkv * d, generator=gen, device="cuda", dtype=torch.float16)
+        hv = torch.arange(hkv, device="cuda", dtype=torch.float16).repeat_interleave(d)[None] * 0.125
+        sv = torch.arange(n, device="cuda", dtype=torch.float16).repeat_interleave(step)[:, None] * 0.0625
+        val = (hv + sv - 0.5).contiguous()
+        past = torch.full((n,), p0, dtype=torch.int32, device="cuda")
+        sbs = (torch.arange(n + 1, dtype=torch.int32) * step).cuda()
+        b2a.paged_kv_store(key, val, cache, past, sbs, bi, bb)
+    past = torch.full((n,), ctxlen - 1, dtype=torch.int32, device="cuda")
+    q = torch.randn(n, hq * d, generator=gen, device="cuda", dtype=torch.float16)
+    out = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1)
+    o = out.float().reshape(n, hkv, hq // hkv, d)
+    expect = (torch.arange(hkv, device="cuda").float()[None, :, None, None] * 0.125
+              + torch.arange(n, device="cuda").float()[:, None, None, None] * 0.0625 - 0.5)
+    assert torch.allclose(o, expect.expand_as(o), atol=2e-3)
+    out_w = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1,
+                                sliding_window=ctxlen)
+    assert torch.equal(out, out_w)

@@ -1,0 +1,150 @@
+"""ScaledDotProductAttention on the GPU, through the C ABI, against the oracle and the reference's vectors."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sdpa as osdpa
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def b2a():
+    import openvino_contrib_b200 as m
+    assert torch.cuda.is_available()
+    return m
+
+
+def _rand(shape, seed, dtype, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def test_reference_golden_vectors(b2a, golden_dir):
+    g = np.load(os.path.join(golden_dir, "sdpa_reference.npz"))
+    for n in sorted({k.split("/")[0] for k in g.files}):
+        q, k, v = (torch.from_numpy(g[f"{n}/{x}"]).cuda() for x in "qkv")
+        mask = torch.from_numpy(g[f"{n}/mask"]).cuda() if f"{n}/mask" in g.files else None
+        scale = float(g[f"{n}/scale"]) or None
+        o = b2a.sdpa(q, k, v, mask, scale, bool(g[f"{n}/causal"]))
+        assert_close(o, g[f"{n}/o"], torch.float32, n)
+
+
+# the shapes of the reference's functional test (scaled_dot_product_attention.cpp:76-104)
+REF_SHAPES = [(1, 1, 4, 8), (1, 4, 16, 32), (1, 8, 32, 64), (4, 2, 8)]
+
+
+@pytest.mark.parametrize("shape", REF_SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_reference_test_grid(b2a, shape, causal, dtype):
+    q, k, v = (_rand(shape, 10 + i, dtype) for i in range(3))
+    o = b2a.SdpaOp(causal=causal)
+    out = torch.empty(shape, dtype=dtype, device="cuda")
+    o.Execute([q.cuda(), k.cuda(), v.cuda()], [out])
+    assert_close(out, osdpa.sdpa_ref(q, k, v, causal=causal), dtype)
+
+
+def test_config1_f32_causal(b2a):
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, 8, 256, 64, generator=g) for _ in range(3))
+    o = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), scale=0.125, causal=True)
+    assert_close(o, osdpa.sdpa_ref(q, k, v, scale=0.125, causal=True), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [
+    # (B, Hq, Hkv, Sq, Skv, D)
+    (1, 8, 2, 512, 512, 128),     # Llama-shaped GQA, several key tiles
+    (2, 4, 4, 128, 128, 128),     # one tile, no GQA
+    (1, 8, 2, 384, 384, 128),     # ragged against 256-row query tiles
+    (1, 4, 1, 200, 333, 128),     # nothing a multiple of the tile sizes, Sq != Skv
+    (1, 2, 2, 1, 129, 128),       # a single query row
+    (1, 4, 2, 77, 77, 64),        # head size 64
+])
+def test_half_precision_shapes(b2a, dtype, causal, shape):
+    B, Hq, Hkv, Sq, Skv, D = shape
+    q = _rand((B, Hq, Sq, D), 1, dtype, 0.5)
+    k = _rand((B, Hkv, Skv, D), 2, dtype, 0.5)
+    v = _rand((B, Hkv, Skv, D), 3, dtype, 0.5)
+    o = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+    assert_close(o, osdpa.sdpa_ref(q, k, v, causal=causal), dtype, str(shape))
+
+
+def test_strided_views_and_out_argument(b2a):
+    # [B, S, H, D] storage viewed as [B, H, S, D]: the layout LLM runtimes hand over
+    B, S, Hq, Hkv, D = 2, 160, 8, 2, 128
+    dtype = torch.bfloat16
+    qs = _rand((B, S, Hq, D), 4, dtype, 0.5).cuda()
+    ks = _rand((B, S, Hkv, D), 5, dtype, 0.5).cuda()
+    vs = _rand((B, S, Hkv, D), 6, dtype, 0.5).cuda()
+    q, k, v = qs.transpose(1, 2), ks.transpose(1, 2), vs.transpose(1, 2)
+    out_store = torch.zeros(B, S, Hq, D, dtype=dtype, device="cuda")
+    b2a.sdpa(q, k, v, causal=True, out=out_store.transpose(1, 2))
+    ref = osdpa.sdpa_ref(q.cpu(), k.cpu(), v.cpu(), causal=True)
+    assert_close(out_store.transpose(1, 2), ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_masks_broadcast_and_uneven_head_sizes(b2a, dtype):
+    B, H, Sq, Skv, D, Dv = 2, 3, 19, 45, 80, 48
+    q = _rand((B, H, Sq, D), 7, dtype)
+    k = _rand((B, H, Skv, D), 8, dtype)
+    v = _rand((B, H, Skv, Dv), 9, dtype)
+    g = torch.Generator().manual_seed(11)
+    bmask = torch.rand(B, 1, Sq, Skv, generator=g) > 0.4
+    bmask[..., 0] = True
+    o = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), bmask.cuda())
+    assert_close(o, osdpa.sdpa_ref(q, k, v, mask=bmask.numpy()), dtype)
+    amask = torch.randn(1, H, 1, Skv, generator=g).to(dtype)
+    o = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), amask.cuda(), scale=0.2)
+    assert_close(o, osdpa.sdpa_ref(q, k, v, mask=amask.float().numpy(), scale=0.2), dtype)
+    # a fully masked row yields zeros, not NaN
+    bmask[0, 0, 3, :] = False
+    o = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), bmask.cuda())
+    assert torch.isfinite(o.float()).all() and float(o[0, :, 3].abs().max()) == 0.0
+
+
+def test_causal_ignores_mask_and_is_deterministic(b2a):
+    q, k, v = (_rand((1, 4, 64, 64), 20 + i, torch.float16).cuda() for i in range(3))
+    m = torch.zeros(64, 64, dtype=torch.bool, device="cuda")
+    a = b2a.sdpa(q, k, v, m, causal=True)
+    b = b2a.sdpa(q, k, v, None, causal=True)
+    assert torch.equal(a, b)
+
+
+def test_bad_arguments_raise(b2a):
+    from openvino_contrib_b200._lib import B2AError
+    q = torch.zeros(1, 6, 8, 64, device="cuda")
+    k = torch.zeros(1, 4, 8, 64, device="cuda")
+    with pytest.raises(B2AError) as e:
+        b2a.sdpa(q, k, k)
+    assert e.value.code == 2
+    with pytest.raises(TypeError):
+        b2a.sdpa(q.double(), q.double(), q.double())
+    big = torch.zeros(1, 1, 4, 512, device="cuda")
+    with pytest.raises(B2AError) as e:
+        b2a.sdpa(big, big, big)
+    assert e.value.code == 7
+
+
+def test_graph_capture_and_replay(b2a):
+    q, k, v = (_rand((1, 8, 96, 128), 30 + i, torch.bfloat16, 0.5).cuda() for i in range(3))
+    out = torch.empty_like(q)
+    b2a.sdpa(q, k, v, causal=True, out=out)  # warm-up outside capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            b2a.sdpa(q, k, v, causal=True, out=out, stream=s)
+    q2 = _rand((1, 8, 96, 128), 99, torch.bfloat16, 0.5).cuda()
+    q.copy_(q2)
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert_close(out, osdpa.sdpa_ref(q2.cpu(), k.cpu(), v.cpu(), causal=True), torch.bfloat16)
