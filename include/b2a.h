@@ -43,7 +43,8 @@ typedef enum b2a_status {
     B2A_ERR_CUDA = 6,        /* a CUDA runtime call failed (no device, launch error) */
     B2A_ERR_UNSUPPORTED = 7, /* valid request this build has no kernel for */
     B2A_ERR_CAPACITY = 8,    /* block manager: pool exhausted / output array too small */
-    B2A_ERR_NOT_FOUND = 9    /* block manager: unknown sequence id */
+    B2A_ERR_NOT_FOUND = 9,   /* block manager: unknown sequence id */
+    B2A_ERR_SCRATCH_LIMIT = 10 /* b2a_paged_attention_noalloc: the step needs more than the built-in scratch */
 } b2a_status;
 
 /* bits OR-ed into the device status word */
@@ -137,6 +138,31 @@ int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const voi
                         const int32_t* past_lens, const int32_t* subsequence_begins, const int32_t* block_indices,
                         const int32_t* block_indices_begins, void* out, void* workspace, size_t workspace_bytes,
                         int32_t* status, b2a_stream_t stream);
+
+/* Decode attention for callers that cannot provide a workspace and must not allocate one.
+ * No counterpart in the reference: there every operation declares its scratch through GetWorkBufferRequest and
+ * the plugin's memory manager lays it out when the model is compiled.  Code that reaches this library some other
+ * way has no such channel and often no way to call cudaMalloc at the point of the call either: an operator body
+ * running under stream capture (an allocation there ends the capture with an error), a custom-operation
+ * extension that only ever sees its input and output buffers, a serving loop that has handed the whole device
+ * memory to its KV pool up front.  For them the split-K partials live in an array that is part of the library
+ * image: B2A_BUILTIN_SCRATCH_BYTES on every GPU that loads libb2a.so, held until the process exits.
+ *
+ * Same arguments and results as b2a_paged_attention, minus the workspace, with these limits:
+ *   - decode steps only: one query token per sequence, u8 cache, D = Dv = 128, block size 16, f16 or bf16
+ *     queries (otherwise B2A_ERR_UNSUPPORTED);
+ *   - the step's split-K partials (b2a_paged_workspace_bytes of the same descriptor) must fit the built-in
+ *     array, otherwise B2A_ERR_SCRATCH_LIMIT and nothing is launched;
+ *   - the first call on each device looks up the array's device address (no allocation, but a runtime query):
+ *     make that first call before any stream capture begins;
+ *   - all calls on one device share the one array, and it keeps whatever the previous call left in it (no part
+ *     of it needs clearing between calls): calls that may run concurrently on the GPU race on it, so keep them
+ *     on one stream or order them with events. */
+#define B2A_BUILTIN_SCRATCH_BYTES (16u << 20)
+int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, const void* k_cache,
+                                const void* v_cache, const int32_t* past_lens, const int32_t* subsequence_begins,
+                                const int32_t* block_indices, const int32_t* block_indices_begins, void* out,
+                                int32_t* status, b2a_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * KV block manager (host only; no CUDA calls).  Owns the free list of a pool of `num_blocks` physical

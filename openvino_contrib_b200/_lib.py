@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(_PKG, "libb2a.so")
 F32, F16, BF16, U8 = 0, 1, 2, 3
 MASK_NONE, MASK_BOOL, MASK_ADD = 0, 1, 2
 DEV_TIMEOUT, DEV_BAD_BLOCK, DEV_BAD_LEN = 1, 2, 4
+BUILTIN_SCRATCH_BYTES = 16 << 20
 
 
 class SdpaDesc(C.Structure):
@@ -45,6 +46,8 @@ SIGNATURES = {
     "b2a_paged_attention": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                       C.c_void_p, C.c_void_p]),
+    "b2a_paged_attention_noalloc": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b2a_kvmgr_create": (C.c_int, [C.c_int32, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p)]),
     "b2a_kvmgr_destroy": (None, [C.c_void_p]),
     "b2a_kvmgr_add_sequence": (C.c_int, [C.c_void_p, C.c_int64]),

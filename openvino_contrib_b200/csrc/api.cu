@@ -111,6 +111,7 @@ const char* b2a_status_string(int status) {
         case B2A_ERR_UNSUPPORTED: return "no kernel for this configuration";
         case B2A_ERR_CAPACITY: return "capacity exceeded";
         case B2A_ERR_NOT_FOUND: return "unknown sequence";
+        case B2A_ERR_SCRATCH_LIMIT: return "the step needs more split-K scratch than the library's built-in 16 MiB";
         default: return "unknown status";
     }
 }
@@ -201,6 +202,28 @@ int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const voi
         return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, workspace, status, s);
     }
     return paged_generic_launch(d, query, k_cache, v_cache, t, out, status, s);
+}
+
+int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, const void* k_cache,
+                                const void* v_cache, const int32_t* past_lens, const int32_t* subsequence_begins,
+                                const int32_t* block_indices, const int32_t* block_indices_begins, void* out,
+                                int32_t* status, b2a_stream_t stream) {
+    b2a_paged_desc d;
+    const int rc = resolve_paged(desc, d);
+    if (rc != B2A_OK) return rc;
+    if (d.num_tokens == 0 || d.num_seqs == 0) return B2A_OK;
+    if (query == nullptr || k_cache == nullptr || v_cache == nullptr || out == nullptr || past_lens == nullptr ||
+        subsequence_begins == nullptr || block_indices == nullptr || block_indices_begins == nullptr)
+        return B2A_ERR_NULL;
+    if (d.max_q_len <= 0 || d.max_context_len <= 0) return B2A_ERR_DIM;
+    if (!paged_decode_supported(d)) return B2A_ERR_UNSUPPORTED;
+    if (!aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(query, 16) || !aligned(out, 16)) return B2A_ERR_ALIGN;
+    const int sms = device_sm_count();
+    if (sms <= 0) return B2A_ERR_CUDA;
+    return paged_decode_launch_builtin_scratch(
+        d, paged_decode_plan(d, sms), query, k_cache, v_cache,
+        tables_of(d, past_lens, subsequence_begins, block_indices, block_indices_begins), out, status,
+        reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

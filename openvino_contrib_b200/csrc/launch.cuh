@@ -30,6 +30,11 @@ int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const v
                         const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
                         cudaStream_t stream);
 
+// Same launch with the split-K partials in the library's built-in device array instead of a caller workspace.
+int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query,
+                                        const void* k_cache, const void* v_cache, const PagedTables& t, void* out,
+                                        int32_t* status, cudaStream_t stream);
+
 // sdpa_tcgen05.cu — TMA + tcgen05 flash prefill (f16 / bf16, D = Dv = 128)
 bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4],
                        const int64_t (&vs)[4], const int64_t (&os)[4], const void* q, const void* k, const void* v,

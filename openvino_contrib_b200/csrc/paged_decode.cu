@@ -485,4 +485,31 @@ int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const v
     return two ? launch_t<__nv_bfloat16, 2>(p, d.num_seqs, stream) : launch_t<__nv_bfloat16, 1>(p, d.num_seqs, stream);
 }
 
+// ---- decode with built-in scratch ---------------------------------------------------------------------------
+//
+// Split-K partials for callers that have nowhere to get a workspace from: the array below is part of the
+// library image, so every GPU that loads libb2a.so carries these 16 MiB until the process exits, and nothing is
+// allocated at call time.  One array per device, shared by every call on that device: two calls that overlap on
+// the GPU (different streams, or graph branches) would write each other's partials, so such calls must be ordered.
+// Nothing in it has to start at zero: every partial the merge kernel reads is written by the decode kernel of the
+// same call, which is why no clearing is issued.
+static __device__ __align__(256) unsigned char g_decode_scratch[B2A_BUILTIN_SCRATCH_BYTES];
+
+int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query,
+                                        const void* k_cache, const void* v_cache, const PagedTables& t, void* out,
+                                        int32_t* status, cudaStream_t stream) {
+    if (plan.workspace_bytes > static_cast<size_t>(B2A_BUILTIN_SCRATCH_BYTES)) return B2A_ERR_SCRATCH_LIMIT;
+    // `g_decode_scratch` as written in host code is only a handle for the runtime; the address the kernels can
+    // use is looked up once per device, with that device current, and remembered.
+    static void* device_address[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
+    void* scratch = (dev >= 0 && dev < 64) ? device_address[dev] : nullptr;
+    if (scratch == nullptr) {
+        if (cudaGetSymbolAddress(&scratch, g_decode_scratch) != cudaSuccess || scratch == nullptr) return B2A_ERR_CUDA;
+        if (dev >= 0 && dev < 64) device_address[dev] = scratch;
+    }
+    return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, scratch, status, stream);
+}
+
 }  // namespace b2a
