@@ -323,10 +323,16 @@ def run_b2a(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     import openvino_contrib_b200  # noqa: F401  (fails loudly if libb2a.so is missing)
 
+    if args.only in ("cfg3", "cfg5"):  # a single decode workload, for profiler captures
+        r = bench_decode(args.only, args.steps, args.warmup, rank, world)
+        if rank == 0:
+            print(json.dumps(r))
+        return
     pre = bench_prefill(args, rank, world, local)
     decode = {}
-    for name in ("cfg3", "cfg5"):
-        decode[name] = bench_decode(name, max(args.steps, 20), max(args.warmup, 3), rank, world)
+    if args.only is None:
+        for name in ("cfg3", "cfg5"):
+            decode[name] = bench_decode(name, max(args.steps, 20), max(args.warmup, 3), rank, world)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         _, _, cpu = cpu_prefill_sample(3, 1, budget_s=20.0)
@@ -359,8 +365,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b2a", choices=["b2a", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", default=None, choices=["prefill", "cfg3", "cfg5"],
+                    help="run one workload only (profiler captures); the default runs all and prints the full line")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b2a" else args.warmup
+    if args.impl == "b2a" and args.only is None:
+        args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
     else:
