@@ -1,10 +1,442 @@
-// placeholder until the tcgen05 kernel lands
+// Fused attention for prefill on the 5th-generation tensor core: S = Q K^T and O = P V as tcgen05.mma with
+// accumulators in tensor memory, Q/K/V tiles staged by TMA, online softmax in registers.  f16 / bf16, D = Dv = 128,
+// causal or unmasked, grouped-query heads.
+//
+// One CTA (10 warps) owns TWO 128-row query tiles of one KV head and walks the keys 128 at a time:
+//   warps 0-3   softmax of tile A: thread = query row = TMEM lane.  Reads S_A (tcgen05.ld), keeps the running max
+//               and sum, writes P_A = exp2(S*c - m) as 16-bit pairs over the first half of S_A's columns
+//               (tcgen05.st), rescales O_A in TMEM when the maximum moved, finally normalises O_A and stores it
+//               through shared memory with TMA stores (one [64 x 32] box per warp and panel).
+//   warps 4-7   the same for tile B.
+//   warp  8     TMA producer (one lane): Q tiles once, then K_j and V_j into two-stage rings.
+//   warp  9     MMA issuer (one lane): S_X(j) = Q_X K_j^T (A and B from shared memory, K-major, 128-byte swizzle),
+//               O_X += P_X(j) V_j (A from TMEM, B from shared memory, MN-major).  Order per step:
+//               PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1) - while one tile's softmax runs, the tensor core works on
+//               the other tile.  The warp also owns the TMEM allocation (all 512 columns: S_A S_B O_A O_B).
+// The two tiles are consecutive entries of the list (row block, query head of the group), query heads fastest, so
+// with an even group size both tiles cover the same rows of two heads that share K/V, and the causal structure of
+// the pair is identical.  Heavy (late) row blocks are scheduled first.
+//
+// The maximum used for P is allowed to lag: O and the sum are rescaled only when some row's maximum grew by more
+// than 2^8, so P stays below 256 and the result is exact after the final division.
+//
+// Every mbarrier wait is bounded (tcgen05.cuh); on a timeout the CTA raises an abort flag, all roles leave their
+// loops, outstanding copies and MMAs are drained with bounded waits, TMEM is freed and the status word gets
+// B2A_DEV_TIMEOUT.
 #include "launch.cuh"
+#include "tcgen05.cuh"
+
 namespace b2a {
-bool sdpa_tc_supported(const b2a_sdpa_desc&, const int64_t (&)[4], const int64_t (&)[4], const int64_t (&)[4],
-                       const int64_t (&)[4], const void*, const void*, const void*, const void*) { return false; }
-int sdpa_tc_launch(const b2a_sdpa_desc&, const int64_t (&)[4], const int64_t (&)[4], const int64_t (&)[4],
-                   const int64_t (&)[4], const void*, const void*, const void*, void*, int32_t*, cudaStream_t) {
-    return B2A_ERR_UNSUPPORTED;
+namespace {
+
+using namespace tc;
+
+constexpr int kBM = 128;             // query rows per tile = TMEM lanes
+constexpr int kBN = 128;             // keys per step
+constexpr int kHeadDim = 128;
+constexpr int kPanel = 128 * 128;    // bytes of one [128 rows x 64 elements] swizzled panel
+constexpr int kTile = 2 * kPanel;    // a [128 x 128] 16-bit tile
+constexpr int kThreads = 320;
+constexpr int kNumBars = 17;
+constexpr int kSmemBytes = 6 * kTile + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot, abort flag */;
+constexpr float kLazyThreshold = 8.0f;  // log2 units
+
+enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16 };
+
+struct TcParams {
+    int B, Hq, Hkv, G, Sq, Skv;
+    int causal;
+    float scale_log2;
+    int32_t* status;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (kBf16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    } else {
+        const __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+// time-bounded wait that ignores the abort flag: used only to drain work already in flight
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kWaitTicks) return;
+    }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte swizzle atoms want 1024-byte aligned tiles
+    uint8_t* gbase = smem_raw + (base - raw);
+    const uint32_t sQ = base, sK = base + 2 * kTile, sV = base + 4 * kTile;
+    const uint32_t bars = base + 6 * kTile;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 6 * kTile + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 6 * kTile + kNumBars * 8 + 8);
+    auto BAR = [&](int i) { return bars + 8u * static_cast<uint32_t>(i); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- which two tiles
+    const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
+    const int nrb = (p.Sq + kBM - 1) / kBM;
+    const int tiles = nrb * p.G;
+    const int pairs = (tiles + 1) / 2;
+    const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // late row blocks (most keys) first
+    int row0[2], head[2], nkv[2];
+#pragma unroll
+    for (int X = 0; X < 2; ++X) {
+        const int t = 2 * pair + X;
+        const bool present = t < tiles;
+        const int rb = present ? t / p.G : 0, g = present ? t % p.G : 0;
+        row0[X] = rb * kBM;
+        head[X] = hk * p.G + g;
+        const int kv_end = p.causal ? min(p.Skv, row0[X] + kBM) : p.Skv;
+        nkv[X] = present ? (kv_end + kBN - 1) / kBN : 0;
+    }
+    const int nmax = max(nkv[0], nkv[1]);
+
+    // ---- set-up: barriers, TMEM
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kNumBars; ++i) mbar_init(BAR(i), (i == P_READY || i == P_READY + 1) ? 128u : 1u);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 8) {
+        // =============================== TMA producer ===============================
+        if (lane == 0) {
+            prefetch_tensormap(&tmQ);
+            prefetch_tensormap(&tmK);
+            prefetch_tensormap(&tmV);
+#pragma unroll
+            for (int X = 0; X < 2; ++X) {
+                if (nkv[X] > 0) {
+                    mbar_expect_tx(BAR(Q_FULL + X), kTile);
+                    tma_load_4d(sQ + X * kTile, &tmQ, BAR(Q_FULL + X), 0, row0[X], head[X], b);
+                    tma_load_4d(sQ + X * kTile + kPanel, &tmQ, BAR(Q_FULL + X), 64, row0[X], head[X], b);
+                }
+            }
+            int issued_k = 0, issued_v = 0;
+            for (int j = 0; j < nmax; ++j) {
+                const int st = j & 1, n = j >> 1;
+                if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(BAR(K_FULL + st), kTile);
+                tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, j * kBN, hk, b);
+                tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, j * kBN, hk, b);
+                ++issued_k;
+                if (n > 0 && !mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(BAR(V_FULL + st), kTile);
+                tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, j * kBN, hk, b);
+                tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, j * kBN, hk, b);
+                ++issued_v;
+            }
+            if (*abort_flag) {  // let copies already in flight land before the CTA goes away
+                for (int X = 0; X < 2; ++X)
+                    if (nkv[X] > 0) mbar_drain(BAR(Q_FULL + X), 0);
+                for (int jj = max(0, issued_k - 2); jj < issued_k; ++jj) mbar_drain(BAR(K_FULL + (jj & 1)), (jj >> 1) & 1);
+                for (int jj = max(0, issued_v - 2); jj < issued_v; ++jj) mbar_drain(BAR(V_FULL + (jj & 1)), (jj >> 1) & 1);
+            }
+        }
+    } else if (warp == 9) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc_f16(kBf16, false, kBM, kBN);
+            constexpr uint32_t idesc_pv = instr_desc_f16(kBf16, true, kBM, kHeadDim);
+            auto issue_qk = [&](int X, int st) {  // S_X = Q_X K^T : 8 steps of 16 along D
+                const uint32_t d = tmem + static_cast<uint32_t>(X * 128);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = static_cast<uint32_t>((ks >> 2) * kPanel + (ks & 3) * 32);
+                    mma_ss(d, smem_desc_sw128(sQ + X * kTile + off, 16, 1024),
+                           smem_desc_sw128(sK + st * kTile + off, 16, 1024), idesc_qk, ks > 0);
+                }
+            };
+            auto issue_pv = [&](int X, int st, bool acc) {  // O_X += P_X V : 8 steps of 16 along the keys
+                const uint32_t d = tmem + static_cast<uint32_t>(256 + X * 128);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    mma_ts(d, tmem + static_cast<uint32_t>(X * 128 + ks * 8),
+                           smem_desc_sw128(sV + st * kTile + ks * 2048, kPanel, 1024), idesc_pv, acc || ks > 0);
+                }
+            };
+            bool ok = true;
+#pragma unroll
+            for (int X = 0; X < 2; ++X)
+                if (nkv[X] > 0) ok = ok && mbar_wait(BAR(Q_FULL + X), 0, abort_flag);
+            ok = ok && mbar_wait(BAR(K_FULL + 0), 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int X = 0; X < 2; ++X) {
+                    if (nkv[X] > 0) {
+                        issue_qk(X, 0);
+                        mma_commit(BAR(S_FULL + X));
+                    }
+                }
+                mma_commit(BAR(K_EMPTY + 0));
+            }
+            for (int j = 0; ok && j < nmax; ++j) {
+                const int stv = j & 1;
+                if (!mbar_wait(BAR(V_FULL + stv), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+                bool k_next_ready = false;
+#pragma unroll
+                for (int X = 0; X < 2; ++X) {
+                    if (ok && j < nkv[X]) {
+                        if (!mbar_wait(BAR(P_READY + X), j & 1, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_pv(X, stv, j > 0);
+                        mma_commit(BAR(O_DONE + X));
+                    }
+                    if (ok && j + 1 < nkv[X]) {
+                        if (!k_next_ready) {
+                            if (!mbar_wait(BAR(K_FULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                            k_next_ready = true;
+                            tc_fence_after();
+                        }
+                        issue_qk(X, (j + 1) & 1);
+                        mma_commit(BAR(S_FULL + X));
+                    }
+                }
+                if (!ok) break;
+                mma_commit(BAR(V_EMPTY + stv));
+                if (j + 1 < nmax) mma_commit(BAR(K_EMPTY + ((j + 1) & 1)));
+            }
+            mma_commit(BAR(DRAIN));  // everything issued has completed before TMEM and shared memory are given up
+            mbar_drain(BAR(DRAIN), 0);
+        }
+    } else {
+        // =============================== softmax + epilogue of tile X ===============================
+        const int X = warp >> 2;
+        const int r = static_cast<int>(threadIdx.x) - X * 128;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem + lane_base + static_cast<uint32_t>(X * 128);
+        const uint32_t tO = tmem + lane_base + static_cast<uint32_t>(256 + X * 128);
+        if (nkv[X] > 0) {
+            const int row = row0[X] + r;
+            const float c = p.scale_log2;
+            float m_used = -1.0e30f, l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nkv[X]; ++j) {
+                // every lane takes the same decision, so the warp-collective TMEM instructions stay converged
+                ok = __all_sync(0xffffffffu, mbar_wait(BAR(S_FULL + X), j & 1, abort_flag));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t s[4][32];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tmem_ld32(tS + 32 * q, s[q]);
+                tmem_wait_ld();
+                const int key0 = j * kBN;
+                const bool boundary = (key0 + kBN - 1 >= p.Skv) || (p.causal && key0 + kBN - 1 > row0[X]);
+                if (boundary) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int key = key0 + q * 32 + i;
+                            const bool keep = key < p.Skv && (!p.causal || key <= row);
+                            if (!keep) s[q][i] = 0xff800000u;  // -inf
+                        }
+                }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[q][i]));
+                const float m_cand = mx * c;
+                const bool need = (j == 0) || (m_cand > m_used + kLazyThreshold);
+                const bool need_any = __any_sync(0xffffffffu, need);
+                float alpha = 1.f;
+                if (need_any) {
+                    const float m_new = fmaxf(m_used, m_cand);
+                    alpha = ex2f(m_used - m_new);
+                    m_used = m_new;
+                    l *= alpha;
+                }
+                float sum = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float p0 = ex2f(fmaf(__uint_as_float(s[q][2 * i]), c, -m_used));
+                        const float p1 = ex2f(fmaf(__uint_as_float(s[q][2 * i + 1]), c, -m_used));
+                        sum += p0 + p1;
+                        pk[i] = pack2<kBf16>(p0, p1);
+                    }
+                    tmem_st16(tS + 16 * q, pk);  // P over the first 64 columns of S, behind what was already read
+                }
+                l += sum;
+                if (need_any && j > 0) {
+                    // O_X still holds the old scale; PV_X(j-1) must have landed before it is touched
+                    ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (j - 1) & 1, abort_flag));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + 32 * q, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tO + 32 * q, o);
+                    }
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(BAR(P_READY + X));
+            }
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (nkv[X] - 1) & 1, abort_flag));
+            if (ok) {
+                tc_fence_after();
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                uint8_t* stage = gbase + X * kTile;  // Q_X is no longer needed: its tile is the staging buffer
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + 32 * q, o);
+                    tmem_wait_ld();
+                    uint8_t* prow = stage + (q >> 1) * kPanel + r * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 v;
+                        v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
+                        v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
+                        v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
+                        v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
+                        const int chunk = (q & 1) * 4 + ch;  // 16-byte chunk of the 128-byte row, swizzled like TMA's
+                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = v;
+                    }
+                }
+                // each warp stores its own 32 rows (a [64 x 32] box per panel): no cross-warp barrier is needed
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const int w = warp & 3;
+                    tma_store_4d(&tmO, sQ + X * kTile + w * 32 * 128, 0, row0[X] + 32 * w, head[X], b);
+                    tma_store_4d(&tmO, sQ + X * kTile + kPanel + w * 32 * 128, 64, row0[X] + 32 * w, head[X], b);
+                    tma_store_commit();
+                    tma_store_wait_all();
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag) report(p.status, B2A_DEV_TIMEOUT);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+// [B, H, S, 128] view with element strides st[0..3] (st[3] == 1) as a 4-D map, box = [64 x box_rows x 1 x 1],
+// 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* ptr, bool bf16, int B, int H, int S, const int64_t (&st)[4], int box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(S),
+                                static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+    // a stride of an extent-1 dimension is never used for addressing but is still validated: give it a legal value
+    auto bytes = [](int64_t elems, int extent) { return static_cast<cuuint64_t>(extent == 1 || elems <= 0 ? 256 : elems * 2); };
+    const cuuint64_t strides[3] = {bytes(st[2], S), bytes(st[1], H), bytes(st[0], B)};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+               const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool strides_ok(const int64_t (&st)[4], int B, int H, int S) {
+    if (st[3] != 1) return false;
+    const int ext[3] = {B, H, S};
+    for (int i = 0; i < 3; ++i)
+        if (ext[i] > 1 && (st[i] <= 0 || st[i] % 8 != 0)) return false;  // 16-byte multiples
+    return true;
+}
+
+}  // namespace
+
+bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
+                       const int64_t (&os)[4], const void* q, const void* k, const void* v, const void* o) {
+    if (d.dtype != B2A_F16 && d.dtype != B2A_BF16) return false;
+    if (d.D != kHeadDim || d.Dv != kHeadDim) return false;
+    if (static_cast<long long>(d.B) * d.Hkv > 65535) return false;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (!al(q) || !al(k) || !al(v) || !al(o)) return false;
+    if (!strides_ok(qs, d.B, d.Hq, d.Sq) || !strides_ok(ks, d.B, d.Hkv, d.Skv) || !strides_ok(vs, d.B, d.Hkv, d.Skv) ||
+        !strides_ok(os, d.B, d.Hq, d.Sq))
+        return false;
+    return encode_fn() != nullptr;
+}
+
+int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
+                   const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
+                   cudaStream_t stream) {
+    const bool bf16 = d.dtype == B2A_BF16;
+    CUtensorMap mq, mk, mv, mo;
+    if (!make_map(&mq, q, bf16, d.B, d.Hq, d.Sq, qs, 128) || !make_map(&mk, k, bf16, d.B, d.Hkv, d.Skv, ks, 128) ||
+        !make_map(&mv, v, bf16, d.B, d.Hkv, d.Skv, vs, 128) || !make_map(&mo, o, bf16, d.B, d.Hq, d.Sq, os, 32))
+        return B2A_ERR_CUDA;
+    TcParams p{};
+    p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.G = d.Hq / d.Hkv; p.Sq = d.Sq; p.Skv = d.Skv;
+    p.causal = d.causal;
+    p.scale_log2 = d.scale * kLog2e;
+    p.status = status;
+    const int nrb = (d.Sq + kBM - 1) / kBM;
+    const int pairs = (nrb * p.G + 1) / 2;
+    dim3 grid(pairs, d.B * d.Hkv);
+    static bool configured[2][64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
+    auto kern = bf16 ? sdpa_tc_kernel<true> : sdpa_tc_kernel<false>;
+    if (dev < 0 || dev >= 64 || !configured[bf16][dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B2A_ERR_CUDA;
+        if (dev >= 0 && dev < 64) configured[bf16][dev] = true;
+    }
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mo, p);
+    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+}
+
 }  // namespace b2a
