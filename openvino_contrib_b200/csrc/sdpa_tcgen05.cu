@@ -55,6 +55,35 @@ __device__ __forceinline__ float ex2f(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two float32 lanes in one 64-bit register pair, for the packed f32x2 arithmetic of sm_100
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if constexpr (kBf16) {
@@ -258,11 +287,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             if (!keep) s[q][i] = 0xff800000u;  // -inf
                         }
                 }
-                float mx = -INFINITY;
+                // row maximum: four independent chains of 3-input max (a single chain of 128 would be latency-bound)
+                float mq[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
+                for (int q = 0; q < 4; ++q) {
+                    mq[q] = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[q][i]));
+                    for (int i = 0; i < 32; i += 2)
+                        mq[q] = max3f(mq[q], __uint_as_float(s[q][i]), __uint_as_float(s[q][i + 1]));
+                }
+                const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
                 const float m_cand = mx * c;
                 const bool need = (j == 0) || (m_cand > m_used + kLazyThreshold);
                 const bool need_any = __any_sync(0xffffffffu, need);
@@ -273,20 +307,28 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     m_used = m_new;
                     l *= alpha;
                 }
-                float sum = 0.f;
+                // P = exp2(S*c - m): the scale-and-shift and the row sum run two elements per instruction (f32x2)
+                const uint64_t c2 = f2_pack(c, c), nm2 = f2_pack(-m_used, -m_used);
+                uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float p0 = ex2f(fmaf(__uint_as_float(s[q][2 * i]), c, -m_used));
-                        const float p1 = ex2f(fmaf(__uint_as_float(s[q][2 * i + 1]), c, -m_used));
-                        sum += p0 + p1;
+                        const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1])), c2, nm2);
+                        float x0, x1;
+                        f2_unpack(x2, x0, x1);
+                        const float p0 = ex2f(x0), p1 = ex2f(x1);
+                        sum2[i & 3] = f2_add(sum2[i & 3], f2_pack(p0, p1));
                         pk[i] = pack2<kBf16>(p0, p1);
                     }
                     tmem_st16(tS + 16 * q, pk);  // P over the first 64 columns of S, behind what was already read
                 }
-                l += sum;
+                {
+                    float a0, a1;
+                    f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), a0, a1);
+                    l += a0 + a1;
+                }
                 if (need_any && j > 0) {
                     // O_X still holds the old scale; PV_X(j-1) must have landed before it is touched
                     ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (j - 1) & 1, abort_flag));
