@@ -36,12 +36,12 @@ constexpr int kBN = 128;             // keys per step
 constexpr int kHeadDim = 128;
 constexpr int kPanel = 128 * 128;    // bytes of one [128 rows x 64 elements] swizzled panel
 constexpr int kTile = 2 * kPanel;    // a [128 x 128] 16-bit tile
-constexpr int kThreads = 320;
-constexpr int kNumBars = 17;
+constexpr int kThreads = 384;          // 3 warpgroups: softmax A, softmax B, {producer, MMA issuer, 2 idle warps}
+constexpr int kNumBars = 19;
 constexpr int kSmemBytes = 6 * kTile + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot, abort flag */;
 constexpr float kLazyThreshold = 8.0f;  // log2 units
 
-enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16 };
+enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16, P_HALF = 17 };
 
 struct TcParams {
     int B, Hq, Hkv, G, Sq, Skv;
@@ -84,6 +84,35 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+// exp2 of two values on the FMA pipe.  The special-function unit delivers 16 exp2 per clock and SM, which is as
+// much time as the tensor core needs for the two matrix products of a tile; moving part of the exponentials to
+// ordinary arithmetic can take the softmax off the critical path.  Measured on B200 with one softmax warp per
+// tile and scheduler partition, the extra issue slots cost as much as the special-function time they save, so
+// the share is 0 by default (B2A_TC_POLY_PER4 selects 0..4 of every 4 element pairs).  x = n + f with n = round(x) (magic-number add),
+// 2^f on [-0.5, 0.5] by a degree-3 minimax polynomial (relative error 7.5e-5, far below the 2^-9 rounding of P
+// to bf16), 2^n by adding n to the exponent field.  Inputs are clamped at -126 so that -inf and very negative
+// scores give a harmless 2^-126 instead of a wrapped exponent.
+#ifndef B2A_TC_POLY_PER4
+#define B2A_TC_POLY_PER4 0
+#endif
+constexpr int kPolyPer4 = B2A_TC_POLY_PER4;  // of every 4 element pairs, this many take the polynomial path
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+    float x0, x1;
+    f2_unpack(x2, x0, x1);
+    const uint64_t xc = f2_pack(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t t2 = f2_add(xc, f2_pack(kMagic, kMagic));
+    const uint64_t n2 = f2_add(t2, f2_pack(-kMagic, -kMagic));
+    const uint64_t f2v = f2_fma(n2, f2_pack(-1.0f, -1.0f), xc);
+    uint64_t r2 = f2_fma(f2v, f2_pack(0.0551716685f, 0.0551716685f), f2_pack(0.2426111251f, 0.2426111251f));
+    r2 = f2_fma(r2, f2v, f2_pack(0.6932609677f, 0.6932609677f));
+    r2 = f2_fma(r2, f2v, f2_pack(0.9999280572f, 0.9999280572f));
+    float r0, r1, t0, t1;
+    f2_unpack(r2, r0, r1);
+    f2_unpack(t2, t0, t1);
+    p0 = __int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
+}
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if constexpr (kBf16) {
@@ -101,6 +130,20 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
         if (clock64() - t0 > kWaitTicks) return;
     }
 }
+
+// Optional cycle trace of the first CTA (compile with -DB2A_TC_TRACE): clock64() at fixed points of the softmax
+// warp 0 of tile A (slots j*8 + k) and of the MMA thread (slots 1024 + j*8 + k) for the first 64 key steps.
+#ifdef B2A_TC_TRACE
+__device__ long long g_tc_trace[2048];
+#define TC_TRACE(base, j, k)                                                                   \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 64) g_tc_trace[(base) + (j)*8 + (k)] = clock64(); \
+    } while (0)
+#else
+#define TC_TRACE(base, j, k) \
+    do {                     \
+    } while (0)
+#endif
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -139,7 +182,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     // ---- set-up: barriers, TMEM
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kNumBars; ++i) mbar_init(BAR(i), (i == P_READY || i == P_READY + 1) ? 128u : 1u);
+        for (int i = 0; i < kNumBars; ++i) mbar_init(BAR(i), (i == P_READY || i == P_READY + 1 || i == P_HALF || i == P_HALF + 1) ? 128u : 1u);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -152,7 +195,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8) {
+    // Registers follow the work: the service warpgroup (producer, MMA issuer, two idle warps) keeps 40 per thread,
+    // the softmax groups get 232.
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    }
+    if (warp >= 10) {
+        // idle warps of the service warpgroup
+    } else if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
             prefetch_tensormap(&tmQ);
@@ -201,10 +251,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                            smem_desc_sw128(sK + st * kTile + off, 16, 1024), idesc_qk, ks > 0);
                 }
             };
-            auto issue_pv = [&](int X, int st, bool acc) {  // O_X += P_X V : 8 steps of 16 along the keys
+            // O_X += P_X V : 8 steps of 16 along the keys, issued in two halves as the halves of P arrive
+            auto issue_pv = [&](int X, int st, bool acc, int ks_lo) {
                 const uint32_t d = tmem + static_cast<uint32_t>(256 + X * 128);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
+                for (int ks = ks_lo; ks < ks_lo + 4; ++ks) {
                     mma_ts(d, tmem + static_cast<uint32_t>(X * 128 + ks * 8),
                            smem_desc_sw128(sV + st * kTile + ks * 2048, kPanel, 1024), idesc_pv, acc || ks > 0);
                 }
@@ -228,13 +279,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int j = 0; ok && j < nmax; ++j) {
                 const int stv = j & 1;
                 if (!mbar_wait(BAR(V_FULL + stv), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+                TC_TRACE(1024, j, 0);
                 bool k_next_ready = false;
 #pragma unroll
                 for (int X = 0; X < 2; ++X) {
                     if (ok && j < nkv[X]) {
+                        if (!mbar_wait(BAR(P_HALF + X), j & 1, abort_flag)) { ok = false; break; }
+                        TC_TRACE(1024, j, 1 + 2 * X);
+                        tc_fence_after();
+                        issue_pv(X, stv, j > 0, 0);
                         if (!mbar_wait(BAR(P_READY + X), j & 1, abort_flag)) { ok = false; break; }
                         tc_fence_after();
-                        issue_pv(X, stv, j > 0);
+                        issue_pv(X, stv, true, 4);
                         mma_commit(BAR(O_DONE + X));
                     }
                     if (ok && j + 1 < nkv[X]) {
@@ -246,6 +302,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         issue_qk(X, (j + 1) & 1);
                         mma_commit(BAR(S_FULL + X));
                     }
+                    TC_TRACE(1024, j, 2 + 2 * X);
                 }
                 if (!ok) break;
                 mma_commit(BAR(V_EMPTY + stv));
@@ -256,6 +313,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
     } else {
         // =============================== softmax + epilogue of tile X ===============================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         const int X = warp >> 2;
         const int r = static_cast<int>(threadIdx.x) - X * 128;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -270,11 +328,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // every lane takes the same decision, so the warp-collective TMEM instructions stay converged
                 ok = __all_sync(0xffffffffu, mbar_wait(BAR(S_FULL + X), j & 1, abort_flag));
                 if (!ok) break;
+                if (threadIdx.x == 0) TC_TRACE(0, j, 0);
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) tmem_ld32(tS + 32 * q, s[q]);
                 tmem_wait_ld();
+                if (threadIdx.x == 0) TC_TRACE(0, j, 1);
                 const int key0 = j * kBN;
                 const bool boundary = (key0 + kBN - 1 >= p.Skv) || (p.causal && key0 + kBN - 1 > row0[X]);
                 if (boundary) {
@@ -298,6 +358,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
                 const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
                 const float m_cand = mx * c;
+                if (threadIdx.x == 0) TC_TRACE(0, j, 2);
                 const bool need = (j == 0) || (m_cand > m_used + kLazyThreshold);
                 const bool need_any = __any_sync(0xffffffffu, need);
                 float alpha = 1.f;
@@ -316,19 +377,32 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1])), c2, nm2);
-                        float x0, x1;
-                        f2_unpack(x2, x0, x1);
-                        const float p0 = ex2f(x0), p1 = ex2f(x1);
+                        float p0, p1;
+                        if ((i & 3) < kPolyPer4) {
+                            exp2_poly2(x2, p0, p1);  // FMA pipe
+                        } else {
+                            float x0, x1;
+                            f2_unpack(x2, x0, x1);
+                            p0 = ex2f(x0);  // MUFU
+                            p1 = ex2f(x1);
+                        }
                         sum2[i & 3] = f2_add(sum2[i & 3], f2_pack(p0, p1));
                         pk[i] = pack2<kBf16>(p0, p1);
                     }
                     tmem_st16(tS + 16 * q, pk);  // P over the first 64 columns of S, behind what was already read
+                    // first 64 keys of P are in TMEM: PV can start on them, unless O still has to be rescaled
+                    if (q == 1 && !(need_any && j > 0)) {
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(BAR(P_HALF + X));
+                    }
                 }
                 {
                     float a0, a1;
                     f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), a0, a1);
                     l += a0 + a1;
                 }
+                if (threadIdx.x == 0) TC_TRACE(0, j, 3);
                 if (need_any && j > 0) {
                     // O_X still holds the old scale; PV_X(j-1) must have landed before it is touched
                     ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (j - 1) & 1, abort_flag));
@@ -343,10 +417,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st32(tO + 32 * q, o);
                     }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(BAR(P_HALF + X));
                 }
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(BAR(P_READY + X));
+                if (threadIdx.x == 0) TC_TRACE(0, j, 4);
             }
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (nkv[X] - 1) & 1, abort_flag));
             if (ok) {
@@ -482,3 +560,9 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
 }
 
 }  // namespace b2a
+
+#ifdef B2A_TC_TRACE
+extern "C" int b2a_debug_tc_trace(long long* host_out, int n) {
+    return cudaMemcpyFromSymbol(host_out, b2a::g_tc_trace, sizeof(long long) * static_cast<size_t>(n)) == cudaSuccess ? 0 : 6;
+}
+#endif
