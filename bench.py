@@ -205,14 +205,16 @@ def bench_prefill(args, rank, world, local):
     v_h = (torch.randn(B, Hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)[:, sl_k].contiguous().pin_memory()
     q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
     out = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16, device="cuda")
-    gathered = torch.empty(world, B, hq_l, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    from openvino_contrib_b200.sharding import HeadShard, gather_heads_bhsd, gather_heads_rows  # noqa: F401
+    shard = HeadShard(rank, world, Hq, Hkv)
+    gathered = torch.empty(world * B, hq_l, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 else None
     launches = [0]
 
     def step():
         b2a.sdpa(q, k, v, causal=True, out=out)
         launches[0] += 1
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            gather_heads_bhsd(out, shard, buffer=gathered)
 
     sampler = ClockSampler(local)
     ms, t0, t1 = timed(step, args.steps, args.warmup, world)
@@ -238,7 +240,7 @@ def bench_prefill(args, rank, world, local):
         qd, kd, vd = q_h.cuda(non_blocking=True), k_h.cuda(non_blocking=True), v_h.cuda(non_blocking=True)
         o = b2a.sdpa(qd, kd, vd, causal=True)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, o)
+            gather_heads_bhsd(o, shard, buffer=gathered)
         out_h.copy_(o, non_blocking=True)
     ems, _, _ = timed(e2e_step, max(3, args.steps // 2), 2, world)
     h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
@@ -296,13 +298,15 @@ def bench_decode(name, steps, warmup, rank, world):
     out = torch.empty(n, hq_l * D, dtype=torch.float16, device="cuda")
     ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, hq_l, n, n, maxc, 1)),
                      dtype=torch.uint8, device="cuda")
-    gathered = torch.empty(world, n, hq_l * D, dtype=torch.float16, device="cuda") if world > 1 else None
+    from openvino_contrib_b200.sharding import HeadShard, gather_heads_rows
+    shard = HeadShard(rank, world, Hq, Hkv)
+    gathered = torch.empty(world * n, hq_l * D, dtype=torch.float16, device="cuda") if world > 1 else None
 
     def step():
         b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1, out=out,
                             workspace=ws)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            gather_heads_rows(out, shard, D, buffer=gathered)
     ms, _, _ = timed(step, steps, warmup, world)
     tokens = int(ctx.sum())
     kv_bytes = tokens * Hkv * 2 * (D + 4)  # whole job: all ranks' heads

@@ -1,0 +1,93 @@
+"""KV-head sharding of the attention path over the GPUs of one node.
+
+Heads are independent, so rank r of N owns KV heads [r*Hkv/N, (r+1)*Hkv/N) and the Hq/Hkv query heads that read
+each of them; its K/V tensors and KV pools hold only those heads and nothing of K or V ever crosses NVLink.  The
+single exchange is the all-gather of the per-head outputs (NCCL over NVLink in production; any
+``torch.distributed`` backend works, which is how the host logic is tested on CPU with gloo).
+
+The reference plugin has no counterpart: it never spans devices (one independent plugin configuration per device
+id, ``modules/nvidia_plugin/src/cuda_plugin.cpp:25-32``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class HeadShard:
+    rank: int
+    world: int
+    hq: int
+    hkv: int
+
+    def __post_init__(self):
+        if self.hkv % self.world != 0 or self.hq % self.hkv != 0:
+            raise ValueError(f"cannot shard Hq={self.hq}, Hkv={self.hkv} over {self.world} ranks by KV head")
+
+    @property
+    def hkv_local(self) -> int:
+        return self.hkv // self.world
+
+    @property
+    def hq_local(self) -> int:
+        return self.hq // self.world
+
+    @property
+    def kv_heads(self) -> slice:
+        return slice(self.rank * self.hkv_local, (self.rank + 1) * self.hkv_local)
+
+    @property
+    def q_heads(self) -> slice:
+        return slice(self.rank * self.hq_local, (self.rank + 1) * self.hq_local)
+
+    # ---- SDPA layout [B, H, S, D]
+    def take_q(self, q: torch.Tensor) -> torch.Tensor:
+        return q[:, self.q_heads]
+
+    def take_kv(self, kv: torch.Tensor) -> torch.Tensor:
+        return kv[:, self.kv_heads]
+
+    # ---- paged layout [tokens, H*D]
+    def take_q_rows(self, q: torch.Tensor, d: int) -> torch.Tensor:
+        return q.view(q.shape[0], self.hq, d)[:, self.q_heads].reshape(q.shape[0], self.hq_local * d)
+
+    def take_kv_rows(self, kv: torch.Tensor, d: int) -> torch.Tensor:
+        return kv.view(kv.shape[0], self.hkv, d)[:, self.kv_heads].reshape(kv.shape[0], self.hkv_local * d)
+
+
+def gather_heads_bhsd(local_out: torch.Tensor, shard: HeadShard, group=None,
+                      buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather [B, Hq/N, S, D] shards into [B, Hq, S, D] (rank-major along the head axis)."""
+    if shard.world == 1:
+        return local_out
+    b, hl, s, d = local_out.shape
+    if buffer is None:
+        buffer = torch.empty((shard.world * b, hl, s, d), dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather_into_tensor(buffer, local_out.contiguous(), group=group)  # rank-major concatenation on dim 0
+    return buffer.view(shard.world, b, hl, s, d).permute(1, 0, 2, 3, 4).reshape(b, shard.world * hl, s, d)
+
+
+def gather_heads_rows(local_out: torch.Tensor, shard: HeadShard, d: int, group=None,
+                      buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather [tokens, Hq/N*D] shards into [tokens, Hq*D]."""
+    if shard.world == 1:
+        return local_out
+    t = local_out.shape[0]
+    if buffer is None:
+        buffer = torch.empty((shard.world * t, shard.hq_local * d), dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather_into_tensor(buffer, local_out.contiguous(), group=group)
+    return buffer.view(shard.world, t, shard.hq_local * d).permute(1, 0, 2).reshape(t, shard.hq * d)
+
+
+def sharded_sdpa(q, k, v, shard: HeadShard, attend: Callable, group=None, **kw) -> torch.Tensor:
+    """Run ``attend(q_local, k_local, v_local, **kw)`` on this rank's heads and gather the full output.
+
+    ``attend`` is the device attention (``openvino_contrib_b200.sdpa`` on a GPU); the tests pass a CPU function to
+    check the slicing and the gather order.
+    """
+    o = attend(shard.take_q(q).contiguous(), shard.take_kv(k).contiguous(), shard.take_kv(v).contiguous(), **kw)
+    return gather_heads_bhsd(o, shard, group)
