@@ -207,7 +207,7 @@ def bench_prefill(args, rank, world, local):
     out = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16, device="cuda")
     from openvino_contrib_b200.sharding import HeadShard, gather_heads_bhsd, gather_heads_rows  # noqa: F401
     shard = HeadShard(rank, world, Hq, Hkv)
-    gathered = torch.empty(world * B, hq_l, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    gathered = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 else None
     launches = [0]
 
     def step():

@@ -1,5 +1,5 @@
 // Thin wrappers over the sm_100a instructions the prefill kernel is built from: mbarrier, TMA (cp.async.bulk.tensor,
-// never with cluster multicast), tcgen05 (TMEM allocation, MMA, commit, TMEM load/store) and the shared-memory /
+// each CTA loading its own tiles), tcgen05 (TMEM allocation, MMA, commit, TMEM load/store) and the shared-memory /
 // instruction descriptors of the 5th-generation tensor core.
 #pragma once
 

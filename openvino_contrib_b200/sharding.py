@@ -61,14 +61,21 @@ class HeadShard:
 
 def gather_heads_bhsd(local_out: torch.Tensor, shard: HeadShard, group=None,
                       buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """All-gather [B, Hq/N, S, D] shards into [B, Hq, S, D] (rank-major along the head axis)."""
+    """All-gather [B, Hq/N, S, D] shards into [B, Hq, S, D].
+
+    One collective per batch entry, each landing directly in its [Hq, S, D] slab of the result (heads are the
+    outermost axis there, so rank-major concatenation is already the final layout): no re-layout copy afterwards.
+    ``buffer`` is the [B, Hq, S, D] result to fill.
+    """
     if shard.world == 1:
         return local_out
     b, hl, s, d = local_out.shape
     if buffer is None:
-        buffer = torch.empty((shard.world * b, hl, s, d), dtype=local_out.dtype, device=local_out.device)
-    dist.all_gather_into_tensor(buffer, local_out.contiguous(), group=group)  # rank-major concatenation on dim 0
-    return buffer.view(shard.world, b, hl, s, d).permute(1, 0, 2, 3, 4).reshape(b, shard.world * hl, s, d)
+        buffer = torch.empty((b, shard.world * hl, s, d), dtype=local_out.dtype, device=local_out.device)
+    local_out = local_out.contiguous()
+    for i in range(b):
+        dist.all_gather_into_tensor(buffer[i], local_out[i], group=group)
+    return buffer
 
 
 def gather_heads_rows(local_out: torch.Tensor, shard: HeadShard, d: int, group=None,
