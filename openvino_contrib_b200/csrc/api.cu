@@ -158,7 +158,8 @@ int b2a_paged_workspace_bytes(const b2a_paged_desc* desc, int sm_count, size_t* 
     if (rc != B2A_OK) return rc;
     if (sm_count <= 0) sm_count = device_sm_count();
     if (sm_count <= 0) sm_count = 148;
-    *out_bytes = paged_decode_supported(d) ? paged_decode_plan(d, sm_count).workspace_bytes : 0;
+    // pure decode steps and mixed steps both run the split-K decode kernel for their one-token sequences
+    *out_bytes = paged_decode_geometry_ok(d) ? paged_decode_plan(d, sm_count).workspace_bytes : 0;
     return B2A_OK;
 }
 
@@ -199,6 +200,17 @@ int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const voi
         const DecodePlan plan = paged_decode_plan(d, sms);
         if (workspace == nullptr || workspace_bytes < plan.workspace_bytes) return B2A_ERR_WORKSPACE;
         if (!aligned(workspace, 16)) return B2A_ERR_ALIGN;
+        return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, workspace, status, s);
+    }
+    if (paged_decode_geometry_ok(d) && paged_tc_supported(d, query, out)) {
+        // mixed step: multi-token sequences on the tensor-core kernel, one-token sequences on the decode kernel
+        const int sms = device_sm_count();
+        if (sms <= 0) return B2A_ERR_CUDA;
+        const DecodePlan plan = paged_decode_plan(d, sms);
+        if (workspace == nullptr || workspace_bytes < plan.workspace_bytes) return B2A_ERR_WORKSPACE;
+        if (!aligned(workspace, 16)) return B2A_ERR_ALIGN;
+        const int rc2 = paged_tc_launch(d, query, k_cache, v_cache, t, out, status, s);
+        if (rc2 != B2A_OK) return rc2;
         return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, workspace, status, s);
     }
     return paged_generic_launch(d, query, k_cache, v_cache, t, out, status, s);

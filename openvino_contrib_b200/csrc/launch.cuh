@@ -24,7 +24,8 @@ struct DecodePlan {
     int max_splits;      // CTAs per (sequence, KV head)
     size_t workspace_bytes;
 };
-bool paged_decode_supported(const b2a_paged_desc& d);
+bool paged_decode_supported(const b2a_paged_desc& d);   // a pure decode step
+bool paged_decode_geometry_ok(const b2a_paged_desc& d); // the kernel's shape limits, whatever the step's mix
 DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count);
 int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
                         const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
@@ -42,6 +43,12 @@ bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int
 int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
                    const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
                    cudaStream_t stream);
+
+// the same kernel body over a paged u8 cache: the multi-token sequences of a step (sequences with one new token are
+// left to the decode kernel, which in turn skips the others)
+bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* out);
+int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
+                    const PagedTables& t, void* out, int32_t* status, cudaStream_t stream);
 
 int device_sm_count();
 

@@ -131,11 +131,11 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeP
 
     const int tok = p.t.subsequence_begins[seq];
     const int qlen = p.t.subsequence_begins[seq + 1] - tok;
-    if (qlen <= 0) return;
+    if (qlen != 1) return;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
     const int past = p.t.past_lens[seq];
     const int ctx = past + 1;  // the query token sits at position `past` and sees 0..past
     const int nblk = (ctx + kBS - 1) / kBS;
-    if (qlen != 1 || past < 0 || nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
+    if (past < 0 || nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
         if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
         return;
     }
@@ -436,10 +436,14 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
 
 }  // namespace
 
-bool paged_decode_supported(const b2a_paged_desc& d) {
+bool paged_decode_geometry_ok(const b2a_paged_desc& d) {
     const int g = d.Hkv > 0 ? d.Hq / d.Hkv : 0;
     return d.kv_dtype == B2A_U8 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) && d.D == kD && d.Dv == kD &&
-           d.block_size == kBS && d.max_q_len == 1 && g >= 1 && g <= 16 && d.num_tokens == d.num_seqs;
+           d.block_size == kBS && g >= 1 && g <= 16;
+}
+
+bool paged_decode_supported(const b2a_paged_desc& d) {
+    return paged_decode_geometry_ok(d) && d.max_q_len == 1 && d.num_tokens == d.num_seqs;
 }
 
 DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count) {

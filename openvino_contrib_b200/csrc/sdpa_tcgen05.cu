@@ -1,18 +1,28 @@
 // Fused attention for prefill on the 5th-generation tensor core: S = Q K^T and O = P V as tcgen05.mma with
-// accumulators in tensor memory, Q/K/V tiles staged by TMA, online softmax in registers.  f16 / bf16, D = Dv = 128,
-// causal or unmasked, grouped-query heads.
+// accumulators in tensor memory, online softmax in registers.  f16 / bf16, D = Dv = 128, grouped-query heads.
+// Two front ends share one kernel body:
+//   * dense  (ScaledDotProductAttention): Q, K, V are [B, H, S, 128] tensors, causal or unmasked; K/V tiles are
+//     staged by TMA;
+//   * paged  (PagedAttentionExtension, sequences with two or more new tokens): Q rows come from the step's
+//     [tokens, Hq*128] matrix, K/V from the u8 block pool through the block table - a producer warpgroup
+//     de-quantises 128-token tiles ((code - zp) * scale in f32, rounded to the query type) straight into the
+//     swizzled shared-memory layout the tensor core reads.  Query token i of a sequence sees cache positions
+//     0 .. past_len + i.
 //
-// One CTA (10 warps) owns TWO 128-row query tiles of one KV head and walks the keys 128 at a time:
+// One CTA owns TWO 128-row query tiles of one KV head and walks the keys 128 at a time:
 //   warps 0-3   softmax of tile A: thread = query row = TMEM lane.  Reads S_A (tcgen05.ld), keeps the running max
 //               and sum, writes P_A = exp2(S*c - m) as 16-bit pairs over the first half of S_A's columns
-//               (tcgen05.st), rescales O_A in TMEM when the maximum moved, finally normalises O_A and stores it
-//               through shared memory with TMA stores (one [64 x 32] box per warp and panel).
+//               (tcgen05.st) and signals the MMA issuer after the first 64 keys and again after all 128; rescales
+//               O_A in TMEM when the maximum moved; finally normalises O_A and stores it (TMA stores from shared
+//               memory, one [64 x 32] box per warp and panel, in dense mode; row-wise stores in paged mode).
 //   warps 4-7   the same for tile B.
-//   warp  8     TMA producer (one lane): Q tiles once, then K_j and V_j into two-stage rings.
+//   warp  8     TMA producer (one lane): Q tiles once, and in dense mode K_j and V_j into two-stage rings.
 //   warp  9     MMA issuer (one lane): S_X(j) = Q_X K_j^T (A and B from shared memory, K-major, 128-byte swizzle),
 //               O_X += P_X(j) V_j (A from TMEM, B from shared memory, MN-major).  Order per step:
 //               PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1) - while one tile's softmax runs, the tensor core works on
 //               the other tile.  The warp also owns the TMEM allocation (all 512 columns: S_A S_B O_A O_B).
+//   warps 10-11 idle (they complete the service warpgroup whose registers are handed to the softmax groups).
+//   warps 12-15 paged mode only: the de-quantising K/V producers.
 // The two tiles are consecutive entries of the list (row block, query head of the group), query heads fastest, so
 // with an even group size both tiles cover the same rows of two heads that share K/V, and the causal structure of
 // the pair is identical.  Heavy (late) row blocks are scheduled first.
@@ -36,18 +46,25 @@ constexpr int kBN = 128;             // keys per step
 constexpr int kHeadDim = 128;
 constexpr int kPanel = 128 * 128;    // bytes of one [128 rows x 64 elements] swizzled panel
 constexpr int kTile = 2 * kPanel;    // a [128 x 128] 16-bit tile
-constexpr int kThreads = 384;          // 3 warpgroups: softmax A, softmax B, {producer, MMA issuer, 2 idle warps}
-constexpr int kNumBars = 19;
+constexpr int kThreadsDense = 384;   // 3 warpgroups: softmax A, softmax B, {producer, MMA issuer, 2 idle warps}
+constexpr int kThreadsPaged = 512;   // plus the de-quantising producer warpgroup
+constexpr int kNumBars = 21;
 constexpr int kSmemBytes = 6 * kTile + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot, abort flag */;
 constexpr float kLazyThreshold = 8.0f;  // log2 units
+constexpr int kCacheChunk = 16 * (kHeadDim + 4);  // bytes of one (block, KV head) chunk of the u8 pool
 
-enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16, P_HALF = 17 };
+enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16, P_HALF = 17, Q_CONV = 19 };
 
 struct TcParams {
     int B, Hq, Hkv, G, Sq, Skv;
     int causal;
     float scale_log2;
     int32_t* status;
+    // paged mode
+    const uint8_t* k_cache;
+    const uint8_t* v_cache;
+    PagedTables t;
+    void* out;  // [tokens, Hq*128]
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -88,14 +105,14 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
 // much time as the tensor core needs for the two matrix products of a tile; moving part of the exponentials to
 // ordinary arithmetic can take the softmax off the critical path.  Measured on B200 with one softmax warp per
 // tile and scheduler partition, the extra issue slots cost as much as the special-function time they save, so
-// the share is 0 by default (B2A_TC_POLY_PER4 selects 0..4 of every 4 element pairs).  x = n + f with n = round(x) (magic-number add),
-// 2^f on [-0.5, 0.5] by a degree-3 minimax polynomial (relative error 7.5e-5, far below the 2^-9 rounding of P
-// to bf16), 2^n by adding n to the exponent field.  Inputs are clamped at -126 so that -inf and very negative
-// scores give a harmless 2^-126 instead of a wrapped exponent.
+// the share is 0 by default (B2A_TC_POLY_PER4 selects 0..4 of every 4 element pairs).
+// x = n + f with n = round(x) (magic-number add), 2^f on [-0.5, 0.5] by a degree-3 minimax polynomial (relative
+// error 7.5e-5, far below the 2^-9 rounding of P to bf16), 2^n by adding n to the exponent field.  Inputs are
+// clamped at -126 so that -inf and very negative scores give a harmless 2^-126 instead of a wrapped exponent.
 #ifndef B2A_TC_POLY_PER4
 #define B2A_TC_POLY_PER4 0
 #endif
-constexpr int kPolyPer4 = B2A_TC_POLY_PER4;  // of every 4 element pairs, this many take the polynomial path
+constexpr int kPolyPer4 = B2A_TC_POLY_PER4;
 __device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
     constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
     float x0, x1;
@@ -135,9 +152,9 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 // warp 0 of tile A (slots j*8 + k) and of the MMA thread (slots 1024 + j*8 + k) for the first 64 key steps.
 #ifdef B2A_TC_TRACE
 __device__ long long g_tc_trace[2048];
-#define TC_TRACE(base, j, k)                                                                   \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 64) g_tc_trace[(base) + (j)*8 + (k)] = clock64(); \
+#define TC_TRACE(base, j, k)                                                                                       \
+    do {                                                                                                           \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64) g_tc_trace[(base) + (j)*8 + (k)] = clock64(); \
     } while (0)
 #else
 #define TC_TRACE(base, j, k) \
@@ -145,9 +162,35 @@ __device__ long long g_tc_trace[2048];
     } while (0)
 #endif
 
+// De-quantise the 16 codes of one 16-byte piece and store them as two 16-byte chunks of a swizzled tile row.
 template <bool kBf16>
-__global__ void __launch_bounds__(kThreads, 1)
-sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+__device__ __forceinline__ void dequant_piece(uint4 w, float scale, float zp, uint8_t* row, int c16, int token) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    const uint64_t nz2 = f2_pack(-zp, -zp), sc2 = f2_pack(scale, scale), nm2 = f2_pack(-8388608.0f, -8388608.0f);
+    uint32_t outw[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // 0x4B0000xx is 2^23 + xx as float32: byte -> float without a convert instruction
+        const float b0 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7440));
+        const float b1 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7441));
+        const float b2 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7442));
+        const float b3 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7443));
+        float x0, x1, x2, x3;
+        f2_unpack(f2_mul(f2_add(f2_add(f2_pack(b0, b1), nm2), nz2), sc2), x0, x1);  // ((2^23 + q) - 2^23 - zp) * scale
+        f2_unpack(f2_mul(f2_add(f2_add(f2_pack(b2, b3), nm2), nz2), sc2), x2, x3);
+        outw[2 * i] = pack2<kBf16>(x0, x1);
+        outw[2 * i + 1] = pack2<kBf16>(x2, x3);
+    }
+    // the piece covers d = 16*c16 .. +15: chunks 2*c16 and 2*c16+1 of the 128-wide row, 8 chunks per 64-wide panel
+    uint8_t* panel = row + (c16 >> 2) * kPanel;
+    const int cp = (2 * c16) & 7;
+    *reinterpret_cast<uint4*>(panel + ((cp ^ (token & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    *reinterpret_cast<uint4*>(panel + (((cp + 1) ^ (token & 7)) << 4)) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+}
+
+template <bool kBf16, bool kPaged>
+__global__ void __launch_bounds__(kPaged ? kThreadsPaged : kThreadsDense, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -158,31 +201,65 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 6 * kTile + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 6 * kTile + kNumBars * 8 + 8);
     auto BAR = [&](int i) { return bars + 8u * static_cast<uint32_t>(i); };
+    constexpr bool kKvBf16 = kPaged ? false : kBf16;  // element format of the K/V tiles and of P
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- which two tiles
-    const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
-    const int nrb = (p.Sq + kBM - 1) / kBM;
+    // ---- which two tiles.  Rows are numbered inside the sequence (paged) or the tensor (dense); `pos_base` is the
+    // key position the first row of the problem may see up to, `kv_limit` the number of keys that exist.
+    int b = 0, hk, seq = 0, tok_base = 0, nrows_total, pos_base = 0, kv_limit;
+    bool causal;
+    if constexpr (kPaged) {
+        seq = blockIdx.z;
+        hk = blockIdx.y;
+        tok_base = p.t.subsequence_begins[seq];
+        nrows_total = p.t.subsequence_begins[seq + 1] - tok_base;
+        if (nrows_total < 2) return;  // decode rows and idle sequences belong to the decode kernel
+        pos_base = p.t.past_lens[seq];
+        kv_limit = pos_base + nrows_total;
+        causal = true;
+        const int nblk = (kv_limit + 15) / 16;
+        if (pos_base < 0 || tok_base < 0 || tok_base + nrows_total > p.t.num_tokens ||
+            nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
+            if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, B2A_DEV_BAD_LEN);
+            return;
+        }
+    } else {
+        b = blockIdx.y / p.Hkv;
+        hk = blockIdx.y % p.Hkv;
+        nrows_total = p.Sq;
+        kv_limit = p.Skv;
+        causal = p.causal != 0;
+    }
+    const int nrb = (nrows_total + kBM - 1) / kBM;
     const int tiles = nrb * p.G;
     const int pairs = (tiles + 1) / 2;
+    if (static_cast<int>(blockIdx.x) >= pairs) return;
     const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // late row blocks (most keys) first
-    int row0[2], head[2], nkv[2];
-#pragma unroll
-    for (int X = 0; X < 2; ++X) {
-        const int t = 2 * pair + X;
-        const bool present = t < tiles;
-        const int rb = present ? t / p.G : 0, g = present ? t % p.G : 0;
-        row0[X] = rb * kBM;
-        head[X] = hk * p.G + g;
-        const int kv_end = p.causal ? min(p.Skv, row0[X] + kBM) : p.Skv;
-        nkv[X] = present ? (kv_end + kBN - 1) / kBN : 0;
+    int row0A, row0B, headA, headB, nkvA, nkvB;
+    {
+        auto tile_of = [&](int t, int& row0, int& head, int& nkv) {
+            const bool present = t < tiles;
+            const int rb = present ? t / p.G : 0, g = present ? t % p.G : 0;
+            row0 = rb * kBM;
+            head = hk * p.G + g;
+            const int kv_end = causal ? min(kv_limit, pos_base + row0 + kBM) : kv_limit;
+            nkv = present ? (kv_end + kBN - 1) / kBN : 0;
+        };
+        tile_of(2 * pair, row0A, headA, nkvA);
+        tile_of(2 * pair + 1, row0B, headB, nkvB);
     }
-    const int nmax = max(nkv[0], nkv[1]);
+    const int nmax = max(nkvA, nkvB);
 
     // ---- set-up: barriers, TMEM
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kNumBars; ++i) mbar_init(BAR(i), (i == P_READY || i == P_READY + 1 || i == P_HALF || i == P_HALF + 1) ? 128u : 1u);
+        for (int i = 0; i < kNumBars; ++i) {
+            uint32_t count = 1;
+            if (i == P_READY || i == P_READY + 1 || i == P_HALF || i == P_HALF + 1) count = 128;
+            if (i == Q_CONV || i == Q_CONV + 1) count = 128;
+            if (kPaged && (i == K_FULL || i == K_FULL + 1 || i == V_FULL || i == V_FULL + 1)) count = 128;
+            mbar_init(BAR(i), count);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -195,44 +272,122 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    // Registers follow the work: the service warpgroup (producer, MMA issuer, two idle warps) keeps 40 per thread,
-    // the softmax groups get 232.
-    if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    // Registers follow the work: the service warpgroup keeps 56 per thread, the softmax groups take what is left
+    // (dense: 2*128*224 + 128*56 = 384*168; paged: 2*128*176 + 128*56 + 128*96 <= 512*128).
+    if (warp >= 8 && warp < 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     }
-    if (warp >= 10) {
+    if (warp >= 12) {
+        // =============================== de-quantising K/V producers (paged) ===============================
+        if constexpr (kPaged) {
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+            const int tp = static_cast<int>(threadIdx.x) - 384;
+            const int tok_in_blk = tp >> 3, c16 = tp & 7;
+            const int32_t* btab = p.t.block_indices + p.t.block_indices_begins[seq];
+            const int nblk = (kv_limit + 15) / 16;
+            bool ok = true;
+            if constexpr (kBf16) {
+                // bf16 queries: convert the Q tiles to f16 where they lie (the swizzle only permutes 16-byte
+                // chunks, so an element-wise pass keeps the layout); magnitudes beyond the f16 range saturate
+#pragma unroll
+                for (int X = 0; X < 2; ++X) {
+                    if ((X ? nkvB : nkvA) > 0) {
+                        ok = ok && __all_sync(0xffffffffu, mbar_wait(BAR(Q_FULL + X), 0, abort_flag));
+                        if (ok) {
+                            uint4* tile = reinterpret_cast<uint4*>(gbase + X * kTile);
+                            for (int i = tp; i < kTile / 16; i += 128) {
+                                uint4 v = tile[i];
+                                uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+                                    w[k] = pack2<false>(fminf(fmaxf(f.x, -65504.f), 65504.f), fminf(fmaxf(f.y, -65504.f), 65504.f));
+                                }
+                                tile[i] = v;
+                            }
+                            fence_proxy_async_smem();
+                            mbar_arrive(BAR(Q_CONV + X));
+                        }
+                    }
+                }
+            }
+            auto fill = [&](const uint8_t* cache, uint8_t* tile, int j) {
+#pragma unroll 2
+                for (int it = 0; it < 8; ++it) {
+                    const int lb = j * 8 + it;  // logical block: one block per pass, 128 threads = 16 tokens x 8 pieces
+                    const int token = it * 16 + tok_in_blk;
+                    const int pos = lb * 16 + tok_in_blk;
+                    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+                    float sc = 0.f, zp = 0.f;
+                    if (lb < nblk && pos < kv_limit) {
+                        const int phys = btab[lb];
+                        if (phys < 0 || phys >= p.t.num_blocks_total) {
+                            report(p.status, B2A_DEV_BAD_BLOCK);
+                        } else {
+                            const uint8_t* chunk = cache + (static_cast<size_t>(phys) * p.Hkv + hk) * kCacheChunk;
+                            w = *reinterpret_cast<const uint4*>(chunk + tok_in_blk * 128 + c16 * 16);
+                            const __half* meta = reinterpret_cast<const __half*>(chunk + 2048);
+                            sc = __half2float(meta[tok_in_blk]);
+                            zp = __half2float(meta[16 + tok_in_blk]);
+                        }
+                    }
+                    // positions past the context (and unusable blocks) become exact zeros: 0 * anything finite
+                    dequant_piece<kKvBf16>(w, sc, zp, tile + token * 128, c16, token);
+                }
+            };
+            for (int j = 0; j < nmax; ++j) {
+                const int st = j & 1, n = j >> 1;
+                if (n > 0) ok = __all_sync(0xffffffffu, mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag));
+                if (!ok) break;
+                fill(p.k_cache, gbase + 2 * kTile + st * kTile, j);
+                fence_proxy_async_smem();  // generic-proxy writes must be visible to the tensor core's reads
+                mbar_arrive(BAR(K_FULL + st));
+                if (n > 0) ok = __all_sync(0xffffffffu, mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag));
+                if (!ok) break;
+                fill(p.v_cache, gbase + 4 * kTile + st * kTile, j);
+                fence_proxy_async_smem();
+                mbar_arrive(BAR(V_FULL + st));
+            }
+        }
+    } else if (warp >= 10) {
         // idle warps of the service warpgroup
     } else if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
             prefetch_tensormap(&tmQ);
-            prefetch_tensormap(&tmK);
-            prefetch_tensormap(&tmV);
-#pragma unroll
-            for (int X = 0; X < 2; ++X) {
-                if (nkv[X] > 0) {
-                    mbar_expect_tx(BAR(Q_FULL + X), kTile);
-                    tma_load_4d(sQ + X * kTile, &tmQ, BAR(Q_FULL + X), 0, row0[X], head[X], b);
-                    tma_load_4d(sQ + X * kTile + kPanel, &tmQ, BAR(Q_FULL + X), 64, row0[X], head[X], b);
-                }
+            if constexpr (!kPaged) {
+                prefetch_tensormap(&tmK);
+                prefetch_tensormap(&tmV);
+            }
+            if (nkvA > 0) {
+                mbar_expect_tx(BAR(Q_FULL + 0), kTile);
+                tma_load_4d(sQ, &tmQ, BAR(Q_FULL + 0), 0, tok_base + row0A, headA, b);
+                tma_load_4d(sQ + kPanel, &tmQ, BAR(Q_FULL + 0), 64, tok_base + row0A, headA, b);
+            }
+            if (nkvB > 0) {
+                mbar_expect_tx(BAR(Q_FULL + 1), kTile);
+                tma_load_4d(sQ + kTile, &tmQ, BAR(Q_FULL + 1), 0, tok_base + row0B, headB, b);
+                tma_load_4d(sQ + kTile + kPanel, &tmQ, BAR(Q_FULL + 1), 64, tok_base + row0B, headB, b);
             }
             int issued_k = 0, issued_v = 0;
-            for (int j = 0; j < nmax; ++j) {
-                const int st = j & 1, n = j >> 1;
-                if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(BAR(K_FULL + st), kTile);
-                tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, j * kBN, hk, b);
-                tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, j * kBN, hk, b);
-                ++issued_k;
-                if (n > 0 && !mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(BAR(V_FULL + st), kTile);
-                tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, j * kBN, hk, b);
-                tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, j * kBN, hk, b);
-                ++issued_v;
+            if constexpr (!kPaged) {
+                for (int j = 0; j < nmax; ++j) {
+                    const int st = j & 1, n = j >> 1;
+                    if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) break;
+                    mbar_expect_tx(BAR(K_FULL + st), kTile);
+                    tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, j * kBN, hk, b);
+                    tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, j * kBN, hk, b);
+                    ++issued_k;
+                    if (n > 0 && !mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag)) break;
+                    mbar_expect_tx(BAR(V_FULL + st), kTile);
+                    tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, j * kBN, hk, b);
+                    tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, j * kBN, hk, b);
+                    ++issued_v;
+                }
             }
             if (*abort_flag) {  // let copies already in flight land before the CTA goes away
-                for (int X = 0; X < 2; ++X)
-                    if (nkv[X] > 0) mbar_drain(BAR(Q_FULL + X), 0);
+                if (nkvA > 0) mbar_drain(BAR(Q_FULL + 0), 0);
+                if (nkvB > 0) mbar_drain(BAR(Q_FULL + 1), 0);
                 for (int jj = max(0, issued_k - 2); jj < issued_k; ++jj) mbar_drain(BAR(K_FULL + (jj & 1)), (jj >> 1) & 1);
                 for (int jj = max(0, issued_v - 2); jj < issued_v; ++jj) mbar_drain(BAR(V_FULL + (jj & 1)), (jj >> 1) & 1);
             }
@@ -240,8 +395,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     } else if (warp == 9) {
         // =============================== MMA issuer ===============================
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc_f16(kBf16, false, kBM, kBN);
-            constexpr uint32_t idesc_pv = instr_desc_f16(kBf16, true, kBM, kHeadDim);
+            // operand formats (A and B of one MMA must agree): dense mode as given; paged mode f16 throughout - the
+            // de-quantised values keep 11 significant bits and bf16 queries are converted in shared memory first
+            constexpr uint32_t idesc_qk = instr_desc_f16(kKvBf16, false, kBM, kBN);
+            constexpr uint32_t idesc_pv = instr_desc_f16(kKvBf16, true, kBM, kHeadDim);
             auto issue_qk = [&](int X, int st) {  // S_X = Q_X K^T : 8 steps of 16 along D
                 const uint32_t d = tmem + static_cast<uint32_t>(X * 128);
 #pragma unroll
@@ -261,18 +418,19 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             };
             bool ok = true;
-#pragma unroll
-            for (int X = 0; X < 2; ++X)
-                if (nkv[X] > 0) ok = ok && mbar_wait(BAR(Q_FULL + X), 0, abort_flag);
+            constexpr int kQReady = (kPaged && kBf16) ? Q_CONV : Q_FULL;
+            if (nkvA > 0) ok = ok && mbar_wait(BAR(kQReady + 0), 0, abort_flag);
+            if (nkvB > 0) ok = ok && mbar_wait(BAR(kQReady + 1), 0, abort_flag);
             ok = ok && mbar_wait(BAR(K_FULL + 0), 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-#pragma unroll
-                for (int X = 0; X < 2; ++X) {
-                    if (nkv[X] > 0) {
-                        issue_qk(X, 0);
-                        mma_commit(BAR(S_FULL + X));
-                    }
+                if (nkvA > 0) {
+                    issue_qk(0, 0);
+                    mma_commit(BAR(S_FULL + 0));
+                }
+                if (nkvB > 0) {
+                    issue_qk(1, 0);
+                    mma_commit(BAR(S_FULL + 1));
                 }
                 mma_commit(BAR(K_EMPTY + 0));
             }
@@ -283,7 +441,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bool k_next_ready = false;
 #pragma unroll
                 for (int X = 0; X < 2; ++X) {
-                    if (ok && j < nkv[X]) {
+                    const int nkvX = X ? nkvB : nkvA;
+                    if (ok && j < nkvX) {
                         if (!mbar_wait(BAR(P_HALF + X), j & 1, abort_flag)) { ok = false; break; }
                         TC_TRACE(1024, j, 1 + 2 * X);
                         tc_fence_after();
@@ -293,7 +452,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         issue_pv(X, stv, true, 4);
                         mma_commit(BAR(O_DONE + X));
                     }
-                    if (ok && j + 1 < nkv[X]) {
+                    if (ok && j + 1 < nkvX) {
                         if (!k_next_ready) {
                             if (!mbar_wait(BAR(K_FULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                             k_next_ready = true;
@@ -313,18 +472,23 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
     } else {
         // =============================== softmax + epilogue of tile X ===============================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        if constexpr (kPaged) {
+            asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+        } else {
+            asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        }
         const int X = warp >> 2;
         const int r = static_cast<int>(threadIdx.x) - X * 128;
+        const int row0 = X ? row0B : row0A, head = X ? headB : headA, nkv = X ? nkvB : nkvA;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tS = tmem + lane_base + static_cast<uint32_t>(X * 128);
         const uint32_t tO = tmem + lane_base + static_cast<uint32_t>(256 + X * 128);
-        if (nkv[X] > 0) {
-            const int row = row0[X] + r;
+        if (nkv > 0) {
+            const int row_pos = pos_base + row0 + r;  // last key position this row may see (causal)
             const float c = p.scale_log2;
             float m_used = -1.0e30f, l = 0.f;
             bool ok = true;
-            for (int j = 0; j < nkv[X]; ++j) {
+            for (int j = 0; j < nkv; ++j) {
                 // every lane takes the same decision, so the warp-collective TMEM instructions stay converged
                 ok = __all_sync(0xffffffffu, mbar_wait(BAR(S_FULL + X), j & 1, abort_flag));
                 if (!ok) break;
@@ -336,14 +500,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 tmem_wait_ld();
                 if (threadIdx.x == 0) TC_TRACE(0, j, 1);
                 const int key0 = j * kBN;
-                const bool boundary = (key0 + kBN - 1 >= p.Skv) || (p.causal && key0 + kBN - 1 > row0[X]);
+                const bool boundary = (key0 + kBN - 1 >= kv_limit) || (causal && key0 + kBN - 1 > pos_base + row0);
                 if (boundary) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int key = key0 + q * 32 + i;
-                            const bool keep = key < p.Skv && (!p.causal || key <= row);
+                            const bool keep = key < kv_limit && (!causal || key <= row_pos);
                             if (!keep) s[q][i] = 0xff800000u;  // -inf
                         }
                 }
@@ -387,7 +551,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             p1 = ex2f(x1);
                         }
                         sum2[i & 3] = f2_add(sum2[i & 3], f2_pack(p0, p1));
-                        pk[i] = pack2<kBf16>(p0, p1);
+                        pk[i] = pack2<kKvBf16>(p0, p1);
                     }
                     tmem_st16(tS + 16 * q, pk);  // P over the first 64 columns of S, behind what was already read
                     // first 64 keys of P are in TMEM: PV can start on them, unless O still has to be rescaled
@@ -426,37 +590,62 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mbar_arrive(BAR(P_READY + X));
                 if (threadIdx.x == 0) TC_TRACE(0, j, 4);
             }
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (nkv[X] - 1) & 1, abort_flag));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (nkv - 1) & 1, abort_flag));
             if (ok) {
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                uint8_t* stage = gbase + X * kTile;  // Q_X is no longer needed: its tile is the staging buffer
+                if constexpr (kPaged) {
+                    // row-wise stores: rows past the sequence's end belong to other sequences and are dropped
+                    const bool valid = row0 + r < nrows_total;
+                    uint4* orow = reinterpret_cast<uint4*>(
+                        reinterpret_cast<uint16_t*>(p.out) +
+                        (static_cast<size_t>(tok_base + row0 + r) * p.Hq + head) * kHeadDim);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t o[32];
-                    tmem_ld32(tO + 32 * q, o);
-                    tmem_wait_ld();
-                    uint8_t* prow = stage + (q >> 1) * kPanel + r * 128;
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + 32 * q, o);
+                        tmem_wait_ld();
+                        if (valid) {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint4 v;
-                        v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
-                        v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
-                        v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
-                        v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
-                        const int chunk = (q & 1) * 4 + ch;  // 16-byte chunk of the 128-byte row, swizzled like TMA's
-                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = v;
+                            for (int ch = 0; ch < 4; ++ch) {
+                                uint4 v;
+                                v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
+                                v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
+                                v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
+                                v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
+                                orow[q * 4 + ch] = v;
+                            }
+                        }
                     }
-                }
-                // each warp stores its own 32 rows (a [64 x 32] box per panel): no cross-warp barrier is needed
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    const int w = warp & 3;
-                    tma_store_4d(&tmO, sQ + X * kTile + w * 32 * 128, 0, row0[X] + 32 * w, head[X], b);
-                    tma_store_4d(&tmO, sQ + X * kTile + kPanel + w * 32 * 128, 64, row0[X] + 32 * w, head[X], b);
-                    tma_store_commit();
-                    tma_store_wait_all();
+                } else {
+                    uint8_t* stage = gbase + X * kTile;  // Q_X is no longer needed: its tile is the staging buffer
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + 32 * q, o);
+                        tmem_wait_ld();
+                        uint8_t* prow = stage + (q >> 1) * kPanel + r * 128;
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint4 v;
+                            v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
+                            v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
+                            v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
+                            v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
+                            const int chunk = (q & 1) * 4 + ch;  // 16-byte chunk of the 128-byte row, swizzled like TMA's
+                            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = v;
+                        }
+                    }
+                    // each warp stores its own 32 rows (a [64 x 32] box per panel): no cross-warp barrier is needed
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int w = warp & 3;
+                        tma_store_4d(&tmO, sQ + X * kTile + w * 32 * 128, 0, row0 + 32 * w, head, b);
+                        tma_store_4d(&tmO, sQ + X * kTile + kPanel + w * 32 * 128, 64, row0 + 32 * w, head, b);
+                        tma_store_commit();
+                        tma_store_wait_all();
+                    }
                 }
             }
         }
@@ -515,6 +704,18 @@ bool strides_ok(const int64_t (&st)[4], int B, int H, int S) {
     return true;
 }
 
+template <typename Kern>
+int configure_once(Kern kern, bool (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B2A_ERR_CUDA;
+        if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+    return B2A_OK;
+}
+
 }  // namespace
 
 bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
@@ -547,15 +748,46 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     const int pairs = (nrb * p.G + 1) / 2;
     dim3 grid(pairs, d.B * d.Hkv);
     static bool configured[2][64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
-    auto kern = bf16 ? sdpa_tc_kernel<true> : sdpa_tc_kernel<false>;
-    if (dev < 0 || dev >= 64 || !configured[bf16][dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return B2A_ERR_CUDA;
-        if (dev >= 0 && dev < 64) configured[bf16][dev] = true;
-    }
-    kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mo, p);
+    auto kern = bf16 ? attn_tc_kernel<true, false> : attn_tc_kernel<false, false>;
+    const int rc = configure_once(kern, configured[bf16]);
+    if (rc != B2A_OK) return rc;
+    kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mo, p);
+    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+}
+
+bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* out) {
+    const int g = d.Hkv > 0 ? d.Hq / d.Hkv : 0;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    return d.kv_dtype == B2A_U8 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) && d.D == kHeadDim &&
+           d.Dv == kHeadDim && d.block_size == 16 && d.sliding_window == 0 && d.max_q_len >= 2 && g >= 1 &&
+           d.Hkv <= 65535 && al(query) && al(out) && encode_fn() != nullptr;
+}
+
+int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
+                    const PagedTables& t, void* out, int32_t* status, cudaStream_t stream) {
+    const bool bf16 = d.q_dtype == B2A_BF16;
+    // the step's query matrix [tokens, Hq*128] as a [1, Hq, tokens, 128] view
+    const int64_t qs[4] = {static_cast<int64_t>(d.num_tokens) * d.Hq * kHeadDim, kHeadDim,
+                           static_cast<int64_t>(d.Hq) * kHeadDim, 1};
+    CUtensorMap mq;
+    if (!make_map(&mq, query, bf16, 1, d.Hq, d.num_tokens, qs, 128)) return B2A_ERR_CUDA;
+    TcParams p{};
+    p.B = 1; p.Hq = d.Hq; p.Hkv = d.Hkv; p.G = d.Hq / d.Hkv; p.Sq = 0; p.Skv = 0;
+    p.causal = 1;
+    p.scale_log2 = d.scale * kLog2e;
+    p.status = status;
+    p.k_cache = static_cast<const uint8_t*>(k_cache);
+    p.v_cache = static_cast<const uint8_t*>(v_cache);
+    p.t = t;
+    p.out = out;
+    const int nrb = (d.max_q_len + kBM - 1) / kBM;
+    const int pairs = (nrb * p.G + 1) / 2;
+    dim3 grid(pairs, d.Hkv, d.num_seqs);
+    static bool configured[2][64] = {};
+    auto kern = bf16 ? attn_tc_kernel<true, true> : attn_tc_kernel<false, true>;
+    const int rc = configure_once(kern, configured[bf16]);
+    if (rc != B2A_OK) return rc;
+    kern<<<grid, kThreadsPaged, kSmemBytes, stream>>>(mq, mq, mq, mq, p);  // only the Q map is read in paged mode
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 

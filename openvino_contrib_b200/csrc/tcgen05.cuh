@@ -139,9 +139,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t
 // Instruction descriptor of kind::f16 (32 bits): D format f32 (1) in [4,6), A format in [7,10), B format in [10,13)
 // (0 = f16, 1 = bf16), A major in bit 15, B major in bit 16 (0 = K-major, 1 = MN-major), N >> 3 in [17,23),
 // M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t instr_desc_f16(bool bf16, bool b_mn_major, int m, int n) {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+__host__ __device__ constexpr uint32_t instr_desc_f16_ab(bool a_bf16, bool b_bf16, bool b_mn_major, int m, int n) {
+    return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t instr_desc_f16(bool bf16, bool b_mn_major, int m, int n) {
+    return instr_desc_f16_ab(bf16, bf16, b_mn_major, m, n);
 }
 
 // D[tmem] (+)= A[smem] . B[smem]; issued by ONE thread

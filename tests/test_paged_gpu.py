@@ -268,3 +268,47 @@ def test_config5_shape_properties(b2a):
     out_w = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1,
                                 sliding_window=ctxlen)
     assert torch.equal(out, out_w)
+
+
+# ---------------------------------------------------------------- multi-token rows on the tensor-core kernel
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_prefill_parity(b2a, dtype):
+    # (past, new tokens): fresh prefills, chunked-prefill continuations, ragged tails, decode rows in between
+    past = np.array([0, 100, 1000, 37, 0, 5, 255], np.int32)
+    qlen = np.array([300, 129, 2, 1, 1024, 128, 1], np.int32)
+    hq, hkv, d = 32, 8, 128
+    w = PagedWorkload(past + qlen, qlen, hq, hkv, d, seed=31)
+    q = _round(w.query, dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=hq,
+                              max_context_len=int((past + qlen).max()), max_q_len=int(qlen.max()), status=status)
+    assert int(status.item()) == 0
+    assert_close(out, w.reference(q.float().numpy()), dtype)
+
+
+def test_config4_mixed_step(b2a):
+    # 8 prefill sequences of 1024 tokens plus 120 decode sequences with contexts uniform in [256, 4096] (seed 4),
+    # bf16 queries, u8 cache, through the operator (store, then attend)
+    rng = np.random.default_rng(4)
+    dec_ctx = rng.integers(256, 4097, size=120)
+    past = np.concatenate([np.zeros(8, np.int64), dec_ctx - 1]).astype(np.int32)
+    qlen = np.concatenate([np.full(8, 1024), np.ones(120, np.int64)]).astype(np.int32)
+    hq, hkv, d, bs = 32, 8, 128, 16
+    w = PagedWorkload(past + qlen, qlen, hq, hkv, d, seed=4, table_seed=4)
+    new_k = _round(rng.standard_normal((int(w.sb[-1]), hkv * d), dtype=np.float32), torch.bfloat16)
+    new_v = _round(rng.standard_normal((int(w.sb[-1]), hkv * d), dtype=np.float32), torch.bfloat16)
+    ref_k, ref_v = w.k_cache.copy(), w.v_cache.copy()
+    opaged.kv_store_ref(new_k, ref_k, w.past, w.sb, w.bi, w.bb, hkv, d, bs)
+    opaged.kv_store_ref(new_v, ref_v, w.past, w.sb, w.bi, w.bb, hkv, d, bs)
+    q = _round(w.query, torch.bfloat16)
+    ref = opaged.paged_attention_ref(q.float().numpy(), ref_k, ref_v, w.past, w.sb, w.bi, w.bb, hq, hkv, d, bs)
+    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=128, max_context_len=4096)
+    cache = w.device_cache()
+    out = torch.empty(int(w.sb[-1]), hq * d, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    op.Execute([q.cuda(), new_k.cuda(), new_v.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, 4096],
+               [out], status=status)
+    assert int(status.item()) == 0
+    assert np.array_equal(cache.k.cpu().numpy(), ref_k) and np.array_equal(cache.v.cpu().numpy(), ref_v)
+    assert_close(out, ref, torch.bfloat16)
