@@ -317,6 +317,54 @@ def bench_decode(name, steps, warmup, rank, world):
             "peak_source": pk["source"], "cached_tokens": tokens, "launches_per_step": 2}
 
 
+def bench_mixed(steps, warmup, rank, world):
+    """Continuous-batching step through PagedAttentionExtension: 8 prefill sequences of 1024 tokens plus 120 decode
+    sequences with contexts uniform in [256, 4096] (seed 4), bf16 queries, u8 KV, Hq 32 / Hkv 8 / D 128.
+    One step = KV store of the 8312 new tokens + attention (tensor-core kernel for the prefill rows, split-K
+    kernel for the decode rows).  Single GPU."""
+    import openvino_contrib_b200 as b2a
+    Hq, Hkv, D, bs = 32, 8, 128, 16
+    rng = np.random.default_rng(4)
+    dec_ctx = rng.integers(256, 4097, size=120)
+    ctx = np.concatenate([np.full(8, 1024), dec_ctx])
+    qlen = np.concatenate([np.full(8, 1024), np.ones(120, np.int64)])
+    n = len(ctx)
+    cache, _, _, _, bi, bb = build_decode_problem(n, ctx, Hq, Hkv, D, seed=11)
+    past = torch.tensor(ctx - qlen, dtype=torch.int32, device="cuda")
+    sb_h = np.zeros(n + 1, np.int64)
+    sb_h[1:] = np.cumsum(qlen)
+    sb = torch.tensor(sb_h, dtype=torch.int32, device="cuda")
+    ntok = int(sb_h[-1])
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    q = torch.randn(ntok, Hq * D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(ntok, Hkv * D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(ntok, Hkv * D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(ntok, Hq * D, dtype=torch.bfloat16, device="cuda")
+    rb = int(sum((int(x) + 127) // 128 for x in qlen if x >= 2))  # what the scheduler knows (KvBlockManager reports it)
+    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.bfloat16, cache, Hq, n, ntok, 4096, 1024, rb)),
+                     dtype=torch.uint8, device="cuda")
+
+    def attend():
+        b2a.paged_attention(q, cache, past, sb, bi, bb, hq=Hq, max_context_len=4096, max_q_len=1024, out=out,
+                            workspace=ws, prefill_row_blocks=rb)
+
+    def step():
+        b2a.paged_kv_store(k, v, cache, past, sb, bi, bb)
+        attend()
+    ms, _, _ = timed(step, steps, warmup, 1)
+    ams, _, _ = timed(attend, steps, 1, 1)
+    pk = peaks()
+    prefill_flops = 8 * 4 * Hq * D * (1024 * 1025 // 2)
+    decode_bytes = int(dec_ctx.sum()) * Hkv * 2 * (D + 4)
+    store_bytes = ntok * Hkv * 2 * (D + 4)
+    # time at the bars: 70 % of the tensor peak for the prefill rows plus 80 % of the HBM peak for the decode rows
+    bar_ms = 1e3 * (prefill_flops / (0.7 * pk["tflops"] * 1e12) + decode_bytes / (0.8 * pk["hbm_gbs"] * 1e9))
+    return {"workload": "cfg4", "ms_per_step": ms, "attention_ms": ams, "new_tokens": ntok,
+            "prefill_flops": prefill_flops, "decode_kv_bytes": decode_bytes, "kv_store_bytes": store_bytes,
+            "tokens_per_s": ntok / (ms * 1e-3), "bar_ms": bar_ms, "bar_over_measured": bar_ms / ams,
+            "launches_per_step": 5}
+
+
 def run_b2a(args):
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
@@ -327,8 +375,9 @@ def run_b2a(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     import openvino_contrib_b200  # noqa: F401  (fails loudly if libb2a.so is missing)
 
-    if args.only in ("cfg3", "cfg5"):  # a single decode workload, for profiler captures
-        r = bench_decode(args.only, args.steps, args.warmup, rank, world)
+    if args.only in ("cfg3", "cfg5", "cfg4"):  # a single paged workload, for profiler captures
+        r = (bench_mixed(args.steps, args.warmup, rank, world) if args.only == "cfg4"
+             else bench_decode(args.only, args.steps, args.warmup, rank, world))
         if rank == 0:
             print(json.dumps(r))
         return
@@ -337,6 +386,8 @@ def run_b2a(args):
     if args.only is None:
         for name in ("cfg3", "cfg5"):
             decode[name] = bench_decode(name, max(args.steps, 20), max(args.warmup, 3), rank, world)
+        if world == 1:
+            decode["cfg4"] = bench_mixed(max(args.steps, 20), max(args.warmup, 3), rank, world)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         _, _, cpu = cpu_prefill_sample(3, 1, budget_s=20.0)
@@ -369,7 +420,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b2a", choices=["b2a", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default=None, choices=["prefill", "cfg3", "cfg5"],
+    ap.add_argument("--only", default=None, choices=["prefill", "cfg3", "cfg5", "cfg4"],
                     help="run one workload only (profiler captures); the default runs all and prints the full line")
     args = ap.parse_args()
     if args.impl == "b2a" and args.only is None:

@@ -117,6 +117,11 @@ typedef struct b2a_paged_desc {
     int32_t max_context_len, max_q_len;
     float scale; /* 0 selects 1/sqrt(D) */
     int32_t sliding_window;
+    /* Optional: sum over the sequences with two or more new tokens of ceil(q_len / 128), as the scheduler that
+     * built the step knows it (b2a_kvmgr_last_prefill_row_blocks).  It only sizes the grid of the prefill kernel
+     * more tightly; 0 = unknown, the bound num_tokens/128 + num_seqs is used.  A value that is too small makes the
+     * kernel report B2A_DEV_BAD_LEN instead of computing a wrong answer. */
+    int32_t prefill_row_blocks;
 } b2a_paged_desc;
 
 /* Bytes of one (block, KV head) chunk of a cache of `kv_dtype` with head size d. */
@@ -178,6 +183,8 @@ int b2a_kvmgr_add_sequence(b2a_kvmgr* m, int64_t seq_id);
 int b2a_kvmgr_free_sequence(b2a_kvmgr* m, int64_t seq_id);
 int32_t b2a_kvmgr_free_blocks(const b2a_kvmgr* m);
 int32_t b2a_kvmgr_sequence_len(const b2a_kvmgr* m, int64_t seq_id); /* -1 if unknown */
+/* b2a_paged_desc.prefill_row_blocks of the step scheduled last */
+int32_t b2a_kvmgr_last_prefill_row_blocks(const b2a_kvmgr* m);
 /* Reserve blocks for q_lens[i] new tokens of seq_ids[i] (all or nothing), fill the step tables (host arrays:
  * past_lens[n], subsequence_begins[n+1], block_indices[capacity], block_indices_begins[n+1]) and advance
  * the sequences' lengths.  *num_block_indices and *max_context_len receive the totals. */

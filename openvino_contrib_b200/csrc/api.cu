@@ -159,7 +159,13 @@ int b2a_paged_workspace_bytes(const b2a_paged_desc* desc, int sm_count, size_t* 
     if (sm_count <= 0) sm_count = device_sm_count();
     if (sm_count <= 0) sm_count = 148;
     // pure decode steps and mixed steps both run the split-K decode kernel for their one-token sequences
-    *out_bytes = paged_decode_geometry_ok(d) ? paged_decode_plan(d, sm_count).workspace_bytes : 0;
+    // layout: [split-K partials of the decode kernel, rounded up to 16 bytes][work list of the prefill kernel]
+    size_t bytes = 0;
+    if (paged_decode_geometry_ok(d)) {
+        bytes = (paged_decode_plan(d, sm_count).workspace_bytes + 15) & ~static_cast<size_t>(15);
+        if (d.max_q_len >= 2) bytes += paged_tc_plan_bytes(d);
+    }
+    *out_bytes = bytes;
     return B2A_OK;
 }
 
@@ -207,9 +213,11 @@ int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const voi
         const int sms = device_sm_count();
         if (sms <= 0) return B2A_ERR_CUDA;
         const DecodePlan plan = paged_decode_plan(d, sms);
-        if (workspace == nullptr || workspace_bytes < plan.workspace_bytes) return B2A_ERR_WORKSPACE;
+        const size_t list_at = (plan.workspace_bytes + 15) & ~static_cast<size_t>(15);
+        if (workspace == nullptr || workspace_bytes < list_at + paged_tc_plan_bytes(d)) return B2A_ERR_WORKSPACE;
         if (!aligned(workspace, 16)) return B2A_ERR_ALIGN;
-        const int rc2 = paged_tc_launch(d, query, k_cache, v_cache, t, out, status, s);
+        const int rc2 = paged_tc_launch(d, query, k_cache, v_cache, t, out, static_cast<char*>(workspace) + list_at,
+                                        status, s);
         if (rc2 != B2A_OK) return rc2;
         return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, workspace, status, s);
     }

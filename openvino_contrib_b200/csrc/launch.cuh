@@ -47,8 +47,9 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
 // the same kernel body over a paged u8 cache: the multi-token sequences of a step (sequences with one new token are
 // left to the decode kernel, which in turn skips the others)
 bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* out);
+size_t paged_tc_plan_bytes(const b2a_paged_desc& d);  // scratch for the device-built work list
 int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
-                    const PagedTables& t, void* out, int32_t* status, cudaStream_t stream);
+                    const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream);
 
 int device_sm_count();
 

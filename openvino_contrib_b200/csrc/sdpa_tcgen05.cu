@@ -5,7 +5,8 @@
 //     staged by TMA;
 //   * paged  (PagedAttentionExtension, sequences with two or more new tokens): Q rows come from the step's
 //     [tokens, Hq*128] matrix, K/V from the u8 block pool through the block table - a producer warpgroup
-//     de-quantises 128-token tiles ((code - zp) * scale in f32, rounded to the query type) straight into the
+//     de-quantises 128-token tiles ((code - zp) * scale, f16: queries, keys, values and P are all f16 in this mode)
+//     straight into the
 //     swizzled shared-memory layout the tensor core reads.  Query token i of a sequence sees cache positions
 //     0 .. past_len + i.
 //
@@ -64,8 +65,38 @@ struct TcParams {
     const uint8_t* k_cache;
     const uint8_t* v_cache;
     PagedTables t;
-    void* out;  // [tokens, Hq*128]
+    void* out;        // [tokens, Hq*128]
+    const int* plan;  // work list built by paged_tc_plan_kernel: plan[0] = count, then (sequence, tile pair) entries
 };
+
+// Work list of the paged front end.  Lengths live on the device, so a one-CTA kernel turns them into the list of
+// (sequence, tile pair) items that have work; the attention grid is then sized by a host-side bound on the item
+// count (exact when the caller passes the scheduler's hint) instead of max_q_len x num_seqs, which for a step with
+// a few long prefills and many decode sequences would be almost all empty CTAs.
+constexpr int kPlanHeaderInts = 4;
+__global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t, const int G, const int capacity,
+                                                            int* plan, int32_t* status) {
+    __shared__ int s_count;
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    for (int s = threadIdx.x; s < t.num_seqs; s += blockDim.x) {
+        const int qlen = t.subsequence_begins[s + 1] - t.subsequence_begins[s];
+        if (qlen < 2) continue;
+        const int pairs = (((qlen + 127) / 128) * G + 1) / 2;
+        const int at = atomicAdd(&s_count, pairs);
+        for (int i = 0; i < pairs; ++i) {
+            if (at + i < capacity) {
+                plan[kPlanHeaderInts + 2 * (at + i)] = s;
+                plan[kPlanHeaderInts + 2 * (at + i) + 1] = pairs - 1 - i;  // late row blocks (most keys) first
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        plan[0] = min(s_count, capacity);
+        if (s_count > capacity) report(status, B2A_DEV_BAD_LEN);  // the caller's prefill_row_blocks was too small
+    }
+}
 
 __device__ __forceinline__ float ex2f(float x) {
     float y;
@@ -162,24 +193,26 @@ __device__ long long g_tc_trace[2048];
     } while (0)
 #endif
 
-// De-quantise the 16 codes of one 16-byte piece and store them as two 16-byte chunks of a swizzled tile row.
-template <bool kBf16>
-__device__ __forceinline__ void dequant_piece(uint4 w, float scale, float zp, uint8_t* row, int c16, int token) {
+// De-quantise the 16 codes of one 16-byte piece to f16 and store them as two 16-byte chunks of a swizzled tile row.
+// All in packed f16: 0x64XX is 1024 + XX, so a byte permute makes two halves at once; subtracting 1024 and then the
+// zero-point is exact (both differences are representable), the multiplication by the scale rounds once - the same
+// value as (code - zp) * scale computed in float32 and rounded to f16.  scale and zp arrive as the raw f16 bits the
+// cache stores.
+__device__ __forceinline__ void dequant_piece_f16(uint4 w, unsigned short scale_bits, unsigned short zp_bits,
+                                                  uint8_t* row, int c16, int token) {
     const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-    const uint64_t nz2 = f2_pack(-zp, -zp), sc2 = f2_pack(scale, scale), nm2 = f2_pack(-8388608.0f, -8388608.0f);
+    const __half2 sc2 = __half2half2(__ushort_as_half(scale_bits));
+    const __half2 zp2 = __half2half2(__ushort_as_half(zp_bits));
+    const uint32_t k1024_bits = 0x64006400u;
+    const __half2 k1024 = *reinterpret_cast<const __half2*>(&k1024_bits);
     uint32_t outw[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        // 0x4B0000xx is 2^23 + xx as float32: byte -> float without a convert instruction
-        const float b0 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7440));
-        const float b1 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7441));
-        const float b2 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7442));
-        const float b3 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7443));
-        float x0, x1, x2, x3;
-        f2_unpack(f2_mul(f2_add(f2_add(f2_pack(b0, b1), nm2), nz2), sc2), x0, x1);  // ((2^23 + q) - 2^23 - zp) * scale
-        f2_unpack(f2_mul(f2_add(f2_add(f2_pack(b2, b3), nm2), nz2), sc2), x2, x3);
-        outw[2 * i] = pack2<kBf16>(x0, x1);
-        outw[2 * i + 1] = pack2<kBf16>(x2, x3);
+        const uint32_t lo = __byte_perm(words[i], 0x64646464u, 0x4140), hi = __byte_perm(words[i], 0x64646464u, 0x4342);
+        const __half2 x01 = __hmul2(__hsub2(__hsub2(*reinterpret_cast<const __half2*>(&lo), k1024), zp2), sc2);
+        const __half2 x23 = __hmul2(__hsub2(__hsub2(*reinterpret_cast<const __half2*>(&hi), k1024), zp2), sc2);
+        outw[2 * i] = *reinterpret_cast<const uint32_t*>(&x01);
+        outw[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&x23);
     }
     // the piece covers d = 16*c16 .. +15: chunks 2*c16 and 2*c16+1 of the 128-wide row, 8 chunks per 64-wide panel
     uint8_t* panel = row + (c16 >> 2) * kPanel;
@@ -209,8 +242,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // key position the first row of the problem may see up to, `kv_limit` the number of keys that exist.
     int b = 0, hk, seq = 0, tok_base = 0, nrows_total, pos_base = 0, kv_limit;
     bool causal;
+    int pair_in_seq = 0;
     if constexpr (kPaged) {
-        seq = blockIdx.z;
+        if (static_cast<int>(blockIdx.x) >= p.plan[0]) return;  // the grid is a bound on the number of items
+        seq = p.plan[kPlanHeaderInts + 2 * blockIdx.x];
+        pair_in_seq = p.plan[kPlanHeaderInts + 2 * blockIdx.x + 1];
         hk = blockIdx.y;
         tok_base = p.t.subsequence_begins[seq];
         nrows_total = p.t.subsequence_begins[seq + 1] - tok_base;
@@ -221,7 +257,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int nblk = (kv_limit + 15) / 16;
         if (pos_base < 0 || tok_base < 0 || tok_base + nrows_total > p.t.num_tokens ||
             nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
-            if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, B2A_DEV_BAD_LEN);
+            if (threadIdx.x == 0) report(p.status, B2A_DEV_BAD_LEN);
             return;
         }
     } else {
@@ -234,8 +270,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int nrb = (nrows_total + kBM - 1) / kBM;
     const int tiles = nrb * p.G;
     const int pairs = (tiles + 1) / 2;
-    if (static_cast<int>(blockIdx.x) >= pairs) return;
-    const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // late row blocks (most keys) first
+    const int pair = kPaged ? pair_in_seq : pairs - 1 - static_cast<int>(blockIdx.x);  // late row blocks first
+    if (pair < 0 || pair >= pairs) return;
     int row0A, row0B, headA, headB, nkvA, nkvB;
     {
         auto tile_of = [&](int t, int& row0, int& head, int& nkv) {
@@ -273,14 +309,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tmem = *tmem_slot;
 
     // Registers follow the work: the service warpgroup keeps 56 per thread, the softmax groups take what is left
-    // (dense: 2*128*224 + 128*56 = 384*168; paged: 2*128*176 + 128*56 + 128*96 <= 512*128).
+    // (dense: 2*128*224 + 128*56 = 384*168; paged: 2*128*168 + 128*56 + 128*112 <= 512*128).
     if (warp >= 8 && warp < 12) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     }
     if (warp >= 12) {
         // =============================== de-quantising K/V producers (paged) ===============================
         if constexpr (kPaged) {
-            asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
             const int tp = static_cast<int>(threadIdx.x) - 384;
             const int tok_in_blk = tp >> 3, c16 = tp & 7;
             const int32_t* btab = p.t.block_indices + p.t.block_indices_begins[seq];
@@ -311,40 +347,67 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     }
                 }
             }
-            auto fill = [&](const uint8_t* cache, uint8_t* tile, int j) {
-#pragma unroll 2
+            // One tile = 8 logical blocks; per block the 128 threads cover 16 tokens x 8 sixteen-byte pieces, so a
+            // block's 2048 code bytes are read with fully coalesced 128-bit loads.  Everything a tile needs is
+            // requested before anything is converted (one memory latency per tile, not one per block), and the
+            // block ids of the next step are fetched while this step is converted.
+            int phys[8], phys_next[8];
+            auto load_ids = [&](int j, int (&ids)[8]) {
+#pragma unroll
                 for (int it = 0; it < 8; ++it) {
-                    const int lb = j * 8 + it;  // logical block: one block per pass, 128 threads = 16 tokens x 8 pieces
-                    const int token = it * 16 + tok_in_blk;
-                    const int pos = lb * 16 + tok_in_blk;
-                    uint4 w = make_uint4(0u, 0u, 0u, 0u);
-                    float sc = 0.f, zp = 0.f;
-                    if (lb < nblk && pos < kv_limit) {
-                        const int phys = btab[lb];
-                        if (phys < 0 || phys >= p.t.num_blocks_total) {
+                    const int lb = j * 8 + it;
+                    int id = -1;
+                    if (lb < nblk && lb * 16 + tok_in_blk < kv_limit) {
+                        id = btab[lb];
+                        if (id < 0 || id >= p.t.num_blocks_total) {
                             report(p.status, B2A_DEV_BAD_BLOCK);
-                        } else {
-                            const uint8_t* chunk = cache + (static_cast<size_t>(phys) * p.Hkv + hk) * kCacheChunk;
-                            w = *reinterpret_cast<const uint4*>(chunk + tok_in_blk * 128 + c16 * 16);
-                            const __half* meta = reinterpret_cast<const __half*>(chunk + 2048);
-                            sc = __half2float(meta[tok_in_blk]);
-                            zp = __half2float(meta[16 + tok_in_blk]);
+                            id = -1;
                         }
                     }
-                    // positions past the context (and unusable blocks) become exact zeros: 0 * anything finite
-                    dequant_piece<kKvBf16>(w, sc, zp, tile + token * 128, c16, token);
+                    ids[it] = id;
                 }
             };
+            uint4 w[8];
+            unsigned short sc[8], zp[8];  // raw f16 bits: converting here would wait for each load in turn
+            auto load_tile = [&](const uint8_t* cache) {
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    // positions past the context (and unusable blocks) become exact zeros: 0 * anything finite
+                    w[it] = make_uint4(0u, 0u, 0u, 0u);
+                    sc[it] = 0;
+                    zp[it] = 0;
+                    if (phys[it] >= 0) {
+                        const uint8_t* chunk = cache + (static_cast<size_t>(phys[it]) * p.Hkv + hk) * kCacheChunk;
+                        w[it] = *reinterpret_cast<const uint4*>(chunk + tok_in_blk * 128 + c16 * 16);
+                        const unsigned short* meta = reinterpret_cast<const unsigned short*>(chunk + 2048);
+                        sc[it] = meta[tok_in_blk];
+                        zp[it] = meta[16 + tok_in_blk];
+                    }
+                }
+            };
+            auto convert_tile = [&](uint8_t* tile) {
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int token = it * 16 + tok_in_blk;
+                    dequant_piece_f16(w[it], sc[it], zp[it], tile + token * 128, c16, token);
+                }
+            };
+            load_ids(0, phys_next);
             for (int j = 0; j < nmax; ++j) {
                 const int st = j & 1, n = j >> 1;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) phys[it] = phys_next[it];
+                load_tile(p.k_cache);
+                if (j + 1 < nmax) load_ids(j + 1, phys_next);
                 if (n > 0) ok = __all_sync(0xffffffffu, mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag));
                 if (!ok) break;
-                fill(p.k_cache, gbase + 2 * kTile + st * kTile, j);
+                convert_tile(gbase + 2 * kTile + st * kTile);
                 fence_proxy_async_smem();  // generic-proxy writes must be visible to the tensor core's reads
                 mbar_arrive(BAR(K_FULL + st));
+                load_tile(p.v_cache);
                 if (n > 0) ok = __all_sync(0xffffffffu, mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag));
                 if (!ok) break;
-                fill(p.v_cache, gbase + 4 * kTile + st * kTile, j);
+                convert_tile(gbase + 4 * kTile + st * kTile);
                 fence_proxy_async_smem();
                 mbar_arrive(BAR(V_FULL + st));
             }
@@ -473,7 +536,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     } else {
         // =============================== softmax + epilogue of tile X ===============================
         if constexpr (kPaged) {
-            asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+            asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
         } else {
             asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         }
@@ -763,9 +826,25 @@ bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* 
            d.Hkv <= 65535 && al(query) && al(out) && encode_fn() != nullptr;
 }
 
+// upper bound on the (sequence, tile pair) items of a step
+static int paged_tc_capacity(const b2a_paged_desc& d) {
+    const long long g = d.Hq / d.Hkv;
+    const long long rb = d.prefill_row_blocks > 0 ? d.prefill_row_blocks
+                                                  : static_cast<long long>(d.num_tokens) / 128 + d.num_seqs;
+    const long long cap = (rb * g + 1) / 2 + (rb < d.num_seqs ? rb : d.num_seqs);  // + one round-up per sequence
+    return static_cast<int>(cap < 1 ? 1 : cap);
+}
+
+size_t paged_tc_plan_bytes(const b2a_paged_desc& d) {
+    return sizeof(int) * (kPlanHeaderInts + 2 * static_cast<size_t>(paged_tc_capacity(d)));
+}
+
 int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
-                    const PagedTables& t, void* out, int32_t* status, cudaStream_t stream) {
+                    const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream) {
     const bool bf16 = d.q_dtype == B2A_BF16;
+    const int capacity = paged_tc_capacity(d);
+    paged_tc_plan_kernel<<<1, 256, 0, stream>>>(t, d.Hq / d.Hkv, capacity, static_cast<int*>(plan_ws), status);
+    if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
     // the step's query matrix [tokens, Hq*128] as a [1, Hq, tokens, 128] view
     const int64_t qs[4] = {static_cast<int64_t>(d.num_tokens) * d.Hq * kHeadDim, kHeadDim,
                            static_cast<int64_t>(d.Hq) * kHeadDim, 1};
@@ -780,9 +859,8 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     p.v_cache = static_cast<const uint8_t*>(v_cache);
     p.t = t;
     p.out = out;
-    const int nrb = (d.max_q_len + kBM - 1) / kBM;
-    const int pairs = (nrb * p.G + 1) / 2;
-    dim3 grid(pairs, d.Hkv, d.num_seqs);
+    p.plan = static_cast<const int*>(plan_ws);
+    dim3 grid(capacity, d.Hkv, 1);
     static bool configured[2][64] = {};
     auto kern = bf16 ? attn_tc_kernel<true, true> : attn_tc_kernel<false, true>;
     const int rc = configure_once(kern, configured[bf16]);

@@ -152,9 +152,11 @@ size_t PagedAttentionOp::WorkspaceBound() const {
     size_t worst = 16;
     for (int n = 1; n <= max_seqs_; ++n) {
         b2a_paged_desc d = desc_;
-        d.num_seqs = d.num_tokens = n;
+        d.num_seqs = n;
+        // a mixed step: the decode partials for n sequences plus the prefill work list for the token capacity
+        d.num_tokens = max_context_len_ + max_seqs_;
         d.max_context_len = max_context_len_;
-        d.max_q_len = 1;
+        d.max_q_len = 2;
         size_t bytes = 0;
         throwIfError(b2a_paged_workspace_bytes(&d, 0, &bytes), "b2a_paged_workspace_bytes");
         worst = std::max(worst, bytes);
@@ -180,6 +182,8 @@ void PagedAttentionOp::Execute(const InferenceRequestContext& context, Inputs in
     if (auto s = dyn.getShape(input_ids_.at(5).GetId())) d.num_seqs = static_cast<int>(s->at(0));
     if (d.num_tokens <= 0 || d.num_seqs <= 0) return;  // an empty step
     if (d.num_seqs > max_seqs_) ov::throw_ov_exception("PagedAttentionExtension: more sequences than the capacity");
+    if (d.num_tokens > max_context_len_ + max_seqs_)
+        ov::throw_ov_exception("PagedAttentionExtension: more tokens in one step than the capacity");
     d.max_context_len = max_context_len_;
     d.max_q_len = d.num_tokens == d.num_seqs ? 1 : d.num_tokens - d.num_seqs + 1;
     if (wb.mutable_buffers.size() < 2) ov::throw_ov_exception("PagedAttentionExtension: work buffers missing");

@@ -88,8 +88,10 @@ int KvBlockManager::schedule_step(const int64_t* ids, const int32_t* q_lens, int
         out.block_indices_begins[static_cast<size_t>(i) + 1] = static_cast<int32_t>(out.block_indices.size());
         out.max_context_len = std::max(out.max_context_len, new_len);
         out.max_q_len = std::max(out.max_q_len, q_lens[i]);
+        if (q_lens[i] >= 2) out.prefill_row_blocks += (q_lens[i] + 127) / 128;
     }
     out.num_tokens = out.subsequence_begins[static_cast<size_t>(n)];
+    last_prefill_row_blocks_ = out.prefill_row_blocks;
     return B2A_OK;
 }
 
@@ -125,6 +127,8 @@ int b2a_kvmgr_free_sequence(b2a_kvmgr* m, int64_t seq_id) {
 int32_t b2a_kvmgr_free_blocks(const b2a_kvmgr* m) { return m ? m->impl.free_blocks() : -1; }
 
 int32_t b2a_kvmgr_sequence_len(const b2a_kvmgr* m, int64_t seq_id) { return m ? m->impl.sequence_len(seq_id) : -1; }
+
+int32_t b2a_kvmgr_last_prefill_row_blocks(const b2a_kvmgr* m) { return m ? m->impl.last_prefill_row_blocks() : 0; }
 
 int b2a_kvmgr_schedule_step(b2a_kvmgr* m, const int64_t* seq_ids, const int32_t* q_lens, int32_t n,
                             int32_t* past_lens, int32_t* subsequence_begins, int32_t* block_indices,

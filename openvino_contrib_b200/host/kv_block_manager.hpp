@@ -19,6 +19,7 @@ struct StepTables {
     std::vector<int32_t> block_indices_begins;  // [n+1]
     int32_t max_context_len = 0;
     int32_t max_q_len = 0;
+    int32_t prefill_row_blocks = 0;  // sum of ceil(q_len / 128) over the sequences with two or more new tokens
     int32_t num_tokens = 0;
 };
 
@@ -34,6 +35,7 @@ public:
     bool add_sequence(int64_t id);   // false if it exists
     bool free_sequence(int64_t id);  // false if unknown; its blocks return to the free list
     int32_t sequence_len(int64_t id) const;  // -1 if unknown
+    int32_t last_prefill_row_blocks() const { return last_prefill_row_blocks_; }  // of the last scheduled step
     const std::vector<int32_t>* sequence_blocks(int64_t id) const;
 
     // Blocks that scheduling q_lens[i] new tokens for ids[i] would take from the free list; -1 if an id is unknown
@@ -50,6 +52,7 @@ private:
         int32_t len = 0;
     };
     int32_t num_blocks_, block_size_;
+    int32_t last_prefill_row_blocks_ = 0;
     std::vector<int32_t> free_;  // stack: back() is handed out next
     std::unordered_map<int64_t, Seq> seqs_;
 };

@@ -188,7 +188,7 @@ class PagedKvCache:
 
 
 def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int, max_context_len: int,
-                max_q_len: int, scale: Optional[float], sliding_window: int) -> PagedDesc:
+                max_q_len: int, scale: Optional[float], sliding_window: int, prefill_row_blocks: int = 0) -> PagedDesc:
     d = PagedDesc()
     d.q_dtype = _dtype_code(q_dtype)
     d.kv_dtype = _dtype_code(cache.kv_dtype)
@@ -197,6 +197,7 @@ def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens
     d.max_context_len, d.max_q_len = max_context_len, max_q_len
     d.scale = 0.0 if scale is None else float(scale)
     d.sliding_window = int(sliding_window)
+    d.prefill_row_blocks = int(prefill_row_blocks)
     return d
 
 
@@ -224,8 +225,9 @@ def paged_kv_store(key: torch.Tensor, value: torch.Tensor, cache: PagedKvCache, 
 
 
 def paged_workspace_bytes(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int,
-                          max_context_len: int, max_q_len: int) -> int:
-    d = _paged_desc(q_dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, None, 0)
+                          max_context_len: int, max_q_len: int, prefill_row_blocks: int = 0) -> int:
+    d = _paged_desc(q_dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, None, 0,
+                    prefill_row_blocks)
     ws = C.c_size_t(0)
     check(_lib.load().b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
     return ws.value
@@ -235,15 +237,18 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
                     block_indices_begins, hq: int, max_context_len: int, max_q_len: int,
                     scale: Optional[float] = None, sliding_window: int = 0, out: Optional[torch.Tensor] = None,
                     workspace: Optional[torch.Tensor] = None, stream=None,
-                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention of query [tokens, Hq*D] over the cache; returns [tokens, Hq*Dv]."""
+                    status: Optional[torch.Tensor] = None, prefill_row_blocks: int = 0) -> torch.Tensor:
+    """Attention of query [tokens, Hq*D] over the cache; returns [tokens, Hq*Dv].
+
+    ``prefill_row_blocks`` is the optional scheduler hint of ``b2a_paged_desc`` (``KvBlockManager`` reports it)."""
     _require_cuda(query, cache.k, cache.v, past_lens, subsequence_begins, block_indices, block_indices_begins, out)
     if not query.is_contiguous() or query.shape[1] != hq * cache.d:
         raise ValueError("query must be dense [tokens, Hq*D]")
     num_tokens, num_seqs = query.shape[0], past_lens.shape[0]
     if out is None:
         out = torch.empty((num_tokens, hq * cache.dv), dtype=query.dtype, device=query.device)
-    d = _paged_desc(query.dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, scale, sliding_window)
+    d = _paged_desc(query.dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, scale, sliding_window,
+                    prefill_row_blocks)
     lib = _lib.load()
     ws = C.c_size_t(0)
     check(lib.b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
@@ -336,6 +341,11 @@ class KvBlockManager:
 
     def sequence_len(self, seq_id: int) -> int:
         return self._lib.b2a_kvmgr_sequence_len(self._h, seq_id)
+
+    @property
+    def last_prefill_row_blocks(self) -> int:
+        """``prefill_row_blocks`` hint of the step scheduled last."""
+        return self._lib.b2a_kvmgr_last_prefill_row_blocks(self._h)
 
     def schedule_step(self, seq_ids: Sequence[int], q_lens: Sequence[int]):
         """Reserve blocks for the new tokens and return the step tables as numpy int32 arrays:
