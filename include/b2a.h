@@ -170,6 +170,35 @@ int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, c
                                 int32_t* status, b2a_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Head-sharded decode over the GPUs of one node (one process per GPU).
+ *
+ * No counterpart in the reference, which never spans devices (one independent plugin configuration per device
+ * id, src/cuda_plugin.cpp:25-32).  Rank r of `world` owns KV heads [r*Hkv/world, (r+1)*Hkv/world) and their query
+ * heads; K/V never cross NVLink.  The per-head outputs are exchanged by the merge kernel itself: it stores this
+ * rank's columns into a staging buffer on EVERY rank (peer stores over NVLink) and publishes a step flag; a
+ * second kernel waits, bounded, for all ranks and copies the full-width rows to `out_full`.
+ *
+ * Set-up (allocates; not for the hot path): every rank creates its group, the 64-byte handles of all ranks are
+ * exchanged by any host-side means (torch.distributed all_gather, MPI, a file), in rank order, and passed to
+ * _connect.  staging_bytes >= num_tokens * Hq_total * D * 2 of the largest step.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct b2a_shard_group b2a_shard_group;
+int b2a_shard_group_create(int rank, int world, size_t staging_bytes, b2a_shard_group** out);
+int b2a_shard_group_handle(const b2a_shard_group* g, unsigned char handle[64]);
+int b2a_shard_group_connect(b2a_shard_group* g, const unsigned char* handles /* world * 64 bytes, rank order */);
+void b2a_shard_group_destroy(b2a_shard_group* g);
+/* Decode step on this rank's heads (`local_desc` carries the LOCAL Hq and Hkv; query [num_tokens, Hq_local*D];
+ * caches hold the local KV heads), output exchanged as above: out_full [num_tokens, Hq_local*world*D] is complete
+ * on every rank when the stream reaches the end of the call's work.  Decode shapes only (as
+ * b2a_paged_attention_noalloc); workspace as b2a_paged_workspace_bytes(local_desc).  All ranks must call it the
+ * same number of times; a rank that never arrives makes the others report B2A_DEV_TIMEOUT after about a second. */
+int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_desc, const void* query,
+                                const void* k_cache, const void* v_cache, const int32_t* past_lens,
+                                const int32_t* subsequence_begins, const int32_t* block_indices,
+                                const int32_t* block_indices_begins, void* out_full, void* workspace,
+                                size_t workspace_bytes, int32_t* status, b2a_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * KV block manager (host only; no CUDA calls).  Owns the free list of a pool of `num_blocks` physical
  * blocks and the per-sequence block lists, and emits the four int32 tables of a step.  It takes the place
  * CudaVariableState has for the contiguous cache (src/cuda_variable_state.hpp:31-183: reset / grow / hand

@@ -25,7 +25,7 @@ NVCC_FLAGS = [
 ]
 
 CU_SOURCES = ["csrc/api.cu", "csrc/attn_generic.cu", "csrc/paged_kv_store.cu", "csrc/paged_decode.cu",
-              "csrc/sdpa_tcgen05.cu"]
+              "csrc/sdpa_tcgen05.cu", "csrc/shard_group.cu"]
 CXX_SOURCES = ["host/kv_block_manager.cpp"]
 
 

@@ -18,6 +18,23 @@ int paged_generic_launch(const b2a_paged_desc& d, const void* query, const void*
 int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* value, void* k_cache, void* v_cache,
                           const PagedTables& t, int32_t* status, cudaStream_t stream);
 
+// Head-sharded decode across the GPUs of a node: where the merge kernel sends a rank's output columns.
+// Every rank owns two full-width staging buffers (alternating by step), an array of per-source-rank flags and two
+// counters, all inside one allocation that its peers map through CUDA IPC.  The merge kernel of rank r stores its
+// columns into the staging buffer of EVERY rank (plain peer stores over NVLink), and its last CTA publishes the
+// step number in every rank's flags[r]; a second kernel on each rank waits (bounded) until all flags show the
+// step and copies the completed rows to the caller's output.  No collective library call is on the path.
+constexpr int kMaxShardWorld = 8;
+struct PeerPush {
+    void* staging[kMaxShardWorld][2];  // [rank][step parity]: that rank's staging buffers as mapped here
+    int32_t* flags[kMaxShardWorld];    // [rank]: that rank's flags array (one int per source rank)
+    int32_t* step_counter;             // local: number of steps published so far
+    int32_t* done_counter;             // local: merge CTAs finished in the current step (self-resetting)
+    int rank, world;                   // world == 0: not sharded
+    int row_elems;                     // elements of one full-width output row (Hq_total * D)
+    int col_offset;                    // first column of this rank's heads
+};
+
 // paged_decode.cu — split-K decode over a u8 cache (D = Dv = 128, block 16, one query token per sequence)
 struct DecodePlan {
     int blocks_per_cta;  // logical KV blocks one CTA walks
@@ -29,7 +46,7 @@ bool paged_decode_geometry_ok(const b2a_paged_desc& d); // the kernel's shape li
 DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count);
 int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
                         const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
-                        cudaStream_t stream);
+                        cudaStream_t stream, const PeerPush* push = nullptr);
 
 // Same launch with the split-K partials in the library's built-in device array instead of a caller workspace.
 int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query,

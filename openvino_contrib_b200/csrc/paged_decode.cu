@@ -45,6 +45,7 @@ struct DecodeParams {
     int sliding_window;
     float scale_log2;  // softmax scale * log2(e)
     int32_t* status;
+    PeerPush push;     // world == 0 unless the heads are sharded over several GPUs
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -298,12 +299,16 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeP
             corr_b[nt] = corr_b[nt] * alpha_b + h2_hi(x0) * zv0 + h2_hi(x1) * zv1;
             pb0[nt] = movmatrix_trans(x0);  // (P'[head gid][token 2*tid4], P'[head gid][token 2*tid4+1])
             pb1[nt] = movmatrix_trans(x1);  // tokens 2*tid4+8, +9
+            // the accumulators only need rescaling when some row maximum of the warp moved, which after the first
+            // few blocks of a context is rare: skip the 32 multiplications otherwise (warp-uniform branch)
+            if (__any_sync(0xffffffffu, alpha_a != 1.f || alpha_b != 1.f)) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                acc[nt][j][0] *= alpha_a;
-                acc[nt][j][1] *= alpha_b;
-                acc[nt][j][2] *= alpha_a;
-                acc[nt][j][3] *= alpha_b;
+                for (int j = 0; j < 8; ++j) {
+                    acc[nt][j][0] *= alpha_a;
+                    acc[nt][j][1] *= alpha_b;
+                    acc[nt][j][2] *= alpha_a;
+                    acc[nt][j][3] *= alpha_b;
+                }
             }
         }
 
@@ -389,31 +394,89 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeP
     }
 }
 
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // Merge the split partials of one (sequence, query head): out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
+// With sharded heads the row segment goes to every rank's staging buffer instead, and the last CTA of the grid
+// publishes the step (see PeerPush).
 template <typename T>
 __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodeParams p) {
     const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const bool pushing = p.push.world > 0;
+    const int parity = pushing ? ((*reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1) & 1) : 0;
     const int tok = p.t.subsequence_begins[seq];
     const int qlen = p.t.subsequence_begins[seq + 1] - tok;
-    if (qlen != 1) return;
     const int past = p.t.past_lens[seq];
-    if (past < 0) return;
     const int ctx = past + 1;
     const int nblk = (ctx + kBS - 1) / kBS;
-    if (nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) return;
-    const int blk_lo = first_block_of(ctx, p.sliding_window);
-    const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
-    const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
-    float mc = kNegBig;
-    for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, p.ws_ml[(base + s) * 2]);
-    float o = 0.f, l = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float f = ex2(p.ws_ml[(base + s) * 2] - mc);
-        o += p.ws_o[(base + s) * kD + d] * f;
-        l += p.ws_ml[(base + s) * 2 + 1] * f;
+    const bool valid = qlen == 1 && past >= 0 &&
+                       nblk <= p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq];
+    if (valid) {
+        const int blk_lo = first_block_of(ctx, p.sliding_window);
+        const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
+        const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
+        float mc = kNegBig;
+        for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, p.ws_ml[(base + s) * 2]);
+        float o = 0.f, l = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float f = ex2(p.ws_ml[(base + s) * 2] - mc);
+            o += p.ws_o[(base + s) * kD + d] * f;
+            l += p.ws_ml[(base + s) * 2 + 1] * f;
+        }
+        const T val = from_f32<T>(l > 0.f ? o / l : 0.f);
+        if (!pushing) {
+            T* orow = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD;
+            orow[d] = val;
+        } else {
+            const size_t at = static_cast<size_t>(tok) * p.push.row_elems + p.push.col_offset + h * kD + d;
+            for (int r = 0; r < p.push.world; ++r) reinterpret_cast<T*>(p.push.staging[r][parity])[at] = val;
+        }
     }
-    T* orow = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD;
-    orow[d] = from_f32<T>(l > 0.f ? o / l : 0.f);
+    if (pushing) {
+        __threadfence_system();  // this CTA's peer stores are ordered before its arrival below
+        __syncthreads();
+        if (d == 0) {
+            const int total = static_cast<int>(gridDim.x * gridDim.y);
+            if (atomicAdd(p.push.done_counter, 1) == total - 1) {
+                *p.push.done_counter = 0;  // every CTA has arrived: ready for the next step
+                const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
+                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;
+                __threadfence_system();
+                for (int r = 0; r < p.push.world; ++r) st_release_sys(p.push.flags[r] + p.push.rank, epoch);
+            }
+        }
+    }
+}
+
+// Second half of the exchange: wait until every rank has published the current step, then copy this rank's staging
+// rows to the caller's output.  One CTA per row; the wait is bounded (about a second) and reports
+// B2A_DEV_TIMEOUT instead of hanging when a peer never arrives.
+__global__ void __launch_bounds__(256) peer_wait_copy_kernel(const PeerPush push, void* out, int row_bytes,
+                                                              int32_t* status) {
+    const int32_t epoch = *reinterpret_cast<volatile int32_t*>(push.step_counter);  // published by our own merge
+    const int parity = epoch & 1;
+    if (static_cast<int>(threadIdx.x) < push.world) {
+        const int32_t* flag = push.flags[push.rank] + threadIdx.x;
+        const long long t0 = clock64();
+        while (ld_acquire_sys(flag) - epoch < 0) {
+            if (clock64() - t0 > (1LL << 31)) {
+                report(status, B2A_DEV_TIMEOUT);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(push.staging[push.rank][parity]) +
+                                                      static_cast<size_t>(blockIdx.x) * row_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(out) + static_cast<size_t>(blockIdx.x) * row_bytes);
+    for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = src[i];
 }
 
 template <typename T, int NT>
@@ -431,6 +494,12 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
     kern<<<grid, kWarps * 32, kSmemBytes, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
     paged_decode_merge_kernel<T><<<dim3(p.Hq, num_seqs), kD, 0, stream>>>(p);
+    if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+    if (p.push.world > 0) {
+        // decode steps carry one token per sequence: row index == sequence index == token index
+        peer_wait_copy_kernel<<<num_seqs, 256, 0, stream>>>(p.push, p.out, p.push.row_elems * static_cast<int>(sizeof(T)),
+                                                            p.status);
+    }
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 
@@ -466,8 +535,9 @@ DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count) {
 
 int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
                         const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const PeerPush* push) {
     DecodeParams p{};
+    if (push != nullptr) p.push = *push;
     p.query = query;
     p.k_cache = static_cast<const uint8_t*>(k_cache);
     p.v_cache = static_cast<const uint8_t*>(v_cache);

@@ -73,11 +73,27 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
     }
 
     uint8_t* chunk = cache + (static_cast<size_t>(blk) * p.Hkv + hk) * u8_chunk_bytes(bs, D);
+    uint8_t* row = chunk + slot * D;
+    // D == 128 with 16-bit inputs: each lane keeps its 4 consecutive values in registers (one 8-byte load, one
+    // 4-byte store); other sizes take the strided loops below.  Same arithmetic either way.
+    const bool vec = (D == 128) && sizeof(T) == 2 && ((reinterpret_cast<uintptr_t>(src) & 7) == 0);
+    float xv[4];
     float mn = INFINITY, mx = -INFINITY;
-    for (int d = lane; d < D; d += 32) {
-        const float x = to_f32<T>(src[d]);
-        mn = fminf(mn, x);
-        mx = fmaxf(mx, x);
+    if (vec) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(src) + 4 * lane);
+        const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            xv[i] = to_f32<T>(h[i]);
+            mn = fminf(mn, xv[i]);
+            mx = fmaxf(mx, xv[i]);
+        }
+    } else {
+        for (int d = lane; d < D; d += 32) {
+            const float x = to_f32<T>(src[d]);
+            mn = fminf(mn, x);
+            mx = fmaxf(mx, x);
+        }
     }
     mx = warp_max(mx);
     mn = -warp_max(-mn);
@@ -89,11 +105,20 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
     }
     const __half z16 = __float2half_rn(__fdiv_rn(-mn, sf));
     const float zf = __half2float(z16);
-    uint8_t* row = chunk + slot * D;
-    for (int d = lane; d < D; d += 32) {
-        const float x = to_f32<T>(src[d]);
-        const float t = rintf(__fadd_rn(__fdiv_rn(x, sf), zf));
-        row[d] = static_cast<uint8_t>(fminf(fmaxf(t, 0.f), 255.f));
+    if (vec) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float t = rintf(__fadd_rn(__fdiv_rn(xv[i], sf), zf));
+            packed |= static_cast<uint32_t>(fminf(fmaxf(t, 0.f), 255.f)) << (8 * i);
+        }
+        reinterpret_cast<uint32_t*>(row)[lane] = packed;
+    } else {
+        for (int d = lane; d < D; d += 32) {
+            const float x = to_f32<T>(src[d]);
+            const float t = rintf(__fadd_rn(__fdiv_rn(x, sf), zf));
+            row[d] = static_cast<uint8_t>(fminf(fmaxf(t, 0.f), 255.f));
+        }
     }
     if (lane == 0) {
         __half* meta = reinterpret_cast<__half*>(chunk + bs * D);

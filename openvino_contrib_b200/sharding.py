@@ -98,3 +98,58 @@ def sharded_sdpa(q, k, v, shard: HeadShard, attend: Callable, group=None, **kw) 
     """
     o = attend(shard.take_q(q).contiguous(), shard.take_kv(k).contiguous(), shard.take_kv(v).contiguous(), **kw)
     return gather_heads_bhsd(o, shard, group)
+
+
+class ShardGroup:
+    """Python face of ``b2a_shard_group``: staging buffers on every rank, mapped into every process with CUDA IPC.
+
+    The 64-byte handles travel through ``torch.distributed`` (any backend) at set-up; after that a decode step
+    involves no collective call: ``paged_attention`` enqueues the split-K decode of the local heads, a merge
+    kernel that stores this rank's output columns on every rank and a kernel that waits for all ranks and fills
+    ``out_full``.
+    """
+
+    def __init__(self, shard: HeadShard, staging_bytes: int, group=None):
+        import ctypes as C
+
+        from . import _lib
+        self._C, self._lib, self.shard = C, _lib.load(), shard
+        self._h = C.c_void_p()
+        _lib.check(self._lib.b2a_shard_group_create(shard.rank, shard.world, staging_bytes, C.byref(self._h)),
+                   "b2a_shard_group_create")
+        buf = C.create_string_buffer(64)
+        _lib.check(self._lib.b2a_shard_group_handle(self._h, buf), "b2a_shard_group_handle")
+        handles = [None] * shard.world
+        if shard.world > 1:
+            dist.all_gather_object(handles, bytes(buf.raw), group=group)
+        else:
+            handles[0] = bytes(buf.raw)
+        _lib.check(self._lib.b2a_shard_group_connect(self._h, b"".join(handles)), "b2a_shard_group_connect")
+        if shard.world > 1:
+            dist.barrier(group=group)  # every rank has mapped every peer before anyone pushes
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.b2a_shard_group_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def paged_attention(self, query_local, cache_local, past_lens, subsequence_begins, block_indices,
+                        block_indices_begins, max_context_len: int, out_full: torch.Tensor, workspace: torch.Tensor,
+                        scale: Optional[float] = None, status: Optional[torch.Tensor] = None, stream=None):
+        """One decode step on this rank's heads; ``out_full`` [tokens, Hq*D] is complete on every rank afterwards."""
+        from . import _lib
+        from .ops import _paged_desc, _ptr, _stream_ptr
+        C = self._C
+        n = query_local.shape[0]
+        d = _paged_desc(query_local.dtype, cache_local, self.shard.hq_local, past_lens.shape[0], n, max_context_len,
+                        1, scale, 0)
+        _lib.check(self._lib.b2a_paged_attention_sharded(
+            self._h, C.byref(d), query_local.data_ptr(), cache_local.k.data_ptr(), cache_local.v.data_ptr(),
+            past_lens.data_ptr(), subsequence_begins.data_ptr(), block_indices.data_ptr(),
+            block_indices_begins.data_ptr(), out_full.data_ptr(), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _ptr(status), _stream_ptr(stream)),
+            "b2a_paged_attention_sharded")
+        return out_full

@@ -1,0 +1,68 @@
+"""Head-sharded decode on N GPUs (one process per GPU): the peer-store exchange against the oracle and against
+the NCCL all-gather of the same shards.  Launch:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        tests/multi_gpu/sharded_decode.py
+
+Every rank builds the same full problem from one seed, keeps its KV heads, runs three steps (the exchange
+alternates two staging buffers, so odd and even steps are both exercised) and checks the full-width output.
+NVLS is not needed and left off.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
+
+def main():
+    rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import openvino_contrib_b200 as b2a
+    from openvino_contrib_b200.sharding import HeadShard, ShardGroup, gather_heads_rows
+    from tests.helpers import PagedWorkload, assert_close
+
+    hq, hkv, d = 64, 8, 128
+    ctx = [37, 1000, 2049, 16, 513, 4096]
+    w = PagedWorkload(ctx, [1] * len(ctx), hq, hkv, d, seed=77)
+    shard = HeadShard(rank, world, hq, hkv)
+    n = len(ctx)
+    # this rank's slice of the pools: [blocks, Hkv, chunk] -> local KV heads
+    kc = torch.from_numpy(w.k_cache[:, shard.kv_heads].copy()).cuda()
+    vc = torch.from_numpy(w.v_cache[:, shard.kv_heads].copy()).cuda()
+    cache = b2a.PagedKvCache(kc, vc, shard.hkv_local, d, d, 16, torch.uint8)
+    tables = w.device_tables()
+    group = ShardGroup(shard, staging_bytes=n * hq * d * 2)
+    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, shard.hq_local, n, n, max(ctx), 1)),
+                     dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for step in range(3):
+        q_full = torch.from_numpy(w.query * (1.0 + 0.25 * step)).to(torch.float16)
+        ref = w.reference(q_full.float().numpy())
+        q_local = shard.take_q_rows(q_full, d).contiguous().cuda()
+        out = torch.zeros(n, hq * d, dtype=torch.float16, device="cuda")
+        group.paged_attention(q_local, cache, *tables, max_context_len=max(ctx), out_full=out, workspace=ws,
+                              status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, f"rank {rank} step {step}: status {int(status.item())}"
+        assert_close(out, ref, torch.float16, f"rank {rank} step {step}")
+        # and bit-identical to the NCCL path over the same shards
+        o_local = b2a.paged_attention(q_local, cache, *tables, hq=shard.hq_local, max_context_len=max(ctx),
+                                      max_q_len=1, workspace=ws)
+        o_nccl = gather_heads_rows(o_local, shard, d)
+        assert torch.equal(o_nccl, out), f"rank {rank} step {step}: differs from the NCCL gather"
+    dist.barrier()
+    group.close()
+    if rank == 0:
+        print(f"sharded decode ok on {world} GPUs")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
