@@ -298,23 +298,40 @@ def bench_decode(name, steps, warmup, rank, world):
     out = torch.empty(n, hq_l * D, dtype=torch.float16, device="cuda")
     ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, hq_l, n, n, maxc, 1)),
                      dtype=torch.uint8, device="cuda")
-    from openvino_contrib_b200.sharding import HeadShard, gather_heads_rows
+    from openvino_contrib_b200.sharding import HeadShard, ShardGroup, gather_heads_rows
     shard = HeadShard(rank, world, Hq, Hkv)
     gathered = torch.empty(world * n, hq_l * D, dtype=torch.float16, device="cuda") if world > 1 else None
+    exchange = "none"
+    group = None
+    if world > 1:
+        exchange = os.environ.get("B2A_BENCH_EXCHANGE", "peer")  # "peer": stores into every rank's memory; "nccl"
+        if exchange == "peer":
+            try:
+                group = ShardGroup(shard, staging_bytes=n * Hq * D * 2)
+            except Exception as e:  # CUDA IPC not available in this container: fall back to the library collective
+                exchange = f"nccl (peer mapping failed: {type(e).__name__})"
+    out_full = torch.empty(n, Hq * D, dtype=torch.float16, device="cuda") if group is not None else None
 
     def step():
+        if group is not None:
+            group.paged_attention(q, cache, past, sb, bi, bb, max_context_len=maxc, out_full=out_full, workspace=ws)
+            return
         b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1, out=out,
                             workspace=ws)
         if world > 1:
             gather_heads_rows(out, shard, D, buffer=gathered)
     ms, _, _ = timed(step, steps, warmup, world)
+    if group is not None:
+        torch.cuda.synchronize()
+        group.close()
     tokens = int(ctx.sum())
     kv_bytes = tokens * Hkv * 2 * (D + 4)  # whole job: all ranks' heads
     pk = peaks()
     gbs = kv_bytes / (ms * 1e-3) / 1e9
     return {"workload": name, "kv_gbs": gbs, "ms_per_step": ms, "kv_bytes_per_step": kv_bytes,
             "frac_of_hbm_peak": gbs / (pk["hbm_gbs"] * world), "peak_gbs_per_gpu": pk["hbm_gbs"],
-            "peak_source": pk["source"], "cached_tokens": tokens, "launches_per_step": 2}
+            "peak_source": pk["source"], "cached_tokens": tokens, "launches_per_step": 3 if group is not None else 2,
+            "output_exchange": exchange}
 
 
 def bench_mixed(steps, warmup, rank, world):

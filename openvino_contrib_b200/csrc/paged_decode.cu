@@ -7,11 +7,11 @@
 // (m16n8k16, f16 in, f32 accumulate) with the u8 codes fed in UNSCALED:
 //     S[t][g]  = scale_k[t] * ( sum_d code_k[t][d] * Q[g][d]  -  zp_k[t] * sum_d Q[g][d] )
 //     O[g][d]  = sum_t P'[g][t] * code_v[t][d]  -  sum_t P'[g][t] * zp_v[t],      P'[g][t] = p[g][t] * scale_v[t]
-// Codes 0..255 are exact in f16, products are exact, accumulation is f32: no de-quantisation rounding at all on
-// the K side, one f16 rounding of P' on the V side.
+// Codes 0..255 (and code + 1024, which is what the byte permute produces for free) are exact in f16, products are
+// exact, accumulation is f32: the only roundings are the f32 accumulation itself and one f16 rounding of P'.
 //
 // Grid = (split, KV head, sequence); a CTA of 4 warps walks `blocks_per_cta` logical blocks of one sequence and KV
-// head, warp w taking blocks w, w+4, ...  Each warp runs its own 4-stage cp.async pipeline: a stage holds the K chunk
+// head, warp w taking blocks w, w+4, ...  Each warp runs its own 3-stage cp.async pipeline: a stage holds the K chunk
 // and the V chunk of one block (2 x 2112 bytes), copied as 16-byte pieces, 512 contiguous bytes per warp
 // instruction, into shared memory with an XOR swizzle of the 16-byte column so that the MMA fragments are read
 // with conflict-free 128-bit loads.  Online softmax per warp (row max by warp shuffle), partials of the 4 warps
@@ -28,7 +28,7 @@ constexpr int kBS = 16;
 constexpr int kChunk = kBS * (kD + 4);   // 2112 bytes: 2048 codes, 16 f16 scales, 16 f16 zero-points
 constexpr int kStage = 2 * kChunk;       // K chunk then V chunk
 constexpr int kWarps = 4;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kSmemBytes = kWarps * kStages * kStage;
 constexpr float kNegBig = -1.0e30f;      // finite "minus infinity" for the running max (keeps exp2 arguments NaN-free)
 
@@ -83,22 +83,12 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
-// 0x64XX as f16 is 1024 + XX: insert the byte under the exponent pattern, subtract 1024 — exact for 0..255.
-__device__ __forceinline__ uint32_t sub1024(uint32_t h2bits) {
-    const __half2 v = *reinterpret_cast<const __half2*>(&h2bits);
-    const uint32_t kbits = 0x64006400u;
-    const __half2 r = __hsub2(v, *reinterpret_cast<const __half2*>(&kbits));
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-// half2(float(byte 2*pair), float(byte 2*pair+1)) of one word
+// 0x64XX as f16 is 1024 + XX exactly: the MMAs are fed code + 1024 (one byte permute per register, no subtraction)
+// and the 1024 joins the zero-point, which is subtracted after the contraction anyway.
+constexpr float kCodeBias = 1024.f;
 template <int PAIR>
-__device__ __forceinline__ uint32_t bytes_to_h2(uint32_t w) {
-    return sub1024(__byte_perm(w, 0x64646464u, PAIR == 0 ? 0x4140 : 0x4342));
-}
-// half2(float(byte e of w0), float(byte e of w1))
-__device__ __forceinline__ uint32_t bytepair_to_h2(uint32_t w0, uint32_t w1, int e) {
-    const uint32_t r = __byte_perm(w0, w1, ((4 + e) << 8) | e);
-    return sub1024((r & 0x00FF00FFu) | 0x64006400u);
+__device__ __forceinline__ uint32_t bytes_to_h2(uint32_t w) {  // (1024 + byte 2*PAIR, 1024 + byte 2*PAIR+1)
+    return __byte_perm(w, 0x64646464u, PAIR == 0 ? 0x4140 : 0x4342);
 }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
@@ -124,7 +114,7 @@ __device__ __forceinline__ int first_block_of(int ctx, int sliding_window) {
 }
 
 template <typename T, int NT>
-__global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -266,12 +256,12 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeP
         // per-token scale / zero-point (forced to 0 for tokens outside the context: unused slots may hold anything)
         const float sk0 = ok0 ? lds_h(sK + 2048 + 2 * gid) * p.scale_log2 : 0.f;
         const float sk1 = ok1 ? lds_h(sK + 2048 + 2 * (gid + 8)) * p.scale_log2 : 0.f;
-        const float zk0 = ok0 ? lds_h(sK + 2048 + 32 + 2 * gid) : 0.f;
-        const float zk1 = ok1 ? lds_h(sK + 2048 + 32 + 2 * (gid + 8)) : 0.f;
+        const float zk0 = ok0 ? lds_h(sK + 2048 + 32 + 2 * gid) + kCodeBias : 0.f;
+        const float zk1 = ok1 ? lds_h(sK + 2048 + 32 + 2 * (gid + 8)) + kCodeBias : 0.f;
         const float sv0 = ok0 ? lds_h(sV + 2048 + 2 * gid) : 0.f;
         const float sv1 = ok1 ? lds_h(sV + 2048 + 2 * (gid + 8)) : 0.f;
-        const float zv0 = ok0 ? lds_h(sV + 2048 + 32 + 2 * gid) : 0.f;
-        const float zv1 = ok1 ? lds_h(sV + 2048 + 32 + 2 * (gid + 8)) : 0.f;
+        const float zv0 = ok0 ? lds_h(sV + 2048 + 32 + 2 * gid) + kCodeBias : 0.f;
+        const float zv1 = ok1 ? lds_h(sV + 2048 + 32 + 2 * (gid + 8)) + kCodeBias : 0.f;
 
         uint32_t pb0[NT], pb1[NT];
 #pragma unroll
@@ -313,23 +303,28 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeP
         }
 
         // ---- O^T += codes_V^T . P'^T  (rows = d, columns = heads, contraction over the 16 tokens)
+        // ldmatrix.trans over byte PAIRS: an 8x8 "b16" matrix is 8 tokens x one 16-byte chunk; transposed, this lane
+        // gets (token 2*tid4, token 2*tid4+1) x bytes (2*gid, 2*gid+1) of the chunk in one register, which is the
+        // token pairing the A fragment wants.  M-tile j is chunk j: row gid <-> d = 16j+2gid, row gid+8 <-> d+1.
         {
-            const int t0 = 2 * tid4;
-            const uint4 v0 = lds128(sV + t0 * 128 + ((gid ^ (t0 & 7)) << 4));
-            const uint4 v1 = lds128(sV + (t0 + 1) * 128 + ((gid ^ ((t0 + 1) & 7)) << 4));
-            const uint4 v2 = lds128(sV + (t0 + 8) * 128 + ((gid ^ (t0 & 7)) << 4));
-            const uint4 v3 = lds128(sV + (t0 + 9) * 128 + ((gid ^ ((t0 + 1) & 7)) << 4));
-            const uint32_t w0[4] = {v0.x, v0.y, v0.z, v0.w}, w1[4] = {v1.x, v1.y, v1.z, v1.w};
-            const uint32_t w2[4] = {v2.x, v2.y, v2.z, v2.w}, w3[4] = {v3.x, v3.y, v3.z, v3.w};
+            const int mrow = lane & 7, mh = (lane >> 3) & 1, mc = lane >> 4;  // row, token half and chunk of "my" matrix row
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int w = j >> 1, e = (j & 1) * 2;
-                const uint32_t a0 = bytepair_to_h2(w0[w], w1[w], e);      // d = gid*16+2j,   tokens t0, t0+1
-                const uint32_t a1 = bytepair_to_h2(w0[w], w1[w], e + 1);  // d = gid*16+2j+1
-                const uint32_t a2 = bytepair_to_h2(w2[w], w3[w], e);      // tokens t0+8, t0+9
-                const uint32_t a3 = bytepair_to_h2(w2[w], w3[w], e + 1);
+            for (int q = 0; q < 4; ++q) {
+                uint32_t r0, r1, r2, r3;  // (tokens 0-7, chunk 2q), (8-15, 2q), (0-7, 2q+1), (8-15, 2q+1)
+                const uint32_t addr = sV + (8 * mh + mrow) * 128 + (((2 * q + mc) ^ mrow) << 4);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                             : "r"(addr));
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) mma16816(acc[nt][j], a0, a1, a2, a3, pb0[nt], pb1[nt]);
+                for (int jj = 0; jj < 2; ++jj) {
+                    const uint32_t lo = jj ? r2 : r0, hi = jj ? r3 : r1;
+                    const uint32_t a0 = __byte_perm(lo, 0x64646464u, 0x4240);  // d,   tokens t0, t0+1
+                    const uint32_t a1 = __byte_perm(lo, 0x64646464u, 0x4341);  // d+1
+                    const uint32_t a2 = __byte_perm(hi, 0x64646464u, 0x4240);  // tokens t0+8, t0+9
+                    const uint32_t a3 = __byte_perm(hi, 0x64646464u, 0x4341);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma16816(acc[nt][2 * q + jj], a0, a1, a2, a3, pb0[nt], pb1[nt]);
+                }
             }
         }
         __syncwarp();  // every lane is done with this stage before it is refilled
@@ -352,7 +347,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(const DecodeP
         const int ga = nt * 8 + 2 * tid4, gb = ga + 1;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const int d = gid * 16 + 2 * j;
+            const int d = 16 * j + 2 * gid;
             *reinterpret_cast<float2*>(wbuf + ga * kD + d) =
                 make_float2(acc[nt][j][0] - corr_a[nt], acc[nt][j][2] - corr_a[nt]);
             *reinterpret_cast<float2*>(wbuf + gb * kD + d) =
@@ -516,11 +511,12 @@ bool paged_decode_supported(const b2a_paged_desc& d) {
 }
 
 DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count) {
-    // Aim at ~4 CTAs per resident slot (3 CTAs fit per SM) so that the tail of the last wave is short, while a
-    // CTA still walks at least 16 blocks (4 per warp) to amortise its prologue and the merge.
+    // Long chunks win (a CTA's pipeline start and its merge are paid once per chunk), so a CTA walks up to 128
+    // blocks - 32 per warp, the size of a warp's block-id window.  Only when the whole step is smaller than one
+    // wave of 4 CTAs per SM are the chunks shortened, so that every SM still has work.
     const long long nblk_max = (static_cast<long long>(d.max_context_len) + kBS - 1) / kBS;
     const long long total = nblk_max * d.Hkv * d.num_seqs;
-    const long long target_ctas = static_cast<long long>(sm_count) * 3 * 4;
+    const long long target_ctas = static_cast<long long>(sm_count) * 4;
     long long bpc = (total + target_ctas - 1) / target_ctas;
     bpc = ((bpc + 3) / 4) * 4;
     if (bpc < 16) bpc = 16;
