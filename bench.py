@@ -18,7 +18,6 @@ import argparse
 import json
 import math
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -31,6 +30,12 @@ sys.path.insert(0, ROOT)
 
 PREFILL = dict(B=4, Hq=32, Hkv=8, S=4096, D=128)
 
+# dram__bytes (read + write) per launch from the profiler captures summarised under profiles/ (bytes)
+NCU_TRAFFIC = {
+    "prefill": 307.5e6,   # attn_tc_kernel<bf16, dense>, full workload: profiles/attn_tc_kernel_prefill_cfg2.md
+    "cfg3": 628.7e6,      # paged_decode_kernel<f16, 1>: profiles/paged_decode_kernel_cfg3.md
+}
+
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -42,58 +47,54 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event reasons of one GPU through NVML (read-only queries) on a thread, every
+    couple of milliseconds, while the timed region runs."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
-    def __init__(self, index: int):
-        self.rows, self.proc = [], None
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.rows, self.handle, self.stop_flag, self.period = [], None, False, period_s
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception as e:  # no NVML: the line says so instead of inventing clocks
+            self.handle, self.error = None, f"NVML unavailable: {type(e).__name__}"
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.time(), line.strip()))
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.rows.append((time.time(), float(mhz), int(mask)))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def stop(self, t0: float, t1: float):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.06)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        mhz, mx, reasons = [], None, set()
-        for ts, line in self.rows:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 7:
-                continue
-            try:
-                mx = float(f[1])
-                if t0 - 0.05 <= ts <= t1 + 0.05:
-                    mhz.append(float(f[0]))
-                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
-                        if v.lower().startswith("active"):
-                            reasons.add(name)
-            except ValueError:
-                continue
-        if not mhz:  # region shorter than the sampling period: take the nearest samples
-            for ts, line in self.rows[-3:]:
-                try:
-                    mhz.append(float(line.split(",")[0]))
-                except ValueError:
-                    pass
-        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+        if self.handle is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error]}
+        self.stop_flag = True
+        self.thread.join(timeout=1.0)
+        inside = [r for r in self.rows if t0 <= r[0] <= t1]
+        near = inside or self.rows[-3:]
+        reasons = sorted({name for _, _, m in near for name, bit in self.REASONS if m & bit})
+        mhz = [r[1] for r in near]
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(inside)}
 
 
 def dist_env():
@@ -230,7 +231,8 @@ def bench_prefill(args, rank, world, local):
     pk = peaks()
     achieved = causal_flops(B, hq_l, S, D) / (kms * 1e-3) / 1e12
     roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-            "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"] + " burst bf16 GEMM",
+            "frac": achieved / pk["tflops"],
+            "traffic": NCU_TRAFFIC["prefill"] / world if world == 1 else None, "peak_source": pk["source"] + " burst bf16 GEMM",
             "kernel_ms": kms}
 
     # end to end through the public API with host buffers: H2D of q,k,v, kernel, D2H of the output
@@ -330,7 +332,8 @@ def bench_decode(name, steps, warmup, rank, world):
     gbs = kv_bytes / (ms * 1e-3) / 1e9
     return {"workload": name, "kv_gbs": gbs, "ms_per_step": ms, "kv_bytes_per_step": kv_bytes,
             "frac_of_hbm_peak": gbs / (pk["hbm_gbs"] * world), "peak_gbs_per_gpu": pk["hbm_gbs"],
-            "peak_source": pk["source"], "cached_tokens": tokens, "launches_per_step": 3 if group is not None else 2,
+            "peak_source": pk["source"], "cached_tokens": tokens,
+            "traffic": NCU_TRAFFIC.get(name) if world == 1 else None, "launches_per_step": 3 if group is not None else 2,
             "output_exchange": exchange}
 
 
@@ -433,7 +436,7 @@ def run_b2a(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b2a", choices=["b2a", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
