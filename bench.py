@@ -208,14 +208,26 @@ def bench_prefill(args, rank, world, local):
     out = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16, device="cuda")
     from openvino_contrib_b200.sharding import HeadShard, gather_heads_bhsd, gather_heads_rows  # noqa: F401
     shard = HeadShard(rank, world, Hq, Hkv)
-    gathered = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    exchange, group = "none", None
+    if world > 1:
+        exchange = os.environ.get("B2A_BENCH_EXCHANGE", "peer")  # "peer": the kernel's epilogue stores to every rank
+        if exchange == "peer":
+            try:
+                from openvino_contrib_b200.sharding import ShardGroup
+                group = ShardGroup(shard, staging_bytes=B * Hq * S * D * 2)
+            except Exception as e:  # CUDA IPC not available: the library collective instead
+                exchange = f"nccl (peer mapping failed: {type(e).__name__})"
+    gathered = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 and group is None else None
     launches = [0]
 
     def step():
-        b2a.sdpa(q, k, v, causal=True, out=out)
         launches[0] += 1
+        if group is not None:
+            return group.sdpa(q, k, v, causal=True)
+        b2a.sdpa(q, k, v, causal=True, out=out)
         if world > 1:
             gather_heads_bhsd(out, shard, buffer=gathered)
+        return out
 
     sampler = ClockSampler(local)
     ms, t0, t1 = timed(step, args.steps, args.warmup, world)
@@ -240,15 +252,23 @@ def bench_prefill(args, rank, world, local):
 
     def e2e_step():
         qd, kd, vd = q_h.cuda(non_blocking=True), k_h.cuda(non_blocking=True), v_h.cuda(non_blocking=True)
-        o = b2a.sdpa(qd, kd, vd, causal=True)
-        if world > 1:
-            gather_heads_bhsd(o, shard, buffer=gathered)
+        if group is not None:
+            o = group.sdpa(qd, kd, vd, causal=True)[:, sl_q]
+        else:
+            o = b2a.sdpa(qd, kd, vd, causal=True)
+            if world > 1:
+                gather_heads_bhsd(o, shard, buffer=gathered)
         out_h.copy_(o, non_blocking=True)
     ems, _, _ = timed(e2e_step, max(3, args.steps // 2), 2, world)
     h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
     e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": out_h.numel() * 2, "ms_per_step": ems}
-    return dict(ms=ms, value=value, roofline=roof, e2e=e2e, clocks=clocks, launches=n_launch)
+    if group is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        group.close()
+    return dict(ms=ms, value=value, roofline=roof, e2e=e2e, clocks=clocks, launches=n_launch * (2 if group else 1),
+                exchange=exchange)
 
 
 def build_decode_problem(n_seqs, ctx_lens, Hq, Hkv, D, seed, device="cuda"):
@@ -420,8 +440,8 @@ def run_b2a(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"prefill_llama3_8b: B={B} Hq={Hq} Hkv={Hkv} S={S} D={D} causal, scale=1/sqrt(128), "
                                    f"Q,K,V ~ N(0,1)*0.5 seed 1",
-                       "sharding": f"KV heads over {world} GPU(s), NCCL all-gather of outputs in the step" if world > 1
-                       else "single GPU",
+                       "sharding": f"KV heads over {world} GPU(s), outputs exchanged inside the step: {pre['exchange']}"
+                       if world > 1 else "single GPU",
                        "l2": "inputs + outputs (335 MB) exceed the 126 MB L2; no flush between steps"},
             "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["launches"],
             "clocks": pre["clocks"], "decode": decode,

@@ -197,6 +197,18 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
                                 const int32_t* subsequence_begins, const int32_t* block_indices,
                                 const int32_t* block_indices_begins, void* out_full, void* workspace,
                                 size_t workspace_bytes, int32_t* status, b2a_stream_t stream);
+/* Prefill SDPA on this rank's heads (`local_desc` carries the LOCAL Hq and Hkv and the strides of the local q, k, v;
+ * o_strides and the mask fields are ignored: no mask operand, dense output).  The tensor-core kernel's epilogue
+ * stores every finished output tile into the full-width buffer of EVERY rank (one TMA store per rank, so the
+ * exchange overlaps the rest of the grid's computation), then the stream waits, bounded, for the other ranks.
+ * *out_full points at this rank's complete [B, Hq_local*world, Sq, Dv] result inside the group's memory (the two
+ * halves of the staging area alternate by step): it is valid once the stream has passed the call's work, and stays
+ * so for work enqueued before the next call on this group.  Shapes: what the tensor-core kernel takes (f16/bf16,
+ * D = Dv = 128, 16-byte aligned strides), else B2A_ERR_UNSUPPORTED; staging_bytes >= the full output.  A group
+ * serves either decode steps or prefill steps (the first call decides), and a sharded prefill call is not
+ * capturable in a CUDA graph (the buffer alternation is host state).  No counterpart in the reference. */
+int b2a_sdpa_forward_sharded(b2a_shard_group* g, const b2a_sdpa_desc* local_desc, const void* q, const void* k,
+                             const void* v, void** out_full, int32_t* status, b2a_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * KV block manager (host only; no CUDA calls).  Owns the free list of a pool of `num_blocks` physical

@@ -55,6 +55,8 @@ SIGNATURES = {
     "b2a_paged_attention_sharded": (C.c_int, [C.c_void_p, C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_size_t, C.c_void_p, C.c_void_p]),
+    "b2a_sdpa_forward_sharded": (C.c_int, [C.c_void_p, C.POINTER(SdpaDesc), C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p]),
     "b2a_kvmgr_create": (C.c_int, [C.c_int32, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p)]),
     "b2a_kvmgr_destroy": (None, [C.c_void_p]),
     "b2a_kvmgr_add_sequence": (C.c_int, [C.c_void_p, C.c_int64]),

@@ -57,9 +57,24 @@ int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePla
 bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4],
                        const int64_t (&vs)[4], const int64_t (&os)[4], const void* q, const void* k, const void* v,
                        const void* o);
+// Head-sharded prefill: where the kernel's epilogue sends its output tiles.  Every rank owns a full-width
+// [B, Hq_total, Sq, 128] output buffer that its peers map; a CTA stores each finished 32-row slab into the buffer of
+// EVERY rank with one TMA store per rank (the all-gather happens tile by tile while other CTAs still compute), the
+// last CTA of the grid publishes `step` in every rank's flags[rank], and sdpa_peer_wait_launch makes the stream wait
+// (bounded) until all ranks have published.
+struct TcPeerOut {
+    void* out_base[kMaxShardWorld];    // [rank]: that rank's output buffer of this step, as mapped here
+    int32_t* flags[kMaxShardWorld];    // [rank]: that rank's flag array (one int per source rank)
+    int32_t* done_counter;             // local: CTAs finished in the current step (self-resetting)
+    int rank, world;
+    int hq_total;                      // heads of the full output
+    int head_offset;                   // first head of this rank
+    int32_t step;                      // value published when the step is complete (increases by one per step)
+};
 int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
                    const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
-                   cudaStream_t stream);
+                   cudaStream_t stream, const TcPeerOut* peers = nullptr);
+int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, int32_t* status, cudaStream_t stream);
 
 // the same kernel body over a paged u8 cache: the multi-token sequences of a step (sequences with one new token are
 // left to the decode kernel, which in turn skips the others)

@@ -69,6 +69,15 @@ struct TcParams {
     const int* plan;  // work list built by paged_tc_plan_kernel: plan[0] = count, then (sequence, tile pair) entries
 };
 
+// Output side of a head-sharded launch (world == 0: single GPU, the tmO map is the output).
+struct TcPeers {
+    CUtensorMap out[kMaxShardWorld];  // [rank]: that rank's [B, Hq_total, Sq, 128] output buffer
+    int32_t* flags[kMaxShardWorld];
+    int32_t* done_counter;
+    int world, rank, head_offset;
+    int32_t step;
+};
+
 // Work list of the paged front end.  Lengths live on the device, so a one-CTA kernel turns them into the list of
 // (sequence, tile pair) items that have work; the attention grid is then sized by a host-side bound on the item
 // count (exact when the caller passes the scheduler's hint) instead of max_q_len x num_seqs, which for a step with
@@ -224,7 +233,8 @@ __device__ __forceinline__ void dequant_piece_f16(uint4 w, unsigned short scale_
 template <bool kBf16, bool kPaged>
 __global__ void __launch_bounds__(kPaged ? kThreadsPaged : kThreadsDense, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p) {
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p,
+               const __grid_constant__ TcPeers peers) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte swizzle atoms want 1024-byte aligned tiles
@@ -704,10 +714,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) {
                         const int w = warp & 3;
-                        tma_store_4d(&tmO, sQ + X * kTile + w * 32 * 128, 0, row0 + 32 * w, head, b);
-                        tma_store_4d(&tmO, sQ + X * kTile + kPanel + w * 32 * 128, 64, row0 + 32 * w, head, b);
+                        const uint32_t src = sQ + X * kTile + w * 32 * 128;
+                        if (peers.world == 0) {
+                            tma_store_4d(&tmO, src, 0, row0 + 32 * w, head, b);
+                            tma_store_4d(&tmO, src + kPanel, 64, row0 + 32 * w, head, b);
+                        } else {
+                            // the same slab into every rank's buffer, the next rank first so that the ranks do
+                            // not all write to the same peer at the same time; local copy last
+                            for (int i = 1; i <= peers.world; ++i) {
+                                const int dst = (peers.rank + i) % peers.world;
+                                tma_store_4d(&peers.out[dst], src, 0, row0 + 32 * w, peers.head_offset + head, b);
+                                tma_store_4d(&peers.out[dst], src + kPanel, 64, row0 + 32 * w, peers.head_offset + head, b);
+                            }
+                        }
                         tma_store_commit();
-                        tma_store_wait_all();
+                        tma_store_wait_all();  // completion of the writes, not only of the reads of shared memory
                     }
                 }
             }
@@ -721,6 +742,40 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tmem_dealloc(tmem, 512);
     }
     if (threadIdx.x == 0 && *abort_flag) report(p.status, B2A_DEV_TIMEOUT);
+    if constexpr (!kPaged) {
+        if (peers.world > 0 && threadIdx.x == 0) {
+            // every storing lane has waited for its writes and passed the barrier above: order them before the
+            // arrival, and let the last CTA of the grid publish the step to every rank
+            __threadfence_system();
+            const int total = static_cast<int>(gridDim.x * gridDim.y);
+            if (atomicAdd(peers.done_counter, 1) == total - 1) {
+                *peers.done_counter = 0;
+                __threadfence_system();
+                for (int r = 0; r < peers.world; ++r)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peers.flags[r] + peers.rank), "r"(peers.step)
+                                 : "memory");
+            }
+        }
+    }
+}
+
+// Stream-ordered wait for the other ranks of a head-sharded prefill step: returns when every flag shows `step`.
+// Bounded (about a second): a peer that never arrives turns into B2A_DEV_TIMEOUT in the status word.
+__global__ void __launch_bounds__(32) sdpa_peer_wait_kernel(const int32_t* flags, const int world, const int32_t step,
+                                                            int32_t* status) {
+    if (static_cast<int>(threadIdx.x) < world) {
+        const int32_t* flag = flags + threadIdx.x;
+        const long long t0 = clock64();
+        for (;;) {
+            int32_t v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v - step >= 0) break;
+            if (clock64() - t0 > (1LL << 31)) {
+                report(status, B2A_DEV_TIMEOUT);
+                break;
+            }
+        }
+    }
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------
@@ -796,12 +851,30 @@ bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int
 
 int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
                    const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const TcPeerOut* peer_out) {
     const bool bf16 = d.dtype == B2A_BF16;
     CUtensorMap mq, mk, mv, mo;
     if (!make_map(&mq, q, bf16, d.B, d.Hq, d.Sq, qs, 128) || !make_map(&mk, k, bf16, d.B, d.Hkv, d.Skv, ks, 128) ||
-        !make_map(&mv, v, bf16, d.B, d.Hkv, d.Skv, vs, 128) || !make_map(&mo, o, bf16, d.B, d.Hq, d.Sq, os, 32))
+        !make_map(&mv, v, bf16, d.B, d.Hkv, d.Skv, vs, 128))
         return B2A_ERR_CUDA;
+    TcPeers peers{};
+    if (peer_out == nullptr) {
+        if (!make_map(&mo, o, bf16, d.B, d.Hq, d.Sq, os, 32)) return B2A_ERR_CUDA;
+    } else {
+        mo = mq;  // not read
+        const int64_t fs[4] = {static_cast<int64_t>(peer_out->hq_total) * d.Sq * kHeadDim,
+                               static_cast<int64_t>(d.Sq) * kHeadDim, kHeadDim, 1};
+        for (int r = 0; r < peer_out->world; ++r) {
+            if (!make_map(&peers.out[r], peer_out->out_base[r], bf16, d.B, peer_out->hq_total, d.Sq, fs, 32))
+                return B2A_ERR_CUDA;
+            peers.flags[r] = peer_out->flags[r];
+        }
+        peers.done_counter = peer_out->done_counter;
+        peers.world = peer_out->world;
+        peers.rank = peer_out->rank;
+        peers.head_offset = peer_out->head_offset;
+        peers.step = peer_out->step;
+    }
     TcParams p{};
     p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.G = d.Hq / d.Hkv; p.Sq = d.Sq; p.Skv = d.Skv;
     p.causal = d.causal;
@@ -814,7 +887,12 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     auto kern = bf16 ? attn_tc_kernel<true, false> : attn_tc_kernel<false, false>;
     const int rc = configure_once(kern, configured[bf16]);
     if (rc != B2A_OK) return rc;
-    kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mo, p);
+    kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mo, p, peers);
+    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+}
+
+int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, int32_t* status, cudaStream_t stream) {
+    sdpa_peer_wait_kernel<<<1, 32, 0, stream>>>(local_flags, world, step, status);
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 
@@ -865,7 +943,8 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     auto kern = bf16 ? attn_tc_kernel<true, true> : attn_tc_kernel<false, true>;
     const int rc = configure_once(kern, configured[bf16]);
     if (rc != B2A_OK) return rc;
-    kern<<<grid, kThreadsPaged, kSmemBytes, stream>>>(mq, mq, mq, mq, p);  // only the Q map is read in paged mode
+    TcPeers peers{};
+    kern<<<grid, kThreadsPaged, kSmemBytes, stream>>>(mq, mq, mq, mq, p, peers);  // only the Q map is read in paged mode
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 

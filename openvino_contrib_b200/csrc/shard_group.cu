@@ -5,16 +5,21 @@
 // merge kernel stores the rank's output columns into every rank's staging buffer over NVLink and publishes the step
 // in every rank's flags; peer_wait_copy_kernel then waits (bounded) for all ranks and copies the full-width rows to
 // the caller's output (see PeerPush in launch.cuh, kernels in paged_decode.cu).
+// b2a_sdpa_forward_sharded does the same for prefill: the tensor-core kernel's epilogue stores each output tile into
+// every rank's buffer (TcPeerOut in launch.cuh), and the result is read in place.
 // The reference never spans devices (one independent plugin configuration per device id,
 // modules/nvidia_plugin/src/cuda_plugin.cpp:25-32), so nothing here has a counterpart there.
+#include <cmath>
 #include <cstring>
 #include <new>
 
 #include "launch.cuh"
 
 namespace {
-constexpr size_t kFlagsBytes = 256;     // kMaxShardWorld ints, padded
-constexpr size_t kCountersBytes = 256;  // step counter at +0, done counter at +64
+constexpr size_t kFlagsBytes = 256;     // decode: ints 0..7; prefill: ints 16..23
+constexpr size_t kCountersBytes = 256;  // decode step counter at +0, decode done counter at +64, prefill done counter at +128
+constexpr int kPrefillFlagOffset = 16;
+enum { kModeUnset = 0, kModeDecode = 1, kModePrefill = 2 };
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 }  // namespace
 
@@ -23,6 +28,8 @@ struct b2a_shard_group {
     size_t staging_bytes = 0;  // one staging buffer
     char* base[b2a::kMaxShardWorld] = {};  // [rank]: that rank's allocation as mapped in this process
     bool connected = false;
+    int mode = kModeUnset;       // a group serves one kind of step: the two kinds alternate the staging halves differently
+    int32_t prefill_step = 0;    // host-side count of prefill steps
     size_t total_bytes() const { return 2 * staging_bytes + kFlagsBytes + kCountersBytes; }
 };
 
@@ -97,6 +104,7 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
         return B2A_ERR_NULL;
     if (d.Hq <= 0 || d.Hkv <= 0 || d.Hq % d.Hkv != 0 || d.num_seqs > 65535 || d.max_context_len <= 0) return B2A_ERR_DIM;
     if (!paged_decode_supported(d)) return B2A_ERR_UNSUPPORTED;  // decode steps only
+    if (g->mode == kModePrefill) return B2A_ERR_UNSUPPORTED;
     const size_t row_bytes = static_cast<size_t>(d.Hq) * g->world * d.D * 2;
     if (static_cast<size_t>(d.num_tokens) * row_bytes > g->staging_bytes) return B2A_ERR_CAPACITY;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -120,8 +128,62 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
     push.col_offset = g->rank * d.Hq * d.D;
     const PagedTables t{past_lens, subsequence_begins, block_indices, block_indices_begins,
                         d.num_seqs, d.num_tokens, d.num_blocks_total, d.block_size};
+    g->mode = kModeDecode;
     return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out_full, workspace, status,
                                reinterpret_cast<cudaStream_t>(stream), &push);
+}
+
+int b2a_sdpa_forward_sharded(b2a_shard_group* g, const b2a_sdpa_desc* local_desc, const void* q, const void* k,
+                             const void* v, void** out_full, int32_t* status, b2a_stream_t stream) {
+    using namespace b2a;
+    if (g == nullptr || local_desc == nullptr || out_full == nullptr) return B2A_ERR_NULL;
+    if (!g->connected || g->mode == kModeDecode) return B2A_ERR_UNSUPPORTED;
+    b2a_sdpa_desc d = *local_desc;
+    if (d.dtype != B2A_F16 && d.dtype != B2A_BF16) return B2A_ERR_UNSUPPORTED;
+    if (d.B <= 0 || d.Hq <= 0 || d.Hkv <= 0 || d.Sq <= 0 || d.Skv <= 0 || d.Hq % d.Hkv != 0) return B2A_ERR_DIM;
+    if (d.B > 65535 || static_cast<long long>(d.Hq) * g->world > 65535) return B2A_ERR_DIM;
+    if (d.mask_kind != B2A_MASK_NONE) return B2A_ERR_UNSUPPORTED;
+    if (q == nullptr || k == nullptr || v == nullptr) return B2A_ERR_NULL;
+    if (!(d.scale >= 0.f) || std::isinf(d.scale)) return B2A_ERR_DIM;
+    if (d.scale == 0.f) d.scale = 1.0f / sqrtf(static_cast<float>(d.D));
+    auto fill = [](int64_t (&s)[4], int64_t h, int64_t n, int64_t e) {
+        if (s[0] == 0 && s[1] == 0 && s[2] == 0 && s[3] == 0) { s[3] = 1; s[2] = e; s[1] = n * e; s[0] = h * n * e; }
+    };
+    int64_t qs[4], ks[4], vs[4], os[4] = {0, 0, 0, 0};
+    std::memcpy(qs, d.q_strides, sizeof qs);
+    std::memcpy(ks, d.k_strides, sizeof ks);
+    std::memcpy(vs, d.v_strides, sizeof vs);
+    fill(qs, d.Hq, d.Sq, d.D);
+    fill(ks, d.Hkv, d.Skv, d.D);
+    fill(vs, d.Hkv, d.Skv, d.Dv);
+    const int hq_total = d.Hq * g->world;
+    fill(os, hq_total, d.Sq, d.Dv);
+    const size_t out_bytes = static_cast<size_t>(d.B) * hq_total * d.Sq * d.Dv * 2;
+    if (out_bytes > g->staging_bytes) return B2A_ERR_CAPACITY;
+    const int32_t step = g->prefill_step + 1;
+    const size_t half = static_cast<size_t>(step & 1) * g->staging_bytes;
+    void* mine = g->base[g->rank] + half;
+    if (!sdpa_tc_supported(d, qs, ks, vs, os, q, k, v, mine)) return B2A_ERR_UNSUPPORTED;
+    TcPeerOut po{};
+    for (int r = 0; r < g->world; ++r) {
+        po.out_base[r] = g->base[r] + half;
+        po.flags[r] = reinterpret_cast<int32_t*>(g->base[r] + 2 * g->staging_bytes) + kPrefillFlagOffset;
+    }
+    po.done_counter = reinterpret_cast<int32_t*>(g->base[g->rank] + 2 * g->staging_bytes + kFlagsBytes + 128);
+    po.rank = g->rank;
+    po.world = g->world;
+    po.hq_total = hq_total;
+    po.head_offset = g->rank * d.Hq;
+    po.step = step;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    int rc = sdpa_tc_launch(d, qs, ks, vs, os, q, k, v, mine, status, s, &po);
+    if (rc != B2A_OK) return rc;
+    g->mode = kModePrefill;
+    g->prefill_step = step;
+    rc = sdpa_peer_wait_launch(po.flags[g->rank], g->world, step, status, s);
+    if (rc != B2A_OK) return rc;
+    *out_full = mine;
+    return B2A_OK;
 }
 
 }  // extern "C"

@@ -153,3 +153,48 @@ class ShardGroup:
             workspace.numel() * workspace.element_size(), _ptr(status), _stream_ptr(stream)),
             "b2a_paged_attention_sharded")
         return out_full
+
+    def sdpa(self, q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor, causal: bool = False,
+             scale: Optional[float] = None, status: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """Prefill SDPA on this rank's heads (q [B, Hq_local, S, 128], k/v [B, Hkv_local, S, 128], f16/bf16).
+
+        Returns the complete [B, Hq, S, 128] result of all ranks as a view of the group's own memory: every rank's
+        kernel stores its output tiles into every rank's buffer while it computes.  The view alternates between
+        two buffers from call to call: use it (on the same stream) before the next call on this group.
+        """
+        from . import _lib
+        from .ops import _dtype_code, _ptr, _stream_ptr
+        C = self._C
+        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+        q4, k4, v4 = fix(q_local), fix(k_local), fix(v_local)
+        B, Hq, Sq, D = q4.shape
+        d = _lib.SdpaDesc()
+        d.dtype = _dtype_code(q4.dtype)
+        d.B, d.Hq, d.Hkv, d.Sq, d.Skv, d.D, d.Dv = B, Hq, k4.shape[1], Sq, k4.shape[2], D, v4.shape[-1]
+        d.causal = int(bool(causal))
+        d.scale = 0.0 if scale is None else float(scale)
+        d.q_strides[:] = q4.stride()
+        d.k_strides[:] = k4.stride()
+        d.v_strides[:] = v4.stride()
+        d.mask_kind = _lib.MASK_NONE
+        out = C.c_void_p()
+        _lib.check(self._lib.b2a_sdpa_forward_sharded(self._h, C.byref(d), q4.data_ptr(), k4.data_ptr(),
+                                                      v4.data_ptr(), C.byref(out), _ptr(status), _stream_ptr(stream)),
+                   "b2a_sdpa_forward_sharded")
+        shape = (B, Hq * self.shard.world, Sq, v4.shape[-1])
+        return _device_view(out.value, shape, q4.dtype, q4.device)
+
+
+class _RawDeviceMemory:
+    """Device memory owned by the library, described through ``__cuda_array_interface__`` (as 16-bit words)."""
+
+    def __init__(self, ptr: int, n16: int):
+        self.__cuda_array_interface__ = {"shape": (n16,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+
+
+def _device_view(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    words = torch.as_tensor(_RawDeviceMemory(ptr, n), device=device)
+    return words.view(dtype).view(*shape)
