@@ -37,6 +37,16 @@
 #include "launch.cuh"
 #include "tcgen05.cuh"
 
+#ifndef B2A_TC_SNAKE
+#define B2A_TC_SNAKE 1
+#endif
+#ifndef B2A_TC_ORDER
+#define B2A_TC_ORDER 0
+#endif
+#ifndef B2A_TC_GRID_ALL
+#define B2A_TC_GRID_ALL 0
+#endif
+
 namespace b2a {
 namespace {
 
@@ -49,12 +59,13 @@ constexpr int kPanel = 128 * 128;    // bytes of one [128 rows x 64 elements] sw
 constexpr int kTile = 2 * kPanel;    // a [128 x 128] 16-bit tile
 constexpr int kThreadsDense = 384;   // 3 warpgroups: softmax A, softmax B, {producer, MMA issuer, 2 idle warps}
 constexpr int kThreadsPaged = 512;   // plus the de-quantising producer warpgroup
-constexpr int kNumBars = 21;
-constexpr int kSmemBytes = 6 * kTile + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot, abort flag */;
+constexpr int kNumBars = 23;
+constexpr int kStageOut = 8 * 4096;  // epilogue staging: one [32 rows x 64 elements] slab per softmax warp
+constexpr int kSmemBytes = 6 * kTile + kStageOut + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot, abort flag */;
 constexpr float kLazyThreshold = 8.0f;  // log2 units
 constexpr int kCacheChunk = 16 * (kHeadDim + 4);  // bytes of one (block, KV head) chunk of the u8 pool
 
-enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16, P_HALF = 17, Q_CONV = 19 };
+enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_READY = 12, O_DONE = 14, DRAIN = 16, P_HALF = 17, Q_CONV = 19, Q_EMPTY = 21 };
 
 struct TcParams {
     int B, Hq, Hkv, G, Sq, Skv;
@@ -240,24 +251,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte swizzle atoms want 1024-byte aligned tiles
     uint8_t* gbase = smem_raw + (base - raw);
     const uint32_t sQ = base, sK = base + 2 * kTile, sV = base + 4 * kTile;
-    const uint32_t bars = base + 6 * kTile;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 6 * kTile + kNumBars * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 6 * kTile + kNumBars * 8 + 8);
+    const uint32_t sOut = base + 6 * kTile;
+    const uint32_t bars = base + 6 * kTile + kStageOut;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 6 * kTile + kStageOut + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 6 * kTile + kStageOut + kNumBars * 8 + 8);
     auto BAR = [&](int i) { return bars + 8u * static_cast<uint32_t>(i); };
     constexpr bool kKvBf16 = kPaged ? false : kBf16;  // element format of the K/V tiles and of P
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- which two tiles.  Rows are numbered inside the sequence (paged) or the tensor (dense); `pos_base` is the
-    // key position the first row of the problem may see up to, `kv_limit` the number of keys that exist.
-    int b = 0, hk, seq = 0, tok_base = 0, nrows_total, pos_base = 0, kv_limit;
+    // ---- work items.  An item is a pair of tiles of one KV head.  Rows are numbered inside the sequence (paged) or
+    // the tensor (dense); `pos_base` is the key position the first row of the problem may see up to, `kv_limit` the
+    // number of keys that exist.  Paged mode: one item per CTA, taken from the device-built list.  Dense mode: the
+    // CTA is persistent; the items, heaviest (late row blocks) first, are dealt to the CTAs in snake order (round
+    // k forwards, round k+1 backwards), which evens out the causal imbalance without any shared counter.
+    struct Item {
+        int b, hk, row0A, row0B, headA, headB, nkvA, nkvB, nmax;
+    };
+    int seq = 0, tok_base = 0, nrows_total, pos_base = 0, kv_limit;
     bool causal;
     int pair_in_seq = 0;
     if constexpr (kPaged) {
         if (static_cast<int>(blockIdx.x) >= p.plan[0]) return;  // the grid is a bound on the number of items
         seq = p.plan[kPlanHeaderInts + 2 * blockIdx.x];
         pair_in_seq = p.plan[kPlanHeaderInts + 2 * blockIdx.x + 1];
-        hk = blockIdx.y;
         tok_base = p.t.subsequence_begins[seq];
         nrows_total = p.t.subsequence_begins[seq + 1] - tok_base;
         if (nrows_total < 2) return;  // decode rows and idle sequences belong to the decode kernel
@@ -271,8 +288,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             return;
         }
     } else {
-        b = blockIdx.y / p.Hkv;
-        hk = blockIdx.y % p.Hkv;
         nrows_total = p.Sq;
         kv_limit = p.Skv;
         causal = p.causal != 0;
@@ -280,22 +295,47 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int nrb = (nrows_total + kBM - 1) / kBM;
     const int tiles = nrb * p.G;
     const int pairs = (tiles + 1) / 2;
-    const int pair = kPaged ? pair_in_seq : pairs - 1 - static_cast<int>(blockIdx.x);  // late row blocks first
-    if (pair < 0 || pair >= pairs) return;
-    int row0A, row0B, headA, headB, nkvA, nkvB;
-    {
+    if (kPaged && (pair_in_seq < 0 || pair_in_seq >= pairs)) return;
+    const int total_items = kPaged ? 1 : pairs * p.B * p.Hkv;  // the launcher keeps this below 2^31
+    auto get_item = [&](int k, Item& it) -> bool {  // the k-th item of this CTA
+        int pair;
+        if constexpr (kPaged) {
+            if (k > 0) return false;
+            pair = pair_in_seq;
+            it.b = 0;
+            it.hk = blockIdx.y;
+        } else {
+            const int ctas = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
+#if B2A_TC_SNAKE
+            const int idx = k * ctas + ((k & 1) ? ctas - 1 - me : me);
+#else
+            const int idx = k * ctas + me;
+#endif
+            if (idx >= total_items) return false;
+            const int bh = p.B * p.Hkv;
+#if B2A_TC_ORDER == 0
+            pair = pairs - 1 - idx / bh;
+            const int y = idx % bh;
+#else
+            pair = pairs - 1 - idx % pairs;
+            const int y = idx / pairs;
+#endif
+            it.b = y / p.Hkv;
+            it.hk = y % p.Hkv;
+        }
         auto tile_of = [&](int t, int& row0, int& head, int& nkv) {
             const bool present = t < tiles;
             const int rb = present ? t / p.G : 0, g = present ? t % p.G : 0;
             row0 = rb * kBM;
-            head = hk * p.G + g;
+            head = it.hk * p.G + g;
             const int kv_end = causal ? min(kv_limit, pos_base + row0 + kBM) : kv_limit;
             nkv = present ? (kv_end + kBN - 1) / kBN : 0;
         };
-        tile_of(2 * pair, row0A, headA, nkvA);
-        tile_of(2 * pair + 1, row0B, headB, nkvB);
-    }
-    const int nmax = max(nkvA, nkvB);
+        tile_of(2 * pair, it.row0A, it.headA, it.nkvA);
+        tile_of(2 * pair + 1, it.row0B, it.headB, it.nkvB);
+        it.nmax = max(it.nkvA, it.nkvB);
+        return true;
+    };
 
     // ---- set-up: barriers, TMEM
     if (threadIdx.x == 0) {
@@ -303,6 +343,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             uint32_t count = 1;
             if (i == P_READY || i == P_READY + 1 || i == P_HALF || i == P_HALF + 1) count = 128;
             if (i == Q_CONV || i == Q_CONV + 1) count = 128;
+            if (i == Q_EMPTY || i == Q_EMPTY + 1) count = 1;
             if (kPaged && (i == K_FULL || i == K_FULL + 1 || i == V_FULL || i == V_FULL + 1)) count = 128;
             mbar_init(BAR(i), count);
         }
@@ -327,6 +368,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // =============================== de-quantising K/V producers (paged) ===============================
         if constexpr (kPaged) {
             asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
+            Item item;
+            get_item(0, item);  // paged mode: exactly one item per CTA
+            const int nkvA = item.nkvA, nkvB = item.nkvB, nmax = item.nmax, hk = item.hk;
             const int tp = static_cast<int>(threadIdx.x) - 384;
             const int tok_in_blk = tp >> 3, c16 = tp & 7;
             const int32_t* btab = p.t.block_indices + p.t.block_indices_begins[seq];
@@ -432,35 +476,43 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 prefetch_tensormap(&tmK);
                 prefetch_tensormap(&tmV);
             }
-            if (nkvA > 0) {
-                mbar_expect_tx(BAR(Q_FULL + 0), kTile);
-                tma_load_4d(sQ, &tmQ, BAR(Q_FULL + 0), 0, tok_base + row0A, headA, b);
-                tma_load_4d(sQ + kPanel, &tmQ, BAR(Q_FULL + 0), 64, tok_base + row0A, headA, b);
-            }
-            if (nkvB > 0) {
-                mbar_expect_tx(BAR(Q_FULL + 1), kTile);
-                tma_load_4d(sQ + kTile, &tmQ, BAR(Q_FULL + 1), 0, tok_base + row0B, headB, b);
-                tma_load_4d(sQ + kTile + kPanel, &tmQ, BAR(Q_FULL + 1), 64, tok_base + row0B, headB, b);
-            }
-            int issued_k = 0, issued_v = 0;
-            if constexpr (!kPaged) {
-                for (int j = 0; j < nmax; ++j) {
-                    const int st = j & 1, n = j >> 1;
-                    if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) break;
-                    mbar_expect_tx(BAR(K_FULL + st), kTile);
-                    tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, j * kBN, hk, b);
-                    tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, j * kBN, hk, b);
-                    ++issued_k;
-                    if (n > 0 && !mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag)) break;
-                    mbar_expect_tx(BAR(V_FULL + st), kTile);
-                    tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, j * kBN, hk, b);
-                    tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, j * kBN, hk, b);
-                    ++issued_v;
+            // running counts over the items of this CTA: K/V tiles issued (ring position) and Q tiles loaded
+            int g = 0, issued_k = 0, issued_v = 0, qn[2] = {0, 0};
+            bool ok = true;
+            Item it;
+            for (int k = 0; ok && get_item(k, it); ++k) {
+                auto load_q = [&](int X) {
+                    const int nkvX = X ? it.nkvB : it.nkvA;
+                    if (nkvX == 0) return;
+                    // the tile's previous occupant is free once its last QK^T has completed
+                    if (qn[X] > 0 && !mbar_wait(BAR(Q_EMPTY + X), (qn[X] - 1) & 1, abort_flag)) { ok = false; return; }
+                    mbar_expect_tx(BAR(Q_FULL + X), kTile);
+                    const int row = tok_base + (X ? it.row0B : it.row0A), head = X ? it.headB : it.headA;
+                    tma_load_4d(sQ + X * kTile, &tmQ, BAR(Q_FULL + X), 0, row, head, it.b);
+                    tma_load_4d(sQ + X * kTile + kPanel, &tmQ, BAR(Q_FULL + X), 64, row, head, it.b);
+                    ++qn[X];
+                };
+                load_q(0);
+                if (ok) load_q(1);
+                if constexpr (!kPaged) {
+                    for (int j = 0; ok && j < it.nmax; ++j, ++g) {
+                        const int st = g & 1, n = g >> 1;
+                        if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) { ok = false; break; }
+                        mbar_expect_tx(BAR(K_FULL + st), kTile);
+                        tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, j * kBN, it.hk, it.b);
+                        tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, j * kBN, it.hk, it.b);
+                        ++issued_k;
+                        if (n > 0 && !mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag)) { ok = false; break; }
+                        mbar_expect_tx(BAR(V_FULL + st), kTile);
+                        tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, j * kBN, it.hk, it.b);
+                        tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, j * kBN, it.hk, it.b);
+                        ++issued_v;
+                    }
                 }
             }
             if (*abort_flag) {  // let copies already in flight land before the CTA goes away
-                if (nkvA > 0) mbar_drain(BAR(Q_FULL + 0), 0);
-                if (nkvB > 0) mbar_drain(BAR(Q_FULL + 1), 0);
+                for (int X = 0; X < 2; ++X)
+                    if (qn[X] > 0) mbar_drain(BAR(Q_FULL + X), (qn[X] - 1) & 1);
                 for (int jj = max(0, issued_k - 2); jj < issued_k; ++jj) mbar_drain(BAR(K_FULL + (jj & 1)), (jj >> 1) & 1);
                 for (int jj = max(0, issued_v - 2); jj < issued_v; ++jj) mbar_drain(BAR(V_FULL + (jj & 1)), (jj >> 1) & 1);
             }
@@ -472,73 +524,91 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // de-quantised values keep 11 significant bits and bf16 queries are converted in shared memory first
             constexpr uint32_t idesc_qk = instr_desc_f16(kKvBf16, false, kBM, kBN);
             constexpr uint32_t idesc_pv = instr_desc_f16(kKvBf16, true, kBM, kHeadDim);
+            // descriptors are assembled at the point of issue from (tile address >> 4) plus compile-time parts
+            constexpr uint32_t kLoK = desc_lo_sw128(16), kHiK = desc_hi_sw128(1024);        // K-major: Q and K tiles
+            constexpr uint32_t kLoV = desc_lo_sw128(kPanel), kHiV = desc_hi_sw128(1024);    // MN-major: V tiles
+            const uint32_t q16 = (sQ >> 4) & 0x3FFFu, k16 = (sK >> 4) & 0x3FFFu, v16 = (sV >> 4) & 0x3FFFu;
             auto issue_qk = [&](int X, int st) {  // S_X = Q_X K^T : 8 steps of 16 along D
                 const uint32_t d = tmem + static_cast<uint32_t>(X * 128);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = static_cast<uint32_t>((ks >> 2) * kPanel + (ks & 3) * 32);
-                    mma_ss(d, smem_desc_sw128(sQ + X * kTile + off, 16, 1024),
-                           smem_desc_sw128(sK + st * kTile + off, 16, 1024), idesc_qk, ks > 0);
-                }
+                const uint32_t qa = q16 + static_cast<uint32_t>(X * (kTile >> 4)), ka = k16 + static_cast<uint32_t>(st * (kTile >> 4));
+#define B2A_QK(ks) \
+    mma_ss_c<((((ks) / 4) * kPanel + ((ks) & 3) * 32) / 16), ((((ks) / 4) * kPanel + ((ks) & 3) * 32) / 16), kLoK, kLoK, kHiK, kHiK, \
+             idesc_qk>(d, qa, ka, (ks) > 0 ? 1u : 0u)
+                B2A_QK(0); B2A_QK(1); B2A_QK(2); B2A_QK(3); B2A_QK(4); B2A_QK(5); B2A_QK(6); B2A_QK(7);
+#undef B2A_QK
             };
             // O_X += P_X V : 8 steps of 16 along the keys, issued in two halves as the halves of P arrive
-            auto issue_pv = [&](int X, int st, bool acc, int ks_lo) {
+            auto issue_pv = [&](int X, int st, bool acc, int half) {
                 const uint32_t d = tmem + static_cast<uint32_t>(256 + X * 128);
-#pragma unroll
-                for (int ks = ks_lo; ks < ks_lo + 4; ++ks) {
-                    mma_ts(d, tmem + static_cast<uint32_t>(X * 128 + ks * 8),
-                           smem_desc_sw128(sV + st * kTile + ks * 2048, kPanel, 1024), idesc_pv, acc || ks > 0);
-                }
+                const uint32_t pa = tmem + static_cast<uint32_t>(X * 128 + half * 32);
+                const uint32_t va = v16 + static_cast<uint32_t>(st * (kTile >> 4) + half * (4 * 2048 / 16));
+#define B2A_PV(ks, accv) mma_ts_c<(ks) * 8, ((ks) * 2048) / 16, kLoV, kHiV, idesc_pv>(d, pa, va, accv)
+                B2A_PV(0, acc ? 1u : 0u); B2A_PV(1, 1u); B2A_PV(2, 1u); B2A_PV(3, 1u);
+#undef B2A_PV
             };
             bool ok = true;
             constexpr int kQReady = (kPaged && kBf16) ? Q_CONV : Q_FULL;
-            if (nkvA > 0) ok = ok && mbar_wait(BAR(kQReady + 0), 0, abort_flag);
-            if (nkvB > 0) ok = ok && mbar_wait(BAR(kQReady + 1), 0, abort_flag);
-            ok = ok && mbar_wait(BAR(K_FULL + 0), 0, abort_flag);
-            if (ok) {
+            // running counts over the items of this CTA: K/V ring position, steps of each tile, Q tiles consumed
+            int g0 = 0, sx[2] = {0, 0}, qn[2] = {0, 0};
+            Item it;
+            for (int k = 0; ok && get_item(k, it); ++k) {
+                const int nkvA = it.nkvA, nkvB = it.nkvB, nmax = it.nmax;
+                if (nkvA > 0) ok = ok && mbar_wait(BAR(kQReady + 0), qn[0] & 1, abort_flag);
+                if (nkvB > 0) ok = ok && mbar_wait(BAR(kQReady + 1), qn[1] & 1, abort_flag);
+                ok = ok && mbar_wait(BAR(K_FULL + (g0 & 1)), (g0 >> 1) & 1, abort_flag);
+                if (!ok) break;
                 tc_fence_after();
                 if (nkvA > 0) {
-                    issue_qk(0, 0);
+                    issue_qk(0, g0 & 1);
                     mma_commit(BAR(S_FULL + 0));
+                    if (nkvA == 1) mma_commit(BAR(Q_EMPTY + 0));  // last use of this Q tile: the producer may refill it
                 }
                 if (nkvB > 0) {
-                    issue_qk(1, 0);
+                    issue_qk(1, g0 & 1);
                     mma_commit(BAR(S_FULL + 1));
+                    if (nkvB == 1) mma_commit(BAR(Q_EMPTY + 1));
                 }
-                mma_commit(BAR(K_EMPTY + 0));
-            }
-            for (int j = 0; ok && j < nmax; ++j) {
-                const int stv = j & 1;
-                if (!mbar_wait(BAR(V_FULL + stv), (j >> 1) & 1, abort_flag)) { ok = false; break; }
-                TC_TRACE(1024, j, 0);
-                bool k_next_ready = false;
+                mma_commit(BAR(K_EMPTY + (g0 & 1)));
+                for (int j = 0; ok && j < nmax; ++j) {
+                    const int g = g0 + j, stv = g & 1;
+                    if (!mbar_wait(BAR(V_FULL + stv), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+                    TC_TRACE(1024, j, 0);
+                    bool k_next_ready = false;
 #pragma unroll
-                for (int X = 0; X < 2; ++X) {
-                    const int nkvX = X ? nkvB : nkvA;
-                    if (ok && j < nkvX) {
-                        if (!mbar_wait(BAR(P_HALF + X), j & 1, abort_flag)) { ok = false; break; }
-                        TC_TRACE(1024, j, 1 + 2 * X);
-                        tc_fence_after();
-                        issue_pv(X, stv, j > 0, 0);
-                        if (!mbar_wait(BAR(P_READY + X), j & 1, abort_flag)) { ok = false; break; }
-                        tc_fence_after();
-                        issue_pv(X, stv, true, 4);
-                        mma_commit(BAR(O_DONE + X));
-                    }
-                    if (ok && j + 1 < nkvX) {
-                        if (!k_next_ready) {
-                            if (!mbar_wait(BAR(K_FULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-                            k_next_ready = true;
+                    for (int X = 0; X < 2; ++X) {
+                        const int nkvX = X ? nkvB : nkvA;
+                        if (ok && j < nkvX) {
+                            const int par = (sx[X] + j) & 1;
+                            if (!mbar_wait(BAR(P_HALF + X), par, abort_flag)) { ok = false; break; }
+                            TC_TRACE(1024, j, 1 + 2 * X);
                             tc_fence_after();
+                            issue_pv(X, stv, j > 0, 0);
+                            if (!mbar_wait(BAR(P_READY + X), par, abort_flag)) { ok = false; break; }
+                            tc_fence_after();
+                            issue_pv(X, stv, true, 1);
+                            mma_commit(BAR(O_DONE + X));
                         }
-                        issue_qk(X, (j + 1) & 1);
-                        mma_commit(BAR(S_FULL + X));
+                        if (ok && j + 1 < nkvX) {
+                            if (!k_next_ready) {
+                                if (!mbar_wait(BAR(K_FULL + ((g + 1) & 1)), ((g + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                                k_next_ready = true;
+                                tc_fence_after();
+                            }
+                            issue_qk(X, (g + 1) & 1);
+                            mma_commit(BAR(S_FULL + X));
+                            if (j + 2 == nkvX) mma_commit(BAR(Q_EMPTY + X));
+                        }
+                        TC_TRACE(1024, j, 2 + 2 * X);
                     }
-                    TC_TRACE(1024, j, 2 + 2 * X);
+                    if (!ok) break;
+                    mma_commit(BAR(V_EMPTY + stv));
+                    if (j + 1 < nmax) mma_commit(BAR(K_EMPTY + ((g + 1) & 1)));
                 }
-                if (!ok) break;
-                mma_commit(BAR(V_EMPTY + stv));
-                if (j + 1 < nmax) mma_commit(BAR(K_EMPTY + ((j + 1) & 1)));
+                g0 += nmax;
+                sx[0] += nkvA;
+                sx[1] += nkvB;
+                qn[0] += nkvA > 0;
+                qn[1] += nkvB > 0;
             }
             mma_commit(BAR(DRAIN));  // everything issued has completed before TMEM and shared memory are given up
             mbar_drain(BAR(DRAIN), 0);
@@ -552,18 +622,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         const int X = warp >> 2;
         const int r = static_cast<int>(threadIdx.x) - X * 128;
-        const int row0 = X ? row0B : row0A, head = X ? headB : headA, nkv = X ? nkvB : nkvA;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tS = tmem + lane_base + static_cast<uint32_t>(X * 128);
         const uint32_t tO = tmem + lane_base + static_cast<uint32_t>(256 + X * 128);
-        if (nkv > 0) {
-            const int row_pos = pos_base + row0 + r;  // last key position this row may see (causal)
+        int sxb = 0;  // steps of this tile in the CTA's earlier items: every per-step barrier is at phase (sxb + j)
+        bool ok = true;
+        Item item;
+        for (int k = 0; ok && get_item(k, item); ++k) {
+            const int nkv = X ? item.nkvB : item.nkvA;
+            if (nkv == 0) continue;
+            const int row_pos0 = pos_base + (X ? item.row0B : item.row0A);
+            // first step whose tile touches the end of the keys or the causal diagonal (both conditions only
+            // become true as j grows): steps before it need no masking
+            int jb;
+            {
+                const int j_end = kv_limit / kBN;
+                const int dgl = row_pos0 - (kBN - 1);
+                const int j_diag = dgl < 0 ? 0 : dgl / kBN + 1;
+                jb = causal ? min(j_end, j_diag) : j_end;
+            }
             const float c = p.scale_log2;
             float m_used = -1.0e30f, l = 0.f;
-            bool ok = true;
             for (int j = 0; j < nkv; ++j) {
                 // every lane takes the same decision, so the warp-collective TMEM instructions stay converged
-                ok = __all_sync(0xffffffffu, mbar_wait(BAR(S_FULL + X), j & 1, abort_flag));
+                ok = __all_sync(0xffffffffu, mbar_wait(BAR(S_FULL + X), (sxb + j) & 1, abort_flag));
                 if (!ok) break;
                 if (threadIdx.x == 0) TC_TRACE(0, j, 0);
                 tc_fence_after();
@@ -573,8 +655,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 tmem_wait_ld();
                 if (threadIdx.x == 0) TC_TRACE(0, j, 1);
                 const int key0 = j * kBN;
-                const bool boundary = (key0 + kBN - 1 >= kv_limit) || (causal && key0 + kBN - 1 > pos_base + row0);
-                if (boundary) {
+                if (j >= jb) {
+                    const int row_pos = row_pos0 + r;  // last key position this row may see (causal)
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
 #pragma unroll
@@ -642,7 +724,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (threadIdx.x == 0) TC_TRACE(0, j, 3);
                 if (need_any && j > 0) {
                     // O_X still holds the old scale; PV_X(j-1) must have landed before it is touched
-                    ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (j - 1) & 1, abort_flag));
+                    ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (sxb + j - 1) & 1, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
@@ -663,10 +745,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mbar_arrive(BAR(P_READY + X));
                 if (threadIdx.x == 0) TC_TRACE(0, j, 4);
             }
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (nkv - 1) & 1, abort_flag));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (sxb + nkv - 1) & 1, abort_flag));
+            sxb += nkv;
             if (ok) {
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
+                // where the tile goes: worked out again here rather than kept in registers across the key loop
+                int k_again = k;
+                asm volatile("" : "+r"(k_again));
+                get_item(k_again, item);
+                const int row0 = X ? item.row0B : item.row0A, head = X ? item.headB : item.headA, b = item.b;
                 if constexpr (kPaged) {
                     // row-wise stores: rows past the sequence's end belong to other sequences and are dropped
                     const bool valid = row0 + r < nrows_total;
@@ -691,48 +779,52 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         }
                     }
                 } else {
-                    uint8_t* stage = gbase + X * kTile;  // Q_X is no longer needed: its tile is the staging buffer
+                    // two passes of 64 columns through this warp's [32 rows x 128 bytes] staging slab
+                    const uint32_t slab = sOut + static_cast<uint32_t>(warp) * 4096u;
+                    uint8_t* prow = gbase + 6 * kTile + warp * 4096 + (r & 31) * 128;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        uint32_t o[32];
-                        tmem_ld32(tO + 32 * q, o);
-                        tmem_wait_ld();
-                        uint8_t* prow = stage + (q >> 1) * kPanel + r * 128;
+                    for (int half = 0; half < 2; ++half) {
+                        if (lane == 0) tma_store_wait_read();  // the slab's previous store has read it
+                        __syncwarp();
 #pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
-                            uint4 v;
-                            v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
-                            v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
-                            v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
-                            v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
-                            const int chunk = (q & 1) * 4 + ch;  // 16-byte chunk of the 128-byte row, swizzled like TMA's
-                            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = v;
-                        }
-                    }
-                    // each warp stores its own 32 rows (a [64 x 32] box per panel): no cross-warp barrier is needed
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        const int w = warp & 3;
-                        const uint32_t src = sQ + X * kTile + w * 32 * 128;
-                        if (peers.world == 0) {
-                            tma_store_4d(&tmO, src, 0, row0 + 32 * w, head, b);
-                            tma_store_4d(&tmO, src + kPanel, 64, row0 + 32 * w, head, b);
-                        } else {
-                            // the same slab into every rank's buffer, the next rank first so that the ranks do
-                            // not all write to the same peer at the same time; local copy last
-                            for (int i = 1; i <= peers.world; ++i) {
-                                const int dst = (peers.rank + i) % peers.world;
-                                tma_store_4d(&peers.out[dst], src, 0, row0 + 32 * w, peers.head_offset + head, b);
-                                tma_store_4d(&peers.out[dst], src + kPanel, 64, row0 + 32 * w, peers.head_offset + head, b);
+                        for (int qq = 0; qq < 2; ++qq) {
+                            const int q = 2 * half + qq;
+                            uint32_t o[32];
+                            tmem_ld32(tO + 32 * q, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int ch = 0; ch < 4; ++ch) {
+                                uint4 v;
+                                v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
+                                v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
+                                v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
+                                v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
+                                const int chunk = qq * 4 + ch;  // 16-byte chunk of the 128-byte row, swizzled like TMA's
+                                *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = v;
                             }
                         }
-                        tma_store_commit();
-                        tma_store_wait_all();  // completion of the writes, not only of the reads of shared memory
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int w = warp & 3;
+                            if (peers.world == 0) {
+                                tma_store_4d(&tmO, slab, 64 * half, row0 + 32 * w, head, b);
+                            } else {
+                                // the same slab into every rank's buffer, the next rank first so that the ranks do
+                                // not all write to the same peer at the same time; local copy last
+                                for (int i = 1; i <= peers.world; ++i) {
+                                    const int dst = (peers.rank + i) % peers.world;
+                                    tma_store_4d(&peers.out[dst], slab, 64 * half, row0 + 32 * w, peers.head_offset + head, b);
+                                }
+                            }
+                            tma_store_commit();
+                        }
                     }
                 }
             }
         }
+        // stores still in flight: their completion (not only the read of shared memory) before the CTA ends
+        if (lane == 0) tma_store_wait_all();
     }
 
     tc_fence_before();
@@ -882,7 +974,11 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     p.status = status;
     const int nrb = (d.Sq + kBM - 1) / kBM;
     const int pairs = (nrb * p.G + 1) / 2;
-    dim3 grid(pairs, d.B * d.Hkv);
+    const long long items = static_cast<long long>(pairs) * d.B * d.Hkv;
+    if (items >= (1LL << 30)) return B2A_ERR_UNSUPPORTED;
+    const int sms = device_sm_count();
+    if (sms <= 0) return B2A_ERR_CUDA;
+    dim3 grid(static_cast<unsigned>(items < sms || B2A_TC_GRID_ALL ? items : sms));  // persistent CTAs, one per SM
     static bool configured[2][64] = {};
     auto kern = bf16 ? attn_tc_kernel<true, false> : attn_tc_kernel<false, false>;
     const int rc = configure_once(kern, configured[bf16]);

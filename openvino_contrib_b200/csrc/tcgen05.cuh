@@ -70,6 +70,8 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sm
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// only until the stores have READ their shared-memory source (it may be overwritten; the writes may still be in flight)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -167,6 +169,48 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
         "}\n" ::"r"(d_tmem),
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+// Register-lean forms for unrolled issue loops: the 64-bit descriptors are put together inside the asm block from a
+// 32-bit base (low word of the descriptor of the tile's first byte), a compile-time offset in 16-byte units and a
+// compile-time high word, so that the compiler has one live register per tile instead of one per MMA.
+__device__ __host__ constexpr uint32_t desc_lo_sw128(uint32_t lbo_bytes) { return ((lbo_bytes >> 4) & 0x3FFFu) << 16; }
+__device__ __host__ constexpr uint32_t desc_hi_sw128(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+template <uint32_t kOffA, uint32_t kOffB, uint32_t kLoA, uint32_t kLoB, uint32_t kHiA, uint32_t kHiB, uint32_t kIdesc>
+__device__ __forceinline__ void mma_ss_c(uint32_t d_tmem, uint32_t a_addr16, uint32_t b_addr16, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b32 la, lb, id;\n"
+        ".reg .b64 da, db;\n"
+        "setp.ne.b32 p, %3, 0;\n"
+        "add.u32 la, %1, %4;\n"
+        "add.u32 lb, %2, %5;\n"
+        "mov.b64 da, {la, %6};\n"
+        "mov.b64 db, {lb, %7};\n"
+        "mov.b32 id, %8;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, id, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_addr16), "r"(b_addr16), "r"(accumulate), "n"(kOffA + kLoA), "n"(kOffB + kLoB), "n"(kHiA), "n"(kHiB), "n"(kIdesc)
+        : "memory");
+}
+template <uint32_t kOffA, uint32_t kOffB, uint32_t kLoB, uint32_t kHiB, uint32_t kIdesc>
+__device__ __forceinline__ void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr16, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b32 ta, lb, id;\n"
+        ".reg .b64 db;\n"
+        "setp.ne.b32 p, %3, 0;\n"
+        "add.u32 ta, %1, %4;\n"
+        "add.u32 lb, %2, %5;\n"
+        "mov.b64 db, {lb, %6};\n"
+        "mov.b32 id, %7;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, id, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_addr16), "r"(accumulate), "n"(kOffA), "n"(kOffB + kLoB), "n"(kHiB), "n"(kIdesc)
         : "memory");
 }
 // the mbarrier receives one arrival when every MMA issued so far by this thread has completed
