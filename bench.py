@@ -332,7 +332,10 @@ def bench_decode(name, steps, warmup, rank, world):
                 group = ShardGroup(shard, staging_bytes=n * Hq * D * 2)
             except Exception as e:  # CUDA IPC not available in this container: fall back to the library collective
                 exchange = f"nccl (peer mapping failed: {type(e).__name__})"
-    out_full = torch.empty(n, Hq * D, dtype=torch.float16, device="cuda") if group is not None else None
+    # B2A_BENCH_DECODE_INPLACE=1: the group's own buffer, the step is ONE kernel producing the rows in place on every
+    # rank; 0: decode + merge-and-push + wait-and-copy kernels into a caller's buffer
+    inplace = os.environ.get("B2A_BENCH_DECODE_INPLACE", "1") == "1"
+    out_full = None if inplace or group is None else torch.empty(n, Hq * D, dtype=torch.float16, device="cuda")
 
     def step():
         if group is not None:
@@ -340,7 +343,7 @@ def bench_decode(name, steps, warmup, rank, world):
             return
         b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1, out=out,
                             workspace=ws)
-        if world > 1:
+        if world > 1 and exchange != "local":  # "local": no exchange at all (diagnosis only; not a valid step)
             gather_heads_rows(out, shard, D, buffer=gathered)
     ms, _, _ = timed(step, steps, warmup, world)
     if group is not None:
@@ -353,8 +356,8 @@ def bench_decode(name, steps, warmup, rank, world):
     return {"workload": name, "kv_gbs": gbs, "ms_per_step": ms, "kv_bytes_per_step": kv_bytes,
             "frac_of_hbm_peak": gbs / (pk["hbm_gbs"] * world), "peak_gbs_per_gpu": pk["hbm_gbs"],
             "peak_source": pk["source"], "cached_tokens": tokens,
-            "traffic": NCU_TRAFFIC.get(name) if world == 1 else None, "launches_per_step": 3 if group is not None else 2,
-            "output_exchange": exchange}
+            "traffic": NCU_TRAFFIC.get(name) if world == 1 else None, "launches_per_step": (1 if inplace else 3) if group is not None else 2,
+            "output_exchange": exchange + (" (one kernel, in place)" if group is not None and inplace else "")}
 
 
 def bench_mixed(steps, warmup, rank, world):
@@ -420,6 +423,10 @@ def run_b2a(args):
              else bench_decode(args.only, args.steps, args.warmup, rank, world))
         if rank == 0:
             print(json.dumps(r))
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
         return
     pre = bench_prefill(args, rank, world, local)
     decode = {}

@@ -187,6 +187,12 @@ int b2a_shard_group_create(int rank, int world, size_t staging_bytes, b2a_shard_
 int b2a_shard_group_handle(const b2a_shard_group* g, unsigned char handle[64]);
 int b2a_shard_group_connect(b2a_shard_group* g, const unsigned char* handles /* world * 64 bytes, rank order */);
 void b2a_shard_group_destroy(b2a_shard_group* g);
+/* The group's own output buffer on this rank (staging_bytes long, fixed for the group's life).  Passing it as
+ * `out_full` to b2a_paged_attention_sharded selects the one-kernel step: the decode kernel's last CTA per
+ * (sequence, KV head) merges the splits and stores the rows straight into this buffer on EVERY rank, the grid's last
+ * CTA publishes the step and waits (bounded) for the other ranks - one launch, no copy, capturable in a CUDA graph.
+ * The rows are then read in place; they stay valid until this rank enqueues its next step on the group. */
+int b2a_shard_group_output(const b2a_shard_group* g, void** out);
 /* Decode step on this rank's heads (`local_desc` carries the LOCAL Hq and Hkv; query [num_tokens, Hq_local*D];
  * caches hold the local KV heads), output exchanged as above: out_full [num_tokens, Hq_local*world*D] is complete
  * on every rank when the stream reaches the end of the call's work.  Decode shapes only (as

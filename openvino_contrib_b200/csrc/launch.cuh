@@ -33,6 +33,13 @@ struct PeerPush {
     int rank, world;                   // world == 0: not sharded
     int row_elems;                     // elements of one full-width output row (Hq_total * D)
     int col_offset;                    // first column of this rank's heads
+    // Single-kernel step (group_counters != nullptr): the decode kernel's last CTA of every (sequence, KV head)
+    // merges that group's splits and stores the result into staging[r][0] of every rank r - the ranks' fixed
+    // output buffers, read in place - and the grid's last CTA publishes the step and waits for the other ranks.
+    // A rank announces in started[r][rank] that it has begun step s, i.e. that its readers of step s-1 are done;
+    // nobody stores into a rank's buffer for step s before that.
+    int32_t* group_counters;           // local: one per (sequence, KV head), self-resetting
+    int32_t* started[kMaxShardWorld];  // [rank]: that rank's array of "rank i has begun step s" (one int per source rank)
 };
 
 // paged_decode.cu — split-K decode over a u8 cache (D = Dv = 128, block 16, one query token per sequence)

@@ -113,32 +113,36 @@ __device__ __forceinline__ int first_block_of(int ctx, int sliding_window) {
     return first_pos / kBS;
 }
 
+// The walk over this CTA's chunk of one (sequence, KV head).  Returns false when the CTA has nothing to do (idle or
+// multi-token sequence, chunk past the context, inconsistent tables - reported); otherwise its partial is in the
+// workspace, `nsplit` is the number of CTAs of this sequence that write one, `tok` the sequence's token row.
 template <typename T, int NT>
-__global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+__device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out) {
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tid4 = lane & 3;
 
     const int tok = p.t.subsequence_begins[seq];
     const int qlen = p.t.subsequence_begins[seq + 1] - tok;
-    if (qlen != 1) return;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
+    if (qlen != 1) return false;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
     const int past = p.t.past_lens[seq];
     const int ctx = past + 1;  // the query token sits at position `past` and sees 0..past
     const int nblk = (ctx + kBS - 1) / kBS;
     if (past < 0 || nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
         if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return;
+        return false;
     }
     const int first_pos = p.sliding_window > 0 ? max(0, ctx - p.sliding_window) : 0;
     const int blk_lo = first_block_of(ctx, p.sliding_window);
     if (nblk - blk_lo > p.max_splits * p.blocks_per_cta) {  // context longer than the max_context_len the grid was sized for
         if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return;
+        return false;
     }
+    nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
+    tok_out = tok;
     const int my_lo = blk_lo + split * p.blocks_per_cta;
     const int my_hi = min(nblk, my_lo + p.blocks_per_cta);
-    if (my_lo >= my_hi) return;
+    if (my_lo >= my_hi) return false;
 
     // blocks of this warp: my_lo + warp + 4*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
     const int n_w = (my_hi - my_lo - warp + kWarps - 1) / kWarps;
@@ -387,6 +391,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const Deco
             p.ws_ml[slot * 2 + 1] = l;
         }
     }
+    return true;
 }
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
@@ -396,6 +401,108 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
     int32_t v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+template <typename T>
+__device__ __forceinline__ uint2 pack4(float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ uint2 pack4<__half>(float a, float b, float c, float d) {
+    return make_uint2(pack_h2(a, b), pack_h2(c, d));
+}
+template <>
+__device__ __forceinline__ uint2 pack4<__nv_bfloat16>(float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// Bounded wait on `n` flags (one thread per flag) until each shows `epoch`; B2A_DEV_TIMEOUT after about a second.
+__device__ __forceinline__ void wait_flags(const int32_t* flags, int n, int32_t epoch, int32_t* status) {
+    if (static_cast<int>(threadIdx.x) < n) {
+        const int32_t* flag = flags + threadIdx.x;
+        const long long t0 = clock64();
+        while (ld_acquire_sys(flag) - epoch < 0) {
+            if (clock64() - t0 > (1LL << 31)) {
+                report(status, B2A_DEV_TIMEOUT);
+                break;
+            }
+        }
+    }
+}
+
+// The whole decode step in one launch, for sharded heads (PeerPush with group_counters).  After its chunk, a CTA
+// takes a ticket of its (sequence, KV head); the CTA that gets the last ticket merges the group's partials - 32
+// threads per query head, four heads at a time, every split's 16-byte piece requested before any is used - and
+// stores the normalised rows into the output buffer of every rank.  The grid's last CTA then publishes the step and
+// waits for the other ranks' steps, so the output is complete on this rank when the kernel ends.
+template <typename T, int NT, bool kFused>
+__global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    int nsplit = 0, tok = 0;
+    if constexpr (!kFused) {
+        decode_chunk<T, NT>(p, smem, nsplit, tok);
+    } else {
+        __shared__ int s_role;
+        const int tid = threadIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+        const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
+            st_release_sys(p.push.started[tid] + p.push.rank, epoch);  // this rank's readers of the previous step are done
+        const bool worked = decode_chunk<T, NT>(p, smem, nsplit, tok);
+        if (worked) {
+            __threadfence();  // this CTA's partial before its ticket
+            __syncthreads();
+            if (tid == 0) {
+                int32_t* ctr = p.push.group_counters + seq * p.Hkv + hk;
+                const bool last = atomicAdd(ctr, 1) == nsplit - 1;
+                if (last) *ctr = 0;
+                s_role = last ? 1 : 0;
+            }
+            __syncthreads();
+            if (s_role == 1) {
+                __threadfence();
+                wait_flags(p.push.started[p.push.rank], p.push.world, epoch, p.status);  // every rank has begun this step
+                __syncthreads();
+                const int d4 = (tid & 31) * 4;
+                for (int g = tid >> 5; g < p.G; g += kWarps) {
+                    const int h = hk * p.G + g;
+                    const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
+                    float mc = kNegBig;
+                    for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, __ldcg(p.ws_ml + (base + s) * 2));
+                    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, l = 0.f;
+#pragma unroll 4
+                    for (int s = 0; s < nsplit; ++s) {
+                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (base + s) * 2));
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (base + s) * kD + d4));
+                        const float f = ex2(ml.x - mc);
+                        o0 += v.x * f;
+                        o1 += v.y * f;
+                        o2 += v.z * f;
+                        o3 += v.w * f;
+                        l += ml.y * f;
+                    }
+                    const bool nz = l > 0.f;
+                    const uint2 val = pack4<T>(nz ? o0 / l : 0.f, nz ? o1 / l : 0.f, nz ? o2 / l : 0.f, nz ? o3 / l : 0.f);
+                    const size_t at = static_cast<size_t>(tok) * p.push.row_elems + p.push.col_offset + h * kD + d4;
+                    for (int r = 0; r < p.push.world; ++r)
+                        *reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.push.staging[r][0]) + at) = val;
+                }
+            }
+        }
+        if (worked && s_role == 1) __threadfence_system();  // this CTA's peer stores before its arrival
+        __syncthreads();
+        if (tid == 0) {
+            const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
+            const bool last = atomicAdd(p.push.done_counter, 1) == total - 1;
+            if (last) {
+                *p.push.done_counter = 0;
+                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;
+                __threadfence_system();
+                for (int r = 0; r < p.push.world; ++r) st_release_sys(p.push.flags[r] + p.push.rank, epoch);
+            }
+            s_role = last ? 2 : 0;
+        }
+        __syncthreads();
+        if (s_role == 2) wait_flags(p.push.flags[p.push.rank], p.push.world, epoch, p.status);
+    }
 }
 
 // Merge the split partials of one (sequence, query head): out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
@@ -474,9 +581,9 @@ __global__ void __launch_bounds__(256) peer_wait_copy_kernel(const PeerPush push
     for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = src[i];
 }
 
-template <typename T, int NT>
-int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
-    auto kern = paged_decode_kernel<T, NT>;
+template <typename T, int NT, bool kFused>
+int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
+    auto kern = paged_decode_kernel<T, NT, kFused>;
     static bool configured[64] = {};  // per device; setting the attribute twice is harmless
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
@@ -487,7 +594,14 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
     }
     dim3 grid(p.max_splits, p.Hkv, num_seqs);
     kern<<<grid, kWarps * 32, kSmemBytes, stream>>>(p);
-    if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+}
+
+template <typename T, int NT>
+int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
+    if (p.push.world > 0 && p.push.group_counters != nullptr) return launch_kernel<T, NT, true>(p, num_seqs, stream);
+    const int rc = launch_kernel<T, NT, false>(p, num_seqs, stream);
+    if (rc != B2A_OK) return rc;
     paged_decode_merge_kernel<T><<<dim3(p.Hq, num_seqs), kD, 0, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
     if (p.push.world > 0) {

@@ -16,10 +16,12 @@
 #include "launch.cuh"
 
 namespace {
-constexpr size_t kFlagsBytes = 256;     // decode: ints 0..7; prefill: ints 16..23
+constexpr size_t kFlagsBytes = 256;     // decode: ints 0..7; prefill: ints 16..23; "step begun" of the one-kernel decode: ints 32..39
 constexpr size_t kCountersBytes = 256;  // decode step counter at +0, decode done counter at +64, prefill done counter at +128
 constexpr int kPrefillFlagOffset = 16;
-enum { kModeUnset = 0, kModeDecode = 1, kModePrefill = 2 };
+constexpr int kStartedFlagOffset = 32;
+constexpr size_t kGroupCounters = 16384;  // (sequence, KV head) tickets of the one-kernel decode step
+enum { kModeUnset = 0, kModeDecode = 1, kModePrefill = 2, kModeDecodeInPlace = 3 };
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 }  // namespace
 
@@ -30,7 +32,7 @@ struct b2a_shard_group {
     bool connected = false;
     int mode = kModeUnset;       // a group serves one kind of step: the two kinds alternate the staging halves differently
     int32_t prefill_step = 0;    // host-side count of prefill steps
-    size_t total_bytes() const { return 2 * staging_bytes + kFlagsBytes + kCountersBytes; }
+    size_t total_bytes() const { return 2 * staging_bytes + kFlagsBytes + kCountersBytes + kGroupCounters * sizeof(int32_t); }
 };
 
 extern "C" {
@@ -79,6 +81,12 @@ int b2a_shard_group_connect(b2a_shard_group* g, const unsigned char* handles) {
     return B2A_OK;
 }
 
+int b2a_shard_group_output(const b2a_shard_group* g, void** out) {
+    if (g == nullptr || out == nullptr) return B2A_ERR_NULL;
+    *out = g->base[g->rank];
+    return B2A_OK;
+}
+
 void b2a_shard_group_destroy(b2a_shard_group* g) {
     if (g == nullptr) return;
     for (int r = 0; r < g->world; ++r) {
@@ -104,7 +112,11 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
         return B2A_ERR_NULL;
     if (d.Hq <= 0 || d.Hkv <= 0 || d.Hq % d.Hkv != 0 || d.num_seqs > 65535 || d.max_context_len <= 0) return B2A_ERR_DIM;
     if (!paged_decode_supported(d)) return B2A_ERR_UNSUPPORTED;  // decode steps only
-    if (g->mode == kModePrefill) return B2A_ERR_UNSUPPORTED;
+    // out_full == the group's own buffer (b2a_shard_group_output): results are produced in place by one kernel
+    const bool in_place = out_full == static_cast<void*>(g->base[g->rank]);
+    const int want = in_place ? kModeDecodeInPlace : kModeDecode;
+    if (g->mode != kModeUnset && g->mode != want) return B2A_ERR_UNSUPPORTED;
+    if (in_place && static_cast<size_t>(d.num_seqs) * d.Hkv > kGroupCounters) return B2A_ERR_CAPACITY;
     const size_t row_bytes = static_cast<size_t>(d.Hq) * g->world * d.D * 2;
     if (static_cast<size_t>(d.num_tokens) * row_bytes > g->staging_bytes) return B2A_ERR_CAPACITY;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -128,7 +140,12 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
     push.col_offset = g->rank * d.Hq * d.D;
     const PagedTables t{past_lens, subsequence_begins, block_indices, block_indices_begins,
                         d.num_seqs, d.num_tokens, d.num_blocks_total, d.block_size};
-    g->mode = kModeDecode;
+    if (in_place) {
+        push.group_counters = reinterpret_cast<int32_t*>(counters + kCountersBytes);
+        for (int r = 0; r < g->world; ++r)
+            push.started[r] = reinterpret_cast<int32_t*>(g->base[r] + 2 * g->staging_bytes) + kStartedFlagOffset;
+    }
+    g->mode = want;
     return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out_full, workspace, status,
                                reinterpret_cast<cudaStream_t>(stream), &push);
 }

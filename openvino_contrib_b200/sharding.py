@@ -137,13 +137,24 @@ class ShardGroup:
         self.close()
 
     def paged_attention(self, query_local, cache_local, past_lens, subsequence_begins, block_indices,
-                        block_indices_begins, max_context_len: int, out_full: torch.Tensor, workspace: torch.Tensor,
-                        scale: Optional[float] = None, status: Optional[torch.Tensor] = None, stream=None):
-        """One decode step on this rank's heads; ``out_full`` [tokens, Hq*D] is complete on every rank afterwards."""
+                        block_indices_begins, max_context_len: int, out_full: Optional[torch.Tensor],
+                        workspace: torch.Tensor, scale: Optional[float] = None,
+                        status: Optional[torch.Tensor] = None, stream=None):
+        """One decode step on this rank's heads; the [tokens, Hq*D] result is complete on every rank afterwards.
+
+        With ``out_full=None`` the step is a single kernel that produces the rows in the group's own buffer on every
+        rank; the returned tensor is a view of that buffer (valid until the next step on this group).  With a
+        caller's ``out_full`` the rows are exchanged through staging buffers and copied there.
+        """
         from . import _lib
         from .ops import _paged_desc, _ptr, _stream_ptr
         C = self._C
         n = query_local.shape[0]
+        if out_full is None:
+            ptr = C.c_void_p()
+            _lib.check(self._lib.b2a_shard_group_output(self._h, C.byref(ptr)), "b2a_shard_group_output")
+            out_full = _device_view(ptr.value, (n, self.shard.hq * cache_local.dv), query_local.dtype,
+                                    query_local.device)
         d = _paged_desc(query_local.dtype, cache_local, self.shard.hq_local, past_lens.shape[0], n, max_context_len,
                         1, scale, 0)
         _lib.check(self._lib.b2a_paged_attention_sharded(

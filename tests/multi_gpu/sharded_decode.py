@@ -59,6 +59,34 @@ def main():
         assert torch.equal(o_nccl, out), f"rank {rank} step {step}: differs from the NCCL gather"
     dist.barrier()
     group.close()
+    # the one-kernel step: results produced in place in the group's own buffer on every rank
+    group2 = ShardGroup(shard, staging_bytes=n * hq * d * 2)
+    for step in range(3):
+        q_full = torch.from_numpy(w.query * (1.0 - 0.125 * step)).to(torch.float16)
+        q_local = shard.take_q_rows(q_full, d).contiguous().cuda()
+        out = group2.paged_attention(q_local, cache, *tables, max_context_len=max(ctx), out_full=None, workspace=ws,
+                                     status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, f"rank {rank} in-place step {step}: status {int(status.item())}"
+        o_local = b2a.paged_attention(q_local, cache, *tables, hq=shard.hq_local, max_context_len=max(ctx),
+                                      max_q_len=1, workspace=ws)
+        o_nccl = gather_heads_rows(o_local, shard, d)
+        assert torch.equal(o_nccl, out), f"rank {rank} in-place step {step}: differs from the NCCL gather"
+        assert_close(out, w.reference(q_full.float().numpy()), torch.float16, f"rank {rank} in-place step {step}")
+    # the same captured once and replayed: the step counter lives on the device
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            out_g = group2.paged_attention(q_local, cache, *tables, max_context_len=max(ctx), out_full=None,
+                                           workspace=ws, status=status, stream=side)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and torch.equal(o_nccl, out_g), f"rank {rank}: graph replay of the in-place step"
+    dist.barrier()
+    group2.close()
     if rank == 0:
         print(f"sharded decode ok on {world} GPUs")
     dist.destroy_process_group()
