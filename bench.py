@@ -384,12 +384,15 @@ def bench_mixed(steps, warmup, rank, world):
     v = torch.randn(ntok, Hkv * D, generator=gen, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(ntok, Hq * D, dtype=torch.bfloat16, device="cuda")
     rb = int(sum((int(x) + 127) // 128 for x in qlen if x >= 2))  # what the scheduler knows (KvBlockManager reports it)
-    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.bfloat16, cache, Hq, n, ntok, 4096, 1024, rb)),
+    kvt = int(sum((int(c) + 127) // 128 * 128 for c, x in zip(ctx, qlen) if x >= 2))  # likewise
+    if os.environ.get("B2A_BENCH_NO_GATHER") == "1":
+        kvt = 0
+    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.bfloat16, cache, Hq, n, ntok, 4096, 1024, rb, kvt)),
                      dtype=torch.uint8, device="cuda")
 
     def attend():
         b2a.paged_attention(q, cache, past, sb, bi, bb, hq=Hq, max_context_len=4096, max_q_len=1024, out=out,
-                            workspace=ws, prefill_row_blocks=rb)
+                            workspace=ws, prefill_row_blocks=rb, prefill_kv_tokens=kvt)
 
     def step():
         b2a.paged_kv_store(k, v, cache, past, sb, bi, bb)
@@ -405,7 +408,8 @@ def bench_mixed(steps, warmup, rank, world):
     return {"workload": "cfg4", "ms_per_step": ms, "attention_ms": ams, "new_tokens": ntok,
             "prefill_flops": prefill_flops, "decode_kv_bytes": decode_bytes, "kv_store_bytes": store_bytes,
             "tokens_per_s": ntok / (ms * 1e-3), "bar_ms": bar_ms, "bar_over_measured": bar_ms / ams,
-            "launches_per_step": 5}
+            "launches_per_step": 6 if kvt else 5, "prefill_kv": "de-quantised once into an f16 scratch" if kvt else
+            "de-quantised inside the prefill kernel"}
 
 
 def run_b2a(args):

@@ -122,6 +122,12 @@ typedef struct b2a_paged_desc {
      * more tightly; 0 = unknown, the bound num_tokens/128 + num_seqs is used.  A value that is too small makes the
      * kernel report B2A_DEV_BAD_LEN instead of computing a wrong answer. */
     int32_t prefill_row_blocks;
+    /* Optional: an upper bound on the sum, over the sequences with two or more new tokens, of their context length
+     * (past + new tokens) rounded up to 128 (b2a_kvmgr_last_prefill_kv_tokens).  With it (and room for it in the
+     * workspace: b2a_paged_workspace_bytes counts 2 * Hkv * this * D * 2 bytes) those contexts are de-quantised once
+     * into an f16 scratch and the prefill kernel stages K/V tiles by TMA; without it (0) every prefill CTA
+     * de-quantises its own tiles.  A bound that is too small makes the step report B2A_DEV_BAD_LEN. */
+    int32_t prefill_kv_tokens;
 } b2a_paged_desc;
 
 /* Bytes of one (block, KV head) chunk of a cache of `kv_dtype` with head size d. */
@@ -232,6 +238,8 @@ int32_t b2a_kvmgr_free_blocks(const b2a_kvmgr* m);
 int32_t b2a_kvmgr_sequence_len(const b2a_kvmgr* m, int64_t seq_id); /* -1 if unknown */
 /* b2a_paged_desc.prefill_row_blocks of the step scheduled last */
 int32_t b2a_kvmgr_last_prefill_row_blocks(const b2a_kvmgr* m);
+/* b2a_paged_desc.prefill_kv_tokens of the step scheduled last */
+int32_t b2a_kvmgr_last_prefill_kv_tokens(const b2a_kvmgr* m);
 /* Reserve blocks for q_lens[i] new tokens of seq_ids[i] (all or nothing), fill the step tables (host arrays:
  * past_lens[n], subsequence_begins[n+1], block_indices[capacity], block_indices_begins[n+1]) and advance
  * the sequences' lengths.  *num_block_indices and *max_context_len receive the totals. */

@@ -29,6 +29,7 @@ class PagedDesc(C.Structure):
         ("Dv", C.c_int32), ("block_size", C.c_int32), ("num_seqs", C.c_int32), ("num_tokens", C.c_int32),
         ("num_blocks_total", C.c_int32), ("max_context_len", C.c_int32), ("max_q_len", C.c_int32),
         ("scale", C.c_float), ("sliding_window", C.c_int32), ("prefill_row_blocks", C.c_int32),
+        ("prefill_kv_tokens", C.c_int32),
     ]
 
 
@@ -65,6 +66,7 @@ SIGNATURES = {
     "b2a_kvmgr_free_blocks": (C.c_int32, [C.c_void_p]),
     "b2a_kvmgr_sequence_len": (C.c_int32, [C.c_void_p, C.c_int64]),
     "b2a_kvmgr_last_prefill_row_blocks": (C.c_int32, [C.c_void_p]),
+    "b2a_kvmgr_last_prefill_kv_tokens": (C.c_int32, [C.c_void_p]),
     "b2a_kvmgr_schedule_step": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_int32,
                                           C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                           C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32),

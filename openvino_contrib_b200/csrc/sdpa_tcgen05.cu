@@ -78,6 +78,7 @@ struct TcParams {
     PagedTables t;
     void* out;        // [tokens, Hq*128]
     const int* plan;  // work list built by paged_tc_plan_kernel: plan[0] = count, then (sequence, tile pair) entries
+    const int* kv_base;  // gathered K/V: first scratch row of every multi-token sequence
 };
 
 // Output side of a head-sharded launch (world == 0: single GPU, the tmO map is the output).
@@ -94,27 +95,76 @@ struct TcPeers {
 // count (exact when the caller passes the scheduler's hint) instead of max_q_len x num_seqs, which for a step with
 // a few long prefills and many decode sequences would be almost all empty CTAs.
 constexpr int kPlanHeaderInts = 4;
+// With `owner` given the kernel also lays out the gathered K/V scratch: every multi-token sequence gets a row range
+// of roundup(context, 128) rows (kv_base[seq]; allocation order is whatever the atomics make it), and owner[g] names
+// the sequence that 128-row group g belongs to (-1: nobody), which is how paged_gather_kernel finds its work.
 __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t, const int G, const int capacity,
-                                                            int* plan, int32_t* status) {
-    __shared__ int s_count;
-    if (threadIdx.x == 0) s_count = 0;
+                                                            int* plan, int32_t* status, int* kv_base, int* owner,
+                                                            const int owner_groups) {
+    // The list is sorted by weight (key steps of the pair's later tile, clamped to 255), heaviest first: a counting
+    // sort in three passes over the sequences - histogram, bucket offsets, scatter.
+    constexpr int kBuckets = 256;
+    __shared__ int s_hist[kBuckets], s_count, s_groups;
+    for (int i = threadIdx.x; i < kBuckets; i += blockDim.x) s_hist[i] = 0;
+    if (threadIdx.x == 0) s_count = s_groups = 0;
+    if (owner != nullptr)
+        for (int g = threadIdx.x; g < owner_groups; g += blockDim.x) owner[g] = -1;
+    __syncthreads();
+    auto weight = [&](int past, int qlen, int pair) {
+        const int tiles = ((qlen + 127) / 128) * G;
+        const int tile = min(2 * pair + 1, tiles - 1);  // the pair's later tile
+        const int keys = min(past + qlen, past + (tile / G) * 128 + 128);
+        return min(kBuckets - 1, max(0, (keys + 127) / 128));
+    };
+    for (int s = threadIdx.x; s < t.num_seqs; s += blockDim.x) {
+        const int qlen = t.subsequence_begins[s + 1] - t.subsequence_begins[s];
+        if (qlen < 2) continue;
+        const int past = max(0, t.past_lens[s]);
+        const int pairs = (((qlen + 127) / 128) * G + 1) / 2;
+        atomicAdd(&s_count, pairs);
+        for (int i = 0; i < pairs; ++i) atomicAdd(&s_hist[weight(past, qlen, i)], 1);
+        if (owner != nullptr) {
+            const int groups = t.past_lens[s] < 0 ? 0 : (past + qlen + 127) / 128;
+            const int g0 = atomicAdd(&s_groups, groups);
+            kv_base[s] = g0 * 128;
+            for (int i = 0; i < groups; ++i)
+                if (g0 + i < owner_groups) owner[g0 + i] = s;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {  // bucket w starts after all heavier buckets
+        int at = 0;
+        for (int w = kBuckets - 1; w >= 0; --w) {
+            const int n = s_hist[w];
+            s_hist[w] = at;
+            at += n;
+        }
+    }
     __syncthreads();
     for (int s = threadIdx.x; s < t.num_seqs; s += blockDim.x) {
         const int qlen = t.subsequence_begins[s + 1] - t.subsequence_begins[s];
         if (qlen < 2) continue;
+        const int past = max(0, t.past_lens[s]);
         const int pairs = (((qlen + 127) / 128) * G + 1) / 2;
-        const int at = atomicAdd(&s_count, pairs);
         for (int i = 0; i < pairs; ++i) {
-            if (at + i < capacity) {
-                plan[kPlanHeaderInts + 2 * (at + i)] = s;
-                plan[kPlanHeaderInts + 2 * (at + i) + 1] = pairs - 1 - i;  // late row blocks (most keys) first
+            const int at = atomicAdd(&s_hist[weight(past, qlen, i)], 1);
+            if (at < capacity) {
+                plan[kPlanHeaderInts + 2 * at] = s;
+                plan[kPlanHeaderInts + 2 * at + 1] = i;
             }
         }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         plan[0] = min(s_count, capacity);
-        if (s_count > capacity) report(status, B2A_DEV_BAD_LEN);  // the caller's prefill_row_blocks was too small
+        if (s_count > capacity) {  // the caller's prefill_row_blocks was too small
+            report(status, B2A_DEV_BAD_LEN);
+            plan[0] = 0;  // a truncated sorted list would drop arbitrary pairs: compute nothing instead
+        }
+        if (owner != nullptr && s_groups > owner_groups) {        // the caller's prefill_kv_tokens was too small
+            report(status, B2A_DEV_BAD_LEN);
+            plan[0] = 0;  // nothing is computed from a scratch that does not hold every sequence
+        }
     }
 }
 
@@ -218,14 +268,12 @@ __device__ long long g_tc_trace[2048];
 // zero-point is exact (both differences are representable), the multiplication by the scale rounds once - the same
 // value as (code - zp) * scale computed in float32 and rounded to f16.  scale and zp arrive as the raw f16 bits the
 // cache stores.
-__device__ __forceinline__ void dequant_piece_f16(uint4 w, unsigned short scale_bits, unsigned short zp_bits,
-                                                  uint8_t* row, int c16, int token) {
+__device__ __forceinline__ void dequant16_f16(uint4 w, unsigned short scale_bits, unsigned short zp_bits, uint32_t (&outw)[8]) {
     const uint32_t words[4] = {w.x, w.y, w.z, w.w};
     const __half2 sc2 = __half2half2(__ushort_as_half(scale_bits));
     const __half2 zp2 = __half2half2(__ushort_as_half(zp_bits));
     const uint32_t k1024_bits = 0x64006400u;
     const __half2 k1024 = *reinterpret_cast<const __half2*>(&k1024_bits);
-    uint32_t outw[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t lo = __byte_perm(words[i], 0x64646464u, 0x4140), hi = __byte_perm(words[i], 0x64646464u, 0x4342);
@@ -234,6 +282,12 @@ __device__ __forceinline__ void dequant_piece_f16(uint4 w, unsigned short scale_
         outw[2 * i] = *reinterpret_cast<const uint32_t*>(&x01);
         outw[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&x23);
     }
+}
+// ... and store them as two 16-byte chunks of a swizzled shared-memory tile row
+__device__ __forceinline__ void dequant_piece_f16(uint4 w, unsigned short scale_bits, unsigned short zp_bits,
+                                                  uint8_t* row, int c16, int token) {
+    uint32_t outw[8];
+    dequant16_f16(w, scale_bits, zp_bits, outw);
     // the piece covers d = 16*c16 .. +15: chunks 2*c16 and 2*c16+1 of the 128-wide row, 8 chunks per 64-wide panel
     uint8_t* panel = row + (c16 >> 2) * kPanel;
     const int cp = (2 * c16) & 7;
@@ -241,8 +295,56 @@ __device__ __forceinline__ void dequant_piece_f16(uint4 w, unsigned short scale_
     *reinterpret_cast<uint4*>(panel + (((cp + 1) ^ (token & 7)) << 4)) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
 }
 
-template <bool kBf16, bool kPaged>
-__global__ void __launch_bounds__(kPaged ? kThreadsPaged : kThreadsDense, 1)
+// De-quantise the contexts of the step's multi-token sequences into the f16 scratch [Hkv][rows][128] (K and V each):
+// one CTA per (16 scratch rows, KV head), thread = (token, 16-byte piece) for K and again for V.  Rows past a
+// sequence's context (its range is rounded up to 128 rows) become zeros, so a tile that reaches past the context
+// holds nothing that could turn 0 * x into NaN.
+__global__ void __launch_bounds__(128) paged_gather_kernel(const PagedTables t, const uint8_t* k_cache, const uint8_t* v_cache,
+                                                           const int Hkv, const int* kv_base, const int* owner,
+                                                           const int scratch_rows, uint16_t* k_out, uint16_t* v_out,
+                                                           int32_t* status) {
+    const int row0 = blockIdx.x * 16, hk = blockIdx.y;
+    const int seq = owner[row0 / 128];
+    if (seq < 0) return;
+    const int tok = threadIdx.x >> 3, c16 = threadIdx.x & 7;
+    const int pos = row0 - kv_base[seq] + tok;  // position inside the sequence
+    const int qlen = t.subsequence_begins[seq + 1] - t.subsequence_begins[seq];
+    const int ctx = t.past_lens[seq] + qlen;
+    uint4 wk = make_uint4(0u, 0u, 0u, 0u), wv = wk;
+    unsigned short sck = 0, zpk = 0, scv = 0, zpv = 0;
+    if (pos < ctx) {
+        const int lb = pos >> 4;
+        int phys = -1;
+        if (lb < t.block_indices_begins[seq + 1] - t.block_indices_begins[seq]) phys = t.block_indices[t.block_indices_begins[seq] + lb];
+        if (phys < 0 || phys >= t.num_blocks_total) {
+            report(status, B2A_DEV_BAD_BLOCK);
+        } else {
+            const size_t chunk = (static_cast<size_t>(phys) * Hkv + hk) * kCacheChunk;
+            const int tb = pos & 15;
+            wk = *reinterpret_cast<const uint4*>(k_cache + chunk + tb * 128 + c16 * 16);
+            wv = *reinterpret_cast<const uint4*>(v_cache + chunk + tb * 128 + c16 * 16);
+            const unsigned short* mk = reinterpret_cast<const unsigned short*>(k_cache + chunk + 2048);
+            const unsigned short* mv = reinterpret_cast<const unsigned short*>(v_cache + chunk + 2048);
+            sck = mk[tb];
+            zpk = mk[16 + tb];
+            scv = mv[tb];
+            zpv = mv[16 + tb];
+        }
+    }
+    const size_t at = (static_cast<size_t>(hk) * scratch_rows + row0 + tok) * kHeadDim + c16 * 16;
+    uint32_t o[8];
+    dequant16_f16(wk, sck, zpk, o);
+    *reinterpret_cast<uint4*>(k_out + at) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(k_out + at + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+    dequant16_f16(wv, scv, zpv, o);
+    *reinterpret_cast<uint4*>(v_out + at) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(v_out + at + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// kMode: 0 dense tensors; 1 paged, K/V de-quantised by producer warps inside the kernel; 2 paged, K/V de-quantised
+// beforehand into per-sequence row ranges of an f16 scratch (paged_gather_kernel) and staged by TMA like dense ones
+template <bool kBf16, int kMode>
+__global__ void __launch_bounds__(kMode == 1 ? kThreadsPaged : kThreadsDense, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p,
                const __grid_constant__ TcPeers peers) {
@@ -256,54 +358,69 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 6 * kTile + kStageOut + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 6 * kTile + kStageOut + kNumBars * 8 + 8);
     auto BAR = [&](int i) { return bars + 8u * static_cast<uint32_t>(i); };
+    constexpr bool kPaged = kMode != 0, kDequant = kMode == 1, kGathered = kMode == 2;
     constexpr bool kKvBf16 = kPaged ? false : kBf16;  // element format of the K/V tiles and of P
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- work items.  An item is a pair of tiles of one KV head.  Rows are numbered inside the sequence (paged) or
     // the tensor (dense); `pos_base` is the key position the first row of the problem may see up to, `kv_limit` the
-    // number of keys that exist.  Paged mode: one item per CTA, taken from the device-built list.  Dense mode: the
-    // CTA is persistent; the items, heaviest (late row blocks) first, are dealt to the CTAs in snake order (round
-    // k forwards, round k+1 backwards), which evens out the causal imbalance without any shared counter.
+    // number of keys that exist.  The CTA is persistent (except with in-kernel de-quantisation: one item per CTA):
+    // the items, heaviest first - late row blocks in dense mode, the weight-sorted device-built list in paged mode -
+    // are dealt to the CTAs in snake order (round k forwards, round k+1 backwards), which evens out the causal
+    // imbalance without any shared counter.  Every role calls get_item for itself, so the per-sequence values
+    // below are private to the calling thread and follow its own progress through the items.
     struct Item {
         int b, hk, row0A, row0B, headA, headB, nkvA, nkvB, nmax;
     };
-    int seq = 0, tok_base = 0, nrows_total, pos_base = 0, kv_limit;
-    bool causal;
-    int pair_in_seq = 0;
+    int seq = 0, tok_base = 0, nrows_total = 0, pos_base = 0, kv_limit = 0;
+    bool causal = true;
+    int nrb = 0, tiles = 0, pairs = 0, total_items = 0;
     if constexpr (kPaged) {
-        if (static_cast<int>(blockIdx.x) >= p.plan[0]) return;  // the grid is a bound on the number of items
-        seq = p.plan[kPlanHeaderInts + 2 * blockIdx.x];
-        pair_in_seq = p.plan[kPlanHeaderInts + 2 * blockIdx.x + 1];
-        tok_base = p.t.subsequence_begins[seq];
-        nrows_total = p.t.subsequence_begins[seq + 1] - tok_base;
-        if (nrows_total < 2) return;  // decode rows and idle sequences belong to the decode kernel
-        pos_base = p.t.past_lens[seq];
-        kv_limit = pos_base + nrows_total;
-        causal = true;
-        const int nblk = (kv_limit + 15) / 16;
-        if (pos_base < 0 || tok_base < 0 || tok_base + nrows_total > p.t.num_tokens ||
-            nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
-            if (threadIdx.x == 0) report(p.status, B2A_DEV_BAD_LEN);
-            return;
-        }
+        total_items = p.plan[0] * p.Hkv;  // the grid is only a bound on the number of items
+        if (kDequant && static_cast<int>(blockIdx.x * gridDim.y + blockIdx.y) >= total_items) return;
     } else {
         nrows_total = p.Sq;
         kv_limit = p.Skv;
         causal = p.causal != 0;
+        nrb = (nrows_total + kBM - 1) / kBM;
+        tiles = nrb * p.G;
+        pairs = (tiles + 1) / 2;
+        total_items = pairs * p.B * p.Hkv;  // the launcher keeps this below 2^31
     }
-    const int nrb = (nrows_total + kBM - 1) / kBM;
-    const int tiles = nrb * p.G;
-    const int pairs = (tiles + 1) / 2;
-    if (kPaged && (pair_in_seq < 0 || pair_in_seq >= pairs)) return;
-    const int total_items = kPaged ? 1 : pairs * p.B * p.Hkv;  // the launcher keeps this below 2^31
     auto get_item = [&](int k, Item& it) -> bool {  // the k-th item of this CTA
         int pair;
         if constexpr (kPaged) {
-            if (k > 0) return false;
-            pair = pair_in_seq;
+            int idx;
+            if constexpr (kDequant) {
+                if (k > 0) return false;
+                idx = static_cast<int>(blockIdx.x * gridDim.y + blockIdx.y);
+            } else {
+                const int ctas = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
+                idx = k * ctas + ((k & 1) ? ctas - 1 - me : me);
+            }
+            if (idx >= total_items) return false;
+            const int e = idx / p.Hkv;
             it.b = 0;
-            it.hk = blockIdx.y;
+            it.hk = idx - e * p.Hkv;
+            seq = p.plan[kPlanHeaderInts + 2 * e];
+            pair = p.plan[kPlanHeaderInts + 2 * e + 1];
+            tok_base = p.t.subsequence_begins[seq];
+            nrows_total = p.t.subsequence_begins[seq + 1] - tok_base;
+            pos_base = p.t.past_lens[seq];
+            kv_limit = pos_base + nrows_total;
+            nrb = (nrows_total + kBM - 1) / kBM;
+            tiles = nrb * p.G;
+            pairs = (tiles + 1) / 2;
+            const int nblk = (kv_limit + 15) / 16;
+            if (nrows_total < 2 || pos_base < 0 || tok_base < 0 || tok_base + nrows_total > p.t.num_tokens ||
+                nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq] || pair < 0 || pair >= pairs) {
+                // inconsistent tables: an empty item, reported once per item by the producer thread
+                if (threadIdx.x == 8 * 32) report(p.status, B2A_DEV_BAD_LEN);
+                it.hk = 0;
+                it.row0A = it.row0B = it.headA = it.headB = it.nkvA = it.nkvB = it.nmax = 0;
+                return true;
+            }
         } else {
             const int ctas = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
 #if B2A_TC_SNAKE
@@ -344,7 +461,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (i == P_READY || i == P_READY + 1 || i == P_HALF || i == P_HALF + 1) count = 128;
             if (i == Q_CONV || i == Q_CONV + 1) count = 128;
             if (i == Q_EMPTY || i == Q_EMPTY + 1) count = 1;
-            if (kPaged && (i == K_FULL || i == K_FULL + 1 || i == V_FULL || i == V_FULL + 1)) count = 128;
+            if (kDequant && (i == K_FULL || i == K_FULL + 1 || i == V_FULL || i == V_FULL + 1)) count = 128;
+            if (kGathered && (i == Q_CONV || i == Q_CONV + 1)) count = 64;  // converted by warps 10 and 11
             mbar_init(BAR(i), count);
         }
         *abort_flag = 0;
@@ -366,7 +484,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     if (warp >= 12) {
         // =============================== de-quantising K/V producers (paged) ===============================
-        if constexpr (kPaged) {
+        if constexpr (kDequant) {
             asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
             Item item;
             get_item(0, item);  // paged mode: exactly one item per CTA
@@ -467,12 +585,42 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
         }
     } else if (warp >= 10) {
-        // idle warps of the service warpgroup
+        // idle warps of the service warpgroup; with gathered K/V and bf16 queries they turn the Q tiles into f16 where
+        // they lie (the swizzle only permutes 16-byte chunks, so an element-wise pass keeps the layout)
+        if constexpr (kGathered && kBf16) {
+            Item item;
+            const int tp = static_cast<int>(threadIdx.x) - 320;  // 0..63
+            bool ok = true;
+            int qn[2] = {0, 0};  // Q tiles of each kind seen so far
+            for (int kk = 0; ok && get_item(kk, item); ++kk)
+#pragma unroll
+            for (int X = 0; X < 2; ++X) {
+                if ((X ? item.nkvB : item.nkvA) > 0) {
+                    ok = ok && __all_sync(0xffffffffu, mbar_wait(BAR(Q_FULL + X), qn[X] & 1, abort_flag));
+                    ++qn[X];
+                    if (ok) {
+                        uint4* tile = reinterpret_cast<uint4*>(gbase + X * kTile);
+                        for (int i = tp; i < kTile / 16; i += 64) {
+                            uint4 v = tile[i];
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+                                w[k] = pack2<false>(fminf(fmaxf(f.x, -65504.f), 65504.f), fminf(fmaxf(f.y, -65504.f), 65504.f));
+                            }
+                            tile[i] = v;
+                        }
+                        fence_proxy_async_smem();
+                        mbar_arrive(BAR(Q_CONV + X));
+                    }
+                }
+            }
+        }
     } else if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
             prefetch_tensormap(&tmQ);
-            if constexpr (!kPaged) {
+            if constexpr (!kDequant) {
                 prefetch_tensormap(&tmK);
                 prefetch_tensormap(&tmV);
             }
@@ -494,18 +642,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 };
                 load_q(0);
                 if (ok) load_q(1);
-                if constexpr (!kPaged) {
+                if constexpr (!kDequant) {
+                    // gathered mode: the sequence's keys start at row kv_row0 of the scratch, which is one [1, Hkv, rows, 128] tensor
+                    const int kv_row0 = kGathered ? p.kv_base[seq] : 0;
                     for (int j = 0; ok && j < it.nmax; ++j, ++g) {
                         const int st = g & 1, n = g >> 1;
                         if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) { ok = false; break; }
                         mbar_expect_tx(BAR(K_FULL + st), kTile);
-                        tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, j * kBN, it.hk, it.b);
-                        tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, j * kBN, it.hk, it.b);
+                        tma_load_4d(sK + st * kTile, &tmK, BAR(K_FULL + st), 0, kv_row0 + j * kBN, it.hk, it.b);
+                        tma_load_4d(sK + st * kTile + kPanel, &tmK, BAR(K_FULL + st), 64, kv_row0 + j * kBN, it.hk, it.b);
                         ++issued_k;
                         if (n > 0 && !mbar_wait(BAR(V_EMPTY + st), (n - 1) & 1, abort_flag)) { ok = false; break; }
                         mbar_expect_tx(BAR(V_FULL + st), kTile);
-                        tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, j * kBN, it.hk, it.b);
-                        tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, j * kBN, it.hk, it.b);
+                        tma_load_4d(sV + st * kTile, &tmV, BAR(V_FULL + st), 0, kv_row0 + j * kBN, it.hk, it.b);
+                        tma_load_4d(sV + st * kTile + kPanel, &tmV, BAR(V_FULL + st), 64, kv_row0 + j * kBN, it.hk, it.b);
                         ++issued_v;
                     }
                 }
@@ -553,6 +703,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             Item it;
             for (int k = 0; ok && get_item(k, it); ++k) {
                 const int nkvA = it.nkvA, nkvB = it.nkvB, nmax = it.nmax;
+                if (nmax == 0) continue;  // an item that was refused (inconsistent tables)
                 if (nkvA > 0) ok = ok && mbar_wait(BAR(kQReady + 0), qn[0] & 1, abort_flag);
                 if (nkvB > 0) ok = ok && mbar_wait(BAR(kQReady + 1), qn[1] & 1, abort_flag);
                 ok = ok && mbar_wait(BAR(K_FULL + (g0 & 1)), (g0 >> 1) & 1, abort_flag);
@@ -615,7 +766,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
     } else {
         // =============================== softmax + epilogue of tile X ===============================
-        if constexpr (kPaged) {
+        if constexpr (kDequant) {
             asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
         } else {
             asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
@@ -751,9 +902,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 // where the tile goes: worked out again here rather than kept in registers across the key loop
-                int k_again = k;
-                asm volatile("" : "+r"(k_again));
-                get_item(k_again, item);
+                if constexpr (!kPaged) {  // (paged items come from tables in global memory: those are kept)
+                    int k_again = k;
+                    asm volatile("" : "+r"(k_again));
+                    get_item(k_again, item);
+                }
                 const int row0 = X ? item.row0B : item.row0A, head = X ? item.headB : item.headA, b = item.b;
                 if constexpr (kPaged) {
                     // row-wise stores: rows past the sequence's end belong to other sequences and are dropped
@@ -980,7 +1133,7 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     if (sms <= 0) return B2A_ERR_CUDA;
     dim3 grid(static_cast<unsigned>(items < sms || B2A_TC_GRID_ALL ? items : sms));  // persistent CTAs, one per SM
     static bool configured[2][64] = {};
-    auto kern = bf16 ? attn_tc_kernel<true, false> : attn_tc_kernel<false, false>;
+    auto kern = bf16 ? attn_tc_kernel<true, 0> : attn_tc_kernel<false, 0>;
     const int rc = configure_once(kern, configured[bf16]);
     if (rc != B2A_OK) return rc;
     kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mo, p, peers);
@@ -1009,21 +1162,67 @@ static int paged_tc_capacity(const b2a_paged_desc& d) {
     return static_cast<int>(cap < 1 ? 1 : cap);
 }
 
-size_t paged_tc_plan_bytes(const b2a_paged_desc& d) {
-    return sizeof(int) * (kPlanHeaderInts + 2 * static_cast<size_t>(paged_tc_capacity(d)));
+// Layout of the prefill kernel's part of the workspace: [work list][kv_base per sequence][owner per 128-row group]
+// [K scratch][V scratch]; the last three only when the caller gave prefill_kv_tokens.
+namespace {
+struct TcWorkspace {
+    size_t kv_base_at, owner_at, k_at, v_at, total;
+    int rows, groups;
+};
+TcWorkspace tc_workspace(const b2a_paged_desc& d) {
+    auto up = [](size_t x, size_t a) { return (x + a - 1) / a * a; };
+    TcWorkspace w{};
+    size_t at = up(sizeof(int) * (kPlanHeaderInts + 2 * static_cast<size_t>(paged_tc_capacity(d))), 16);
+    if (d.prefill_kv_tokens > 0) {
+        w.rows = (d.prefill_kv_tokens + 127) / 128 * 128;
+        w.groups = w.rows / 128;
+        w.kv_base_at = at;
+        at = up(at + sizeof(int) * static_cast<size_t>(d.num_seqs), 16);
+        w.owner_at = at;
+        at = up(at + sizeof(int) * static_cast<size_t>(w.groups), 256);
+        const size_t scratch = static_cast<size_t>(d.Hkv) * w.rows * kHeadDim * 2;
+        w.k_at = at;
+        w.v_at = at + scratch;
+        at += 2 * scratch;
+    }
+    w.total = at;
+    return w;
 }
+}  // namespace
+
+size_t paged_tc_plan_bytes(const b2a_paged_desc& d) { return tc_workspace(d).total; }
 
 int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
                     const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream) {
     const bool bf16 = d.q_dtype == B2A_BF16;
     const int capacity = paged_tc_capacity(d);
-    paged_tc_plan_kernel<<<1, 256, 0, stream>>>(t, d.Hq / d.Hkv, capacity, static_cast<int*>(plan_ws), status);
+    const TcWorkspace w = tc_workspace(d);
+    const bool gathered = w.rows > 0;
+    char* ws = static_cast<char*>(plan_ws);
+    int* kv_base = gathered ? reinterpret_cast<int*>(ws + w.kv_base_at) : nullptr;
+    int* owner = gathered ? reinterpret_cast<int*>(ws + w.owner_at) : nullptr;
+    paged_tc_plan_kernel<<<1, 256, 0, stream>>>(t, d.Hq / d.Hkv, capacity, static_cast<int*>(plan_ws), status, kv_base,
+                                                owner, w.groups);
     if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
     // the step's query matrix [tokens, Hq*128] as a [1, Hq, tokens, 128] view
     const int64_t qs[4] = {static_cast<int64_t>(d.num_tokens) * d.Hq * kHeadDim, kHeadDim,
                            static_cast<int64_t>(d.Hq) * kHeadDim, 1};
-    CUtensorMap mq;
+    CUtensorMap mq, mk, mv;
     if (!make_map(&mq, query, bf16, 1, d.Hq, d.num_tokens, qs, 128)) return B2A_ERR_CUDA;
+    mk = mv = mq;  // not read unless K/V are gathered
+    if (gathered) {
+        uint16_t* ks = reinterpret_cast<uint16_t*>(ws + w.k_at);
+        uint16_t* vs = reinterpret_cast<uint16_t*>(ws + w.v_at);
+        paged_gather_kernel<<<dim3(w.rows / 16, d.Hkv), 128, 0, stream>>>(
+            t, static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), d.Hkv, kv_base, owner, w.rows,
+            ks, vs, status);
+        if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+        // the scratch as a [1, Hkv, rows, 128] f16 tensor
+        const int64_t ss[4] = {static_cast<int64_t>(d.Hkv) * w.rows * kHeadDim, static_cast<int64_t>(w.rows) * kHeadDim,
+                               kHeadDim, 1};
+        if (!make_map(&mk, ks, false, 1, d.Hkv, w.rows, ss, 128) || !make_map(&mv, vs, false, 1, d.Hkv, w.rows, ss, 128))
+            return B2A_ERR_CUDA;
+    }
     TcParams p{};
     p.B = 1; p.Hq = d.Hq; p.Hkv = d.Hkv; p.G = d.Hq / d.Hkv; p.Sq = 0; p.Skv = 0;
     p.causal = 1;
@@ -1034,13 +1233,26 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     p.t = t;
     p.out = out;
     p.plan = static_cast<const int*>(plan_ws);
+    p.kv_base = kv_base;
     dim3 grid(capacity, d.Hkv, 1);
-    static bool configured[2][64] = {};
-    auto kern = bf16 ? attn_tc_kernel<true, true> : attn_tc_kernel<false, true>;
-    const int rc = configure_once(kern, configured[bf16]);
-    if (rc != B2A_OK) return rc;
     TcPeers peers{};
-    kern<<<grid, kThreadsPaged, kSmemBytes, stream>>>(mq, mq, mq, mq, p, peers);  // only the Q map is read in paged mode
+    if (gathered) {
+        const int sms = device_sm_count();
+        if (sms <= 0) return B2A_ERR_CUDA;
+        const long long bound = static_cast<long long>(capacity) * d.Hkv;
+        grid = dim3(static_cast<unsigned>(bound < sms ? bound : sms));  // persistent CTAs over the sorted list
+        static bool configured[2][64] = {};
+        auto kern = bf16 ? attn_tc_kernel<true, 2> : attn_tc_kernel<false, 2>;
+        const int rc = configure_once(kern, configured[bf16]);
+        if (rc != B2A_OK) return rc;
+        kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mq, p, peers);
+    } else {
+        static bool configured[2][64] = {};
+        auto kern = bf16 ? attn_tc_kernel<true, 1> : attn_tc_kernel<false, 1>;
+        const int rc = configure_once(kern, configured[bf16]);
+        if (rc != B2A_OK) return rc;
+        kern<<<grid, kThreadsPaged, kSmemBytes, stream>>>(mq, mq, mq, mq, p, peers);  // only the Q map is read
+    }
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 

@@ -88,10 +88,14 @@ int KvBlockManager::schedule_step(const int64_t* ids, const int32_t* q_lens, int
         out.block_indices_begins[static_cast<size_t>(i) + 1] = static_cast<int32_t>(out.block_indices.size());
         out.max_context_len = std::max(out.max_context_len, new_len);
         out.max_q_len = std::max(out.max_q_len, q_lens[i]);
-        if (q_lens[i] >= 2) out.prefill_row_blocks += (q_lens[i] + 127) / 128;
+        if (q_lens[i] >= 2) {
+            out.prefill_row_blocks += (q_lens[i] + 127) / 128;
+            out.prefill_kv_tokens += (new_len + 127) / 128 * 128;
+        }
     }
     out.num_tokens = out.subsequence_begins[static_cast<size_t>(n)];
     last_prefill_row_blocks_ = out.prefill_row_blocks;
+    last_prefill_kv_tokens_ = out.prefill_kv_tokens;
     return B2A_OK;
 }
 
@@ -129,6 +133,7 @@ int32_t b2a_kvmgr_free_blocks(const b2a_kvmgr* m) { return m ? m->impl.free_bloc
 int32_t b2a_kvmgr_sequence_len(const b2a_kvmgr* m, int64_t seq_id) { return m ? m->impl.sequence_len(seq_id) : -1; }
 
 int32_t b2a_kvmgr_last_prefill_row_blocks(const b2a_kvmgr* m) { return m ? m->impl.last_prefill_row_blocks() : 0; }
+int32_t b2a_kvmgr_last_prefill_kv_tokens(const b2a_kvmgr* m) { return m ? m->impl.last_prefill_kv_tokens() : 0; }
 
 int b2a_kvmgr_schedule_step(b2a_kvmgr* m, const int64_t* seq_ids, const int32_t* q_lens, int32_t n,
                             int32_t* past_lens, int32_t* subsequence_begins, int32_t* block_indices,

@@ -20,6 +20,7 @@ struct StepTables {
     int32_t max_context_len = 0;
     int32_t max_q_len = 0;
     int32_t prefill_row_blocks = 0;  // sum of ceil(q_len / 128) over the sequences with two or more new tokens
+    int32_t prefill_kv_tokens = 0;   // sum of their context lengths, each rounded up to 128
     int32_t num_tokens = 0;
 };
 
@@ -36,6 +37,7 @@ public:
     bool free_sequence(int64_t id);  // false if unknown; its blocks return to the free list
     int32_t sequence_len(int64_t id) const;  // -1 if unknown
     int32_t last_prefill_row_blocks() const { return last_prefill_row_blocks_; }  // of the last scheduled step
+    int32_t last_prefill_kv_tokens() const { return last_prefill_kv_tokens_; }
     const std::vector<int32_t>* sequence_blocks(int64_t id) const;
 
     // Blocks that scheduling q_lens[i] new tokens for ids[i] would take from the free list; -1 if an id is unknown
@@ -53,6 +55,7 @@ private:
     };
     int32_t num_blocks_, block_size_;
     int32_t last_prefill_row_blocks_ = 0;
+    int32_t last_prefill_kv_tokens_ = 0;
     std::vector<int32_t> free_;  // stack: back() is handed out next
     std::unordered_map<int64_t, Seq> seqs_;
 };

@@ -188,7 +188,8 @@ class PagedKvCache:
 
 
 def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int, max_context_len: int,
-                max_q_len: int, scale: Optional[float], sliding_window: int, prefill_row_blocks: int = 0) -> PagedDesc:
+                max_q_len: int, scale: Optional[float], sliding_window: int, prefill_row_blocks: int = 0,
+                prefill_kv_tokens: int = 0) -> PagedDesc:
     d = PagedDesc()
     d.q_dtype = _dtype_code(q_dtype)
     d.kv_dtype = _dtype_code(cache.kv_dtype)
@@ -198,6 +199,7 @@ def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens
     d.scale = 0.0 if scale is None else float(scale)
     d.sliding_window = int(sliding_window)
     d.prefill_row_blocks = int(prefill_row_blocks)
+    d.prefill_kv_tokens = int(prefill_kv_tokens)
     return d
 
 
@@ -225,9 +227,10 @@ def paged_kv_store(key: torch.Tensor, value: torch.Tensor, cache: PagedKvCache, 
 
 
 def paged_workspace_bytes(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int,
-                          max_context_len: int, max_q_len: int, prefill_row_blocks: int = 0) -> int:
+                          max_context_len: int, max_q_len: int, prefill_row_blocks: int = 0,
+                          prefill_kv_tokens: int = 0) -> int:
     d = _paged_desc(q_dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, None, 0,
-                    prefill_row_blocks)
+                    prefill_row_blocks, prefill_kv_tokens)
     ws = C.c_size_t(0)
     check(_lib.load().b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
     return ws.value
@@ -237,10 +240,12 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
                     block_indices_begins, hq: int, max_context_len: int, max_q_len: int,
                     scale: Optional[float] = None, sliding_window: int = 0, out: Optional[torch.Tensor] = None,
                     workspace: Optional[torch.Tensor] = None, stream=None,
-                    status: Optional[torch.Tensor] = None, prefill_row_blocks: int = 0) -> torch.Tensor:
+                    status: Optional[torch.Tensor] = None, prefill_row_blocks: int = 0,
+                    prefill_kv_tokens: int = 0) -> torch.Tensor:
     """Attention of query [tokens, Hq*D] over the cache; returns [tokens, Hq*Dv].
 
-    ``prefill_row_blocks`` is the optional scheduler hint of ``b2a_paged_desc`` (``KvBlockManager`` reports it)."""
+    ``prefill_row_blocks`` and ``prefill_kv_tokens`` are the optional scheduler hints of ``b2a_paged_desc``
+    (``KvBlockManager`` reports both); the second lets a mixed step de-quantise its prefill contexts once."""
     _require_cuda(query, cache.k, cache.v, past_lens, subsequence_begins, block_indices, block_indices_begins, out)
     if not query.is_contiguous() or query.shape[1] != hq * cache.d:
         raise ValueError("query must be dense [tokens, Hq*D]")
@@ -248,7 +253,7 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
     if out is None:
         out = torch.empty((num_tokens, hq * cache.dv), dtype=query.dtype, device=query.device)
     d = _paged_desc(query.dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, scale, sliding_window,
-                    prefill_row_blocks)
+                    prefill_row_blocks, prefill_kv_tokens)
     lib = _lib.load()
     ws = C.c_size_t(0)
     check(lib.b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
@@ -343,6 +348,10 @@ class KvBlockManager:
         return self._lib.b2a_kvmgr_sequence_len(self._h, seq_id)
 
     @property
+    def last_prefill_kv_tokens(self) -> int:
+        """``prefill_kv_tokens`` hint of the step scheduled last."""
+        return self._lib.b2a_kvmgr_last_prefill_kv_tokens(self._h)
+
     def last_prefill_row_blocks(self) -> int:
         """``prefill_row_blocks`` hint of the step scheduled last."""
         return self._lib.b2a_kvmgr_last_prefill_row_blocks(self._h)

@@ -285,6 +285,21 @@ def test_paged_prefill_parity(b2a, dtype):
                               max_context_len=int((past + qlen).max()), max_q_len=int(qlen.max()), status=status)
     assert int(status.item()) == 0
     assert_close(out, w.reference(q.float().numpy()), dtype)
+    # with the scheduler's hints the prefill contexts are de-quantised once into a scratch and staged by TMA
+    ctx = past + qlen
+    hint_rb = int(sum((int(x) + 127) // 128 for x in qlen if x >= 2))
+    hint_kv = int(sum((int(c) + 127) // 128 * 128 for c, x in zip(ctx, qlen) if x >= 2))
+    out2 = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=hq, max_context_len=int(ctx.max()),
+                               max_q_len=int(qlen.max()), status=status, prefill_row_blocks=hint_rb,
+                               prefill_kv_tokens=hint_kv)
+    assert int(status.item()) == 0
+    assert_close(out2, w.reference(q.float().numpy()), dtype)
+    assert torch.equal(out2, out)  # same de-quantised values, same kernel body
+    # a hint that is too small is reported, not followed
+    b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), hq=hq, max_context_len=int(ctx.max()),
+                        max_q_len=int(qlen.max()), status=status, prefill_row_blocks=hint_rb,
+                        prefill_kv_tokens=hint_kv - 128)
+    assert int(status.item()) & 4  # B2A_DEV_BAD_LEN
 
 
 def test_config4_mixed_step(b2a):
