@@ -140,11 +140,18 @@ PagedAttentionOp::PagedAttentionOp(const CreationContext& context, const NodeOp&
     workspace_bytes_ = WorkspaceBound();
 }
 
-void PagedAttentionOp::SetCapacity(int max_seqs, int max_context_len) {
-    if (max_seqs <= 0 || max_context_len <= 0) ov::throw_ov_exception("PagedAttentionExtension: bad capacity");
+void PagedAttentionOp::SetCapacity(int max_seqs, int max_context_len, int max_prefill_kv_tokens) {
+    if (max_seqs <= 0 || max_context_len <= 0 || max_prefill_kv_tokens < 0)
+        ov::throw_ov_exception("PagedAttentionExtension: bad capacity");
     max_seqs_ = max_seqs;
     max_context_len_ = max_context_len;
+    max_prefill_kv_tokens_ = max_prefill_kv_tokens;
     workspace_bytes_ = WorkspaceBound();
+}
+
+void PagedAttentionOp::SetStepHints(int32_t prefill_row_blocks, int32_t prefill_kv_tokens) {
+    hint_row_blocks_ = prefill_row_blocks > 0 ? prefill_row_blocks : 0;
+    hint_kv_tokens_ = prefill_kv_tokens > 0 && prefill_kv_tokens <= max_prefill_kv_tokens_ ? prefill_kv_tokens : 0;
 }
 
 size_t PagedAttentionOp::WorkspaceBound() const {
@@ -157,6 +164,7 @@ size_t PagedAttentionOp::WorkspaceBound() const {
         d.num_tokens = max_context_len_ + max_seqs_;
         d.max_context_len = max_context_len_;
         d.max_q_len = 2;
+        d.prefill_kv_tokens = max_prefill_kv_tokens_;
         size_t bytes = 0;
         throwIfError(b2a_paged_workspace_bytes(&d, 0, &bytes), "b2a_paged_workspace_bytes");
         worst = std::max(worst, bytes);
@@ -186,6 +194,8 @@ void PagedAttentionOp::Execute(const InferenceRequestContext& context, Inputs in
         ov::throw_ov_exception("PagedAttentionExtension: more tokens in one step than the capacity");
     d.max_context_len = max_context_len_;
     d.max_q_len = d.num_tokens == d.num_seqs ? 1 : d.num_tokens - d.num_seqs + 1;
+    d.prefill_row_blocks = hint_row_blocks_;
+    d.prefill_kv_tokens = hint_kv_tokens_;
     if (wb.mutable_buffers.size() < 2) ov::throw_ov_exception("PagedAttentionExtension: work buffers missing");
     auto stream = context.getThreadContext().stream().get();
     auto* status = static_cast<int32_t*>(wb.mutable_buffers[1].get());

@@ -50,13 +50,19 @@ public:
     CudaGraphCompatibility GetCudaGraphCompatibilityImpl() const override { return CudaGraphCompatibility::FULL; }
     WorkbufferRequest GetWorkBufferRequest() const override;
     // Capacity the grids and the workspace are sized for; defaults to the static operand shapes.
-    void SetCapacity(int max_seqs, int max_context_len);
+    // max_prefill_kv_tokens > 0 also reserves the f16 scratch that lets a step de-quantise the contexts of its
+    // multi-token sequences once (up to that many context tokens, each sequence rounded up to 128).
+    void SetCapacity(int max_seqs, int max_context_len, int max_prefill_kv_tokens = 0);
+    // What the scheduler knows about the next step (KvBlockManager::StepTables carries both); zeros = unknown.
+    // Hints beyond the reserved capacity are ignored.
+    void SetStepHints(int32_t prefill_row_blocks, int32_t prefill_kv_tokens);
     const b2a_paged_desc& desc() const { return desc_; }
 
 private:
     size_t WorkspaceBound() const;
     b2a_paged_desc desc_{};  // num_seqs / num_tokens hold the static extents (0 = dynamic)
-    int max_seqs_ = 0, max_context_len_ = 0;
+    int max_seqs_ = 0, max_context_len_ = 0, max_prefill_kv_tokens_ = 0;
+    int32_t hint_row_blocks_ = 0, hint_kv_tokens_ = 0;
     size_t workspace_bytes_ = 0;
 };
 

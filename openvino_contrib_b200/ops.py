@@ -284,6 +284,11 @@ class PagedAttentionOp:
                  max_seqs: int = 256, max_context_len: int = 32768):
         self.hq, self.hkv, self.d, self.block_size, self.kv_dtype = hq, hkv, d, block_size, kv_dtype
         self.max_seqs, self.max_context_len = max_seqs, max_context_len
+        self._hint_row_blocks = self._hint_kv_tokens = 0
+
+    def SetStepHints(self, prefill_row_blocks: int = 0, prefill_kv_tokens: int = 0) -> None:
+        """What the scheduler knows about the next step (``KvBlockManager`` reports both); zeros = unknown."""
+        self._hint_row_blocks, self._hint_kv_tokens = max(0, int(prefill_row_blocks)), max(0, int(prefill_kv_tokens))
 
     def GetCudaGraphCompatibility(self) -> str:
         return "FULL"
@@ -313,7 +318,8 @@ class PagedAttentionOp:
         sw = int(sliding_window.item()) if isinstance(sliding_window, torch.Tensor) else int(sliding_window or 0)
         paged_attention(query, cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
                         self.hq, max_ctx, max_q_len, sc, sw, out=outputs[0], workspace=ws, stream=stream,
-                        status=status)
+                        status=status, prefill_row_blocks=self._hint_row_blocks,
+                        prefill_kv_tokens=self._hint_kv_tokens)
 
 
 # ------------------------------------------------------------------------------------------------------------

@@ -327,3 +327,11 @@ def test_config4_mixed_step(b2a):
     assert int(status.item()) == 0
     assert np.array_equal(cache.k.cpu().numpy(), ref_k) and np.array_equal(cache.v.cpu().numpy(), ref_v)
     assert_close(out, ref, torch.bfloat16)
+    # the same step with the scheduler's hints (contexts de-quantised once): storing the same rows again leaves
+    # the pools as they are, and the output is the same to the bit
+    op.SetStepHints(prefill_row_blocks=8 * 8, prefill_kv_tokens=8 * 1024)
+    out2 = torch.empty_like(out)
+    op.Execute([q.cuda(), new_k.cuda(), new_v.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, 4096],
+               [out2], status=status)
+    assert int(status.item()) == 0
+    assert np.array_equal(cache.k.cpu().numpy(), ref_k) and torch.equal(out2, out)
