@@ -1,39 +1,48 @@
 // Fused attention for prefill on the 5th-generation tensor core: S = Q K^T and O = P V as tcgen05.mma with
 // accumulators in tensor memory, online softmax in registers.  f16 / bf16, D = Dv = 128, grouped-query heads.
-// Two front ends share one kernel body:
-//   * dense  (ScaledDotProductAttention): Q, K, V are [B, H, S, 128] tensors, causal or unmasked; K/V tiles are
+// Three front ends share one kernel body (template parameter kMode):
+//   0 dense  (ScaledDotProductAttention): Q, K, V are [B, H, S, 128] tensors, causal or unmasked; K/V tiles are
 //     staged by TMA;
-//   * paged  (PagedAttentionExtension, sequences with two or more new tokens): Q rows come from the step's
-//     [tokens, Hq*128] matrix, K/V from the u8 block pool through the block table - a producer warpgroup
-//     de-quantises 128-token tiles ((code - zp) * scale, f16: queries, keys, values and P are all f16 in this mode)
-//     straight into the
-//     swizzled shared-memory layout the tensor core reads.  Query token i of a sequence sees cache positions
-//     0 .. past_len + i.
+//   1 paged, de-quantising in the kernel (PagedAttentionExtension, sequences with two or more new tokens): Q rows
+//     come from the step's [tokens, Hq*128] matrix, K/V from the u8 block pool through the block table - a producer
+//     warpgroup de-quantises 128-token tiles ((code - zp) * scale, f16: queries, keys, values and P are all f16 in
+//     the paged modes) straight into the swizzled shared-memory layout the tensor core reads;
+//   2 paged, gathered: paged_gather_kernel has de-quantised the contexts of the step's multi-token sequences once
+//     into an f16 scratch (a row range per sequence), and K/V tiles are staged from there by TMA like dense ones.
+//     Taken when the caller passes the scheduler's bound on those contexts (b2a_paged_desc.prefill_kv_tokens).
+//   In the paged modes query token i of a sequence sees cache positions 0 .. past_len + i.
 //
-// One CTA owns TWO 128-row query tiles of one KV head and walks the keys 128 at a time:
+// Work is cut into items: TWO 128-row query tiles of one KV head, walked over the keys 128 at a time.  CTAs are
+// persistent (one per SM; mode 1 keeps one item per CTA): the items, heaviest first, are dealt in snake order.
 //   warps 0-3   softmax of tile A: thread = query row = TMEM lane.  Reads S_A (tcgen05.ld), keeps the running max
 //               and sum, writes P_A = exp2(S*c - m) as 16-bit pairs over the first half of S_A's columns
 //               (tcgen05.st) and signals the MMA issuer after the first 64 keys and again after all 128; rescales
-//               O_A in TMEM when the maximum moved; finally normalises O_A and stores it (TMA stores from shared
-//               memory, one [64 x 32] box per warp and panel, in dense mode; row-wise stores in paged mode).
+//               O_A in TMEM when the maximum moved; finally normalises O_A and stores it (dense: through a
+//               [32 x 64] staging slab per warp and one TMA store per slab - to every rank's buffer when the heads
+//               are sharded; paged: row-wise stores).
 //   warps 4-7   the same for tile B.
-//   warp  8     TMA producer (one lane): Q tiles once, and in dense mode K_j and V_j into two-stage rings.
+//   warp  8     TMA producer (one lane): the Q tiles of an item as soon as the previous item's last QK^T has
+//               completed, and (modes 0, 2) K_j and V_j into two-stage rings that run on across items.
 //   warp  9     MMA issuer (one lane): S_X(j) = Q_X K_j^T (A and B from shared memory, K-major, 128-byte swizzle),
 //               O_X += P_X(j) V_j (A from TMEM, B from shared memory, MN-major).  Order per step:
 //               PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1) - while one tile's softmax runs, the tensor core works on
-//               the other tile.  The warp also owns the TMEM allocation (all 512 columns: S_A S_B O_A O_B).
-//   warps 10-11 idle (they complete the service warpgroup whose registers are handed to the softmax groups).
-//   warps 12-15 paged mode only: the de-quantising K/V producers.
+//               the other tile.  Descriptors are put together at the point of issue (tcgen05.cuh) so the thread
+//               stays within its 56 registers.  The warp also owns the TMEM allocation (all 512 columns: S_A S_B
+//               O_A O_B).
+//   warps 10-11 complete the service warpgroup whose registers are handed to the softmax groups; in mode 2 with
+//               bf16 queries they convert the Q tiles to f16 in shared memory.
+//   warps 12-15 mode 1 only: the de-quantising K/V producers.
 // The two tiles are consecutive entries of the list (row block, query head of the group), query heads fastest, so
 // with an even group size both tiles cover the same rows of two heads that share K/V, and the causal structure of
-// the pair is identical.  Heavy (late) row blocks are scheduled first.
+// the pair is identical.
 //
 // The maximum used for P is allowed to lag: O and the sum are rescaled only when some row's maximum grew by more
 // than 2^8, so P stays below 256 and the result is exact after the final division.
 //
 // Every mbarrier wait is bounded (tcgen05.cuh); on a timeout the CTA raises an abort flag, all roles leave their
 // loops, outstanding copies and MMAs are drained with bounded waits, TMEM is freed and the status word gets
-// B2A_DEV_TIMEOUT.
+// B2A_DEV_TIMEOUT.  All barrier phases are derived from running counts (K/V ring position, steps of a tile, Q tiles
+// loaded) so that they carry over from one item to the next.
 #include "launch.cuh"
 #include "tcgen05.cuh"
 
