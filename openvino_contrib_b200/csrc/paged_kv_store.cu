@@ -25,6 +25,25 @@ struct StoreParams {
     int32_t* status;
 };
 
+// Sequence of token `tok`: the last s with subsequence_begins[s] <= tok, found by the whole warp - every round the 32
+// lanes probe 32 evenly spaced entries of the remaining range and a ballot picks the segment, so 65535 sequences take
+// four dependent loads instead of sixteen.  Returns -1 for a token outside the scheduled range.
+__device__ __forceinline__ int find_sequence(const PagedTables& t, int tok, int lane) {
+    if (tok >= t.subsequence_begins[t.num_seqs] || tok < t.subsequence_begins[0]) return -1;
+    int lo = 0, hi = t.num_seqs;  // invariant: begins[lo] <= tok < begins[hi]
+    while (hi - lo > 1) {
+        const int step = (hi - lo + 31) / 32;
+        const int probe = lo + lane * step;  // lane 0 probes lo itself
+        const bool le = probe < hi && t.subsequence_begins[probe] <= tok;
+        const unsigned m = __ballot_sync(0xffffffffu, le);  // a prefix of the lanes (begins are non-decreasing)
+        const int last = 31 - __clz(static_cast<int>(m));
+        const int nlo = lo + last * step;
+        hi = min(hi, nlo + step);
+        lo = nlo;
+    }
+    return lo;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const StoreParams p) {
     const int lane = threadIdx.x & 31;
@@ -36,14 +55,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
     const int tok = static_cast<int>(item / (2LL * p.Hkv));
     const int D = which ? p.Dv : p.D;
 
-    // sequence of this token: last s with subsequence_begins[s] <= tok
-    int lo = 0, hi = p.t.num_seqs;  // invariant: begins[lo] <= tok < begins[hi]
-    if (tok >= p.t.subsequence_begins[p.t.num_seqs] || tok < p.t.subsequence_begins[0]) return;  // not scheduled
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (p.t.subsequence_begins[mid] <= tok) lo = mid; else hi = mid;
-    }
-    const int seq = lo;
+    const int seq = find_sequence(p.t, tok, lane);
+    if (seq < 0) return;  // not scheduled
     const int pos = p.t.past_lens[seq] + (tok - p.t.subsequence_begins[seq]);
     const int bs = p.t.block_size;
     const int nblk_seq = p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq];
@@ -127,6 +140,108 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
     }
 }
 
+// The common geometry (u8 cache, D = Dv = 128, 16-bit rows) with one warp per TOKEN: the walk through the step tables
+// is paid once for the token's 2*Hkv rows, and a row is handled by EIGHT lanes (16 values each: two 16-byte loads,
+// one 16-byte store of codes), so one pass of the warp quantises four rows - the per-row work (min/max reduction,
+// now three shuffle steps, the two scalar divisions, addressing) is issued once for four rows.  Same arithmetic as
+// above, operation for operation, except that x / s for the row's values uses one reciprocal (see below).
+template <typename T>
+__device__ __forceinline__ float bits_to_f32(uint32_t h16);
+template <>
+__device__ __forceinline__ float bits_to_f32<__half>(uint32_t h16) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
+}
+template <>
+__device__ __forceinline__ float bits_to_f32<__nv_bfloat16>(uint32_t h16) {
+    return __uint_as_float(h16 << 16);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kernel(const StoreParams p) {
+    constexpr int D = 128;
+    const int lane = threadIdx.x & 31, l8 = lane & 7, rg = lane >> 3;
+    const int tok = static_cast<int>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    if (tok >= p.t.num_tokens) return;
+    const int seq = find_sequence(p.t, tok, lane);
+    if (seq < 0) return;  // not scheduled
+    const int pos = p.t.past_lens[seq] + (tok - p.t.subsequence_begins[seq]);
+    const int bs = p.t.block_size;
+    const int nblk_seq = p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq];
+    if (pos < 0 || pos / bs >= nblk_seq) {
+        if (lane == 0) report(p.status, B2A_DEV_BAD_LEN);
+        return;
+    }
+    const int blk = p.t.block_indices[p.t.block_indices_begins[seq] + pos / bs];
+    if (blk < 0 || blk >= p.t.num_blocks_total) {
+        if (lane == 0) report(p.status, B2A_DEV_BAD_BLOCK);
+        return;
+    }
+    const int slot = pos % bs;
+    const size_t chunk_bytes = u8_chunk_bytes(bs, D);
+    const int rows = 2 * p.Hkv;  // row r: head r >> 1, key (0) or value (1)
+    for (int r0 = 0; r0 < rows; r0 += 4) {
+        const int r = r0 + rg;
+        const bool live = r < rows;  // whole 8-lane groups are live or not: the shuffles below stay inside a group
+        uint4 raw0 = make_uint4(0u, 0u, 0u, 0u), raw1 = raw0;
+        if (live) {
+            const uint4* src = reinterpret_cast<const uint4*>(
+                reinterpret_cast<const T*>((r & 1) ? p.value : p.key) + (static_cast<size_t>(tok) * p.Hkv + (r >> 1)) * D);
+            raw0 = src[2 * l8];
+            raw1 = src[2 * l8 + 1];
+        }
+        const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+        float xv[16];
+        float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            xv[2 * i] = bits_to_f32<T>(w[i] & 0xffffu);
+            xv[2 * i + 1] = bits_to_f32<T>(w[i] >> 16);
+            mn = fminf(mn, fminf(xv[2 * i], xv[2 * i + 1]));
+            mx = fmaxf(mx, fmaxf(xv[2 * i], xv[2 * i + 1]));
+        }
+#pragma unroll
+        for (int o = 1; o <= 4; o <<= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        }
+        __half s16 = __float2half_rn(__fdiv_rn(__fsub_rn(mx, mn), 255.0f));
+        float sf = __half2float(s16);
+        if (sf == 0.f || isinf(sf) || isnan(sf)) {
+            s16 = __float2half_rn(1.0f);
+            sf = 1.0f;
+        }
+        const __half z16 = __float2half_rn(__fdiv_rn(-mn, sf));
+        const float zf = __half2float(z16);
+        // x / s for the row's values with ONE reciprocal: q0 = x * r, then one Newton step in fused arithmetic.
+        // For a scale that is an f16 value and x an f16 or bf16 value this equals the correctly rounded quotient in
+        // every case except |x| below 2^-116, which take the division itself (checked exhaustively on the CPU by
+        // oracle/div_by_scale_check.c).
+        const float rs = __frcp_rn(sf);
+        uint32_t packed[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            float q;
+            if (fabsf(xv[e]) < 1e-30f) {
+                q = __fdiv_rn(xv[e], sf);
+            } else {
+                const float q0 = __fmul_rn(xv[e], rs);
+                q = fabsf(q0) < INFINITY ? __fmaf_rn(__fmaf_rn(-sf, q0, xv[e]), rs, q0) : q0;
+            }
+            const float t = rintf(__fadd_rn(q, zf));
+            packed[e >> 2] |= static_cast<uint32_t>(fminf(fmaxf(t, 0.f), 255.f)) << (8 * (e & 3));
+        }
+        if (live) {
+            uint8_t* chunk = ((r & 1) ? p.v_cache : p.k_cache) + (static_cast<size_t>(blk) * p.Hkv + (r >> 1)) * chunk_bytes;
+            reinterpret_cast<uint4*>(chunk + slot * D)[l8] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            if (l8 == 0) {
+                __half* meta = reinterpret_cast<__half*>(chunk + bs * D);
+                meta[slot] = s16;
+                meta[bs + slot] = z16;
+            }
+        }
+    }
+}
+
 }  // namespace
 
 int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* value, void* k_cache, void* v_cache,
@@ -134,6 +249,14 @@ int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* 
     if (d.num_tokens == 0) return B2A_OK;
     StoreParams p{key, value, static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), t,
                   d.Hkv, d.D, d.Dv, d.kv_dtype, status};
+    auto al8 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (d.kv_dtype == B2A_U8 && d.D == 128 && d.Dv == 128 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) &&
+        al8(key) && al8(value)) {
+        const unsigned grid_t = static_cast<unsigned>((d.num_tokens + kWarpsPerCta - 1) / kWarpsPerCta);
+        if (d.q_dtype == B2A_F16) paged_kv_store_rows128_kernel<__half><<<grid_t, kWarpsPerCta * 32, 0, stream>>>(p);
+        else paged_kv_store_rows128_kernel<__nv_bfloat16><<<grid_t, kWarpsPerCta * 32, 0, stream>>>(p);
+        return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+    }
     const long long total = 2LL * d.num_tokens * d.Hkv;
     const unsigned grid = static_cast<unsigned>((total + kWarpsPerCta - 1) / kWarpsPerCta);
     switch (d.q_dtype) {

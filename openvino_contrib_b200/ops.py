@@ -124,6 +124,50 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[
     return out
 
 
+class HostSdpaPipeline:
+    """SDPA on HOST tensors (pinned memory), pipelined over the batch dimension.
+
+    What a plugin does for a model whose inputs and outputs live in host memory (``ParameterOp`` uploads, ``ResultOp``
+    downloads, modules/nvidia_plugin/src/ops/parameter.cpp:24-33 and result.cpp) - except that here the upload of
+    batch entry b+1, the kernel on entry b and the download of entry b-1 run on three streams at the same time, so
+    a step costs about the larger of the two copy directions instead of their sum plus the kernel.
+    Device buffers are allocated once, for the shapes given at construction.
+    """
+
+    def __init__(self, b: int, hq: int, hkv: int, sq: int, skv: int, d: int, dtype: torch.dtype, device="cuda"):
+        self.shape_q, self.shape_kv, self.dtype = (b, hq, sq, d), (b, hkv, skv, d), dtype
+        mk = lambda shape: torch.empty(shape, dtype=dtype, device=device)
+        self.q, self.k, self.v, self.o = mk(self.shape_q), mk(self.shape_kv), mk(self.shape_kv), mk(self.shape_q)
+        self.up, self.down = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+        self.ev_in = [torch.cuda.Event() for _ in range(b)]
+        self.ev_done = [torch.cuda.Event() for _ in range(b)]
+
+    def __call__(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, out_host: torch.Tensor,
+                 causal: bool = False, scale: Optional[float] = None) -> torch.Tensor:
+        """Enqueues the whole step; ``out_host`` is complete when the current stream has been synchronised."""
+        for t in (q_host, k_host, v_host, out_host):
+            if t.is_cuda or not t.is_pinned():
+                raise ValueError("HostSdpaPipeline takes pinned host tensors")
+        main = torch.cuda.current_stream()
+        self.up.wait_stream(main)    # earlier users of the device buffers are done
+        self.down.wait_stream(main)
+        nb = self.shape_q[0]
+        for b in range(nb):
+            with torch.cuda.stream(self.up):
+                self.q[b].copy_(q_host[b], non_blocking=True)
+                self.k[b].copy_(k_host[b], non_blocking=True)
+                self.v[b].copy_(v_host[b], non_blocking=True)
+                self.ev_in[b].record(self.up)
+            main.wait_event(self.ev_in[b])
+            sdpa(self.q[b:b + 1], self.k[b:b + 1], self.v[b:b + 1], causal=causal, scale=scale, out=self.o[b:b + 1])
+            self.ev_done[b].record(main)
+            with torch.cuda.stream(self.down):
+                self.down.wait_event(self.ev_done[b])
+                out_host[b].copy_(self.o[b], non_blocking=True)
+        main.wait_stream(self.down)
+        return out_host
+
+
 class SdpaOp:
     """Operator-shaped wrapper: static attributes at construction, device buffers at ``Execute``.
 

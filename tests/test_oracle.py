@@ -119,3 +119,18 @@ def test_sliding_window_and_empty_sequence():
     vv = paged.gather_sequence(vc, 0, 40, bi, bb, d, bs)[:, -8:]
     ref = sdpa.sdpa_ref(q[0].reshape(1, hq, 1, d), kk[None], vv[None]).reshape(-1)
     np.testing.assert_allclose(win[0], ref, rtol=1e-5, atol=1e-6)
+
+
+def test_division_by_scale_identity(tmp_path):
+    """The store kernel's reciprocal-plus-fused-correction form of x / scale equals the IEEE division for every
+    f16-valued scale visited and every f16 / bf16 x (every 16th scale here; the exhaustive run is stride 1)."""
+    import os
+    import shutil
+    import subprocess
+    src = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "div_by_scale_check.c")
+    if shutil.which("gcc") is None or "fma" not in open("/proc/cpuinfo").read():
+        pytest.skip("needs gcc and a host CPU with FMA")
+    exe = str(tmp_path / "div_by_scale_check")
+    subprocess.run(["gcc", "-O2", "-mfma", "-o", exe, src, "-lm"], check=True)
+    r = subprocess.run([exe, "16"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and " 0 mismatches" in r.stdout, r.stdout

@@ -148,3 +148,21 @@ def test_graph_capture_and_replay(b2a):
     g.replay()
     torch.cuda.synchronize()
     assert_close(out, osdpa.sdpa_ref(q2.cpu(), k.cpu(), v.cpu(), causal=True), torch.bfloat16)
+
+
+def test_host_pipeline_matches_device_call(b2a):
+    # host tensors in, host tensor out, batch entries pipelined on three streams: same bits as the plain call
+    B, hq, hkv, S, D = 3, 8, 2, 384, 128
+    gen = torch.Generator().manual_seed(9)
+    q = (torch.randn(B, hq, S, D, generator=gen) * 0.5).to(torch.bfloat16).pin_memory()
+    k = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16).pin_memory()
+    v = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16).pin_memory()
+    out = torch.empty(B, hq, S, D, dtype=torch.bfloat16).pin_memory()
+    pipe = b2a.HostSdpaPipeline(B, hq, hkv, S, S, D, torch.bfloat16)
+    for _ in range(2):  # the second call reuses the device buffers behind the first
+        pipe(q, k, v, out, causal=True)
+        torch.cuda.synchronize()
+        ref = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), causal=True)
+        assert torch.equal(out.cuda(), ref)
+    with pytest.raises(ValueError):
+        pipe(q.cuda(), k, v, out)
