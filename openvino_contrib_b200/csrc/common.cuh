@@ -59,4 +59,30 @@ __host__ __device__ __forceinline__ size_t u8_chunk_bytes(int block_size, int d)
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Programmatic dependent launch: a kernel launched with launch_overlapped may be scheduled while the kernel before
+// it on the stream is still running (as soon as that one has executed grid_launch_dependents in every CTA, or has
+// finished), so that its launch latency and set-up hide behind the predecessor's tail.  It must call
+// grid_dependency_wait before it reads or writes anything an earlier kernel on the stream touches: the wait
+// returns when the predecessor grid has completed and its memory operations are visible.  EVERY kernel launched
+// this way calls the wait (a kernel that skipped it could finish before its predecessor and let ITS successor
+// overtake that one).  Both calls are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KernelArgs(args)...);
+}
+
 }  // namespace b2a

@@ -10,7 +10,7 @@
 // Codes 0..255 (and code + 1024, which is what the byte permute produces for free) are exact in f16, products are
 // exact, accumulation is f32: the only roundings are the f32 accumulation itself and one f16 rounding of P'.
 //
-// Grid = (split, KV head, sequence); a CTA of 4 warps walks `blocks_per_cta` logical blocks of one sequence and KV
+// Grid = (KV head, sequence, split); a CTA of 4 warps walks `blocks_per_cta` logical blocks of one sequence and KV
 // head, warp w taking blocks w, w+4, ...  Each warp runs its own 3-stage cp.async pipeline: a stage holds the K chunk
 // and the V chunk of one block (2 x 2112 bytes), copied as 16-byte pieces, 512 contiguous bytes per warp
 // instruction, into shared memory with an XOR swizzle of the 16-byte column so that the MMA fragments are read
@@ -118,7 +118,7 @@ __device__ __forceinline__ int first_block_of(int ctx, int sliding_window) {
 // workspace, `nsplit` is the number of CTAs of this sequence that write one, `tok` the sequence's token row.
 template <typename T, int NT>
 __device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out) {
-    const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+    const int hk = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tid4 = lane & 3;
 
@@ -438,11 +438,13 @@ template <typename T, int NT, bool kFused>
 __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     int nsplit = 0, tok = 0;
+    grid_dependency_wait();     // the cache rows of this step's new tokens and the query come from earlier kernels
+    grid_launch_dependents();   // the merge kernel's CTAs may take their seats while this grid drains
     if constexpr (!kFused) {
         decode_chunk<T, NT>(p, smem, nsplit, tok);
     } else {
         __shared__ int s_role;
-        const int tid = threadIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+        const int tid = threadIdx.x, hk = blockIdx.x, seq = blockIdx.y;
         const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
             st_release_sys(p.push.started[tid] + p.push.rank, epoch);  // this rank's readers of the previous step are done
@@ -511,6 +513,8 @@ __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const Deco
 template <typename T>
 __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodeParams p) {
     const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    grid_dependency_wait();  // the partials
+    grid_launch_dependents();
     const bool pushing = p.push.world > 0;
     const int parity = pushing ? ((*reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1) & 1) : 0;
     const int tok = p.t.subsequence_begins[seq];
@@ -562,6 +566,8 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
 // B2A_DEV_TIMEOUT instead of hanging when a peer never arrives.
 __global__ void __launch_bounds__(256) peer_wait_copy_kernel(const PeerPush push, void* out, int row_bytes,
                                                               int32_t* status) {
+    grid_dependency_wait();  // our own merge kernel
+    grid_launch_dependents();
     const int32_t epoch = *reinterpret_cast<volatile int32_t*>(push.step_counter);  // published by our own merge
     const int parity = epoch & 1;
     if (static_cast<int>(threadIdx.x) < push.world) {
@@ -592,9 +598,10 @@ int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
             return B2A_ERR_CUDA;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    dim3 grid(p.max_splits, p.Hkv, num_seqs);
-    kern<<<grid, kWarps * 32, kSmemBytes, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+    // the split index is the slowest-varying one: every sequence's first chunks (always full) are dispatched before
+    // anybody's last chunk (partial or empty), which shortens the tail of a step with uneven contexts
+    dim3 grid(p.Hkv, num_seqs, p.max_splits);
+    return launch_overlapped(kern, grid, dim3(kWarps * 32), kSmemBytes, stream, p) == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 
 template <typename T, int NT>
@@ -602,14 +609,15 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
     if (p.push.world > 0 && p.push.group_counters != nullptr) return launch_kernel<T, NT, true>(p, num_seqs, stream);
     const int rc = launch_kernel<T, NT, false>(p, num_seqs, stream);
     if (rc != B2A_OK) return rc;
-    paged_decode_merge_kernel<T><<<dim3(p.Hq, num_seqs), kD, 0, stream>>>(p);
-    if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+    if (launch_overlapped(paged_decode_merge_kernel<T>, dim3(p.Hq, num_seqs), dim3(kD), 0, stream, p) != cudaSuccess)
+        return B2A_ERR_CUDA;
     if (p.push.world > 0) {
         // decode steps carry one token per sequence: row index == sequence index == token index
-        peer_wait_copy_kernel<<<num_seqs, 256, 0, stream>>>(p.push, p.out, p.push.row_elems * static_cast<int>(sizeof(T)),
-                                                            p.status);
+        if (launch_overlapped(peer_wait_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push, p.out,
+                              p.push.row_elems * static_cast<int>(sizeof(T)), p.status) != cudaSuccess)
+            return B2A_ERR_CUDA;
     }
-    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+    return B2A_OK;
 }
 
 }  // namespace

@@ -161,6 +161,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kern
     constexpr int D = 128;
     const int lane = threadIdx.x & 31, l8 = lane & 7, rg = lane >> 3;
     const int tok = static_cast<int>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    grid_dependency_wait();  // the new key/value rows (and the pool's previous readers) belong to earlier kernels
+    grid_launch_dependents();
     if (tok >= p.t.num_tokens) return;
     const int seq = find_sequence(p.t, tok, lane);
     if (seq < 0) return;  // not scheduled
@@ -253,9 +255,10 @@ int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* 
     if (d.kv_dtype == B2A_U8 && d.D == 128 && d.Dv == 128 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) &&
         al8(key) && al8(value)) {
         const unsigned grid_t = static_cast<unsigned>((d.num_tokens + kWarpsPerCta - 1) / kWarpsPerCta);
-        if (d.q_dtype == B2A_F16) paged_kv_store_rows128_kernel<__half><<<grid_t, kWarpsPerCta * 32, 0, stream>>>(p);
-        else paged_kv_store_rows128_kernel<__nv_bfloat16><<<grid_t, kWarpsPerCta * 32, 0, stream>>>(p);
-        return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+        const cudaError_t e = d.q_dtype == B2A_F16
+            ? launch_overlapped(paged_kv_store_rows128_kernel<__half>, dim3(grid_t), dim3(kWarpsPerCta * 32), 0, stream, p)
+            : launch_overlapped(paged_kv_store_rows128_kernel<__nv_bfloat16>, dim3(grid_t), dim3(kWarpsPerCta * 32), 0, stream, p);
+        return e == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
     }
     const long long total = 2LL * d.num_tokens * d.Hkv;
     const unsigned grid = static_cast<unsigned>((total + kWarpsPerCta - 1) / kWarpsPerCta);

@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t,
     // sort in three passes over the sequences - histogram, bucket offsets, scatter.
     constexpr int kBuckets = 256;
     __shared__ int s_hist[kBuckets], s_count, s_groups;
+    grid_dependency_wait();  // earlier kernels may still read the previous step's list and scratch layout
+    grid_launch_dependents();
     for (int i = threadIdx.x; i < kBuckets; i += blockDim.x) s_hist[i] = 0;
     if (threadIdx.x == 0) s_count = s_groups = 0;
     if (owner != nullptr)
@@ -313,6 +315,8 @@ __global__ void __launch_bounds__(128) paged_gather_kernel(const PagedTables t, 
                                                            const int scratch_rows, uint16_t* k_out, uint16_t* v_out,
                                                            int32_t* status) {
     const int row0 = blockIdx.x * 16, hk = blockIdx.y;
+    grid_dependency_wait();  // the scratch layout (plan kernel) and this step's cache rows (store kernel)
+    grid_launch_dependents();
     const int seq = owner[row0 / 128];
     if (seq < 0) return;
     const int tok = threadIdx.x >> 3, c16 = threadIdx.x & 7;
@@ -1210,9 +1214,9 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     char* ws = static_cast<char*>(plan_ws);
     int* kv_base = gathered ? reinterpret_cast<int*>(ws + w.kv_base_at) : nullptr;
     int* owner = gathered ? reinterpret_cast<int*>(ws + w.owner_at) : nullptr;
-    paged_tc_plan_kernel<<<1, 256, 0, stream>>>(t, d.Hq / d.Hkv, capacity, static_cast<int*>(plan_ws), status, kv_base,
-                                                owner, w.groups);
-    if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+    if (launch_overlapped(paged_tc_plan_kernel, dim3(1), dim3(256), 0, stream, t, d.Hq / d.Hkv, capacity,
+                          static_cast<int*>(plan_ws), status, kv_base, owner, w.groups) != cudaSuccess)
+        return B2A_ERR_CUDA;
     // the step's query matrix [tokens, Hq*128] as a [1, Hq, tokens, 128] view
     const int64_t qs[4] = {static_cast<int64_t>(d.num_tokens) * d.Hq * kHeadDim, kHeadDim,
                            static_cast<int64_t>(d.Hq) * kHeadDim, 1};
@@ -1222,10 +1226,11 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     if (gathered) {
         uint16_t* ks = reinterpret_cast<uint16_t*>(ws + w.k_at);
         uint16_t* vs = reinterpret_cast<uint16_t*>(ws + w.v_at);
-        paged_gather_kernel<<<dim3(w.rows / 16, d.Hkv), 128, 0, stream>>>(
-            t, static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), d.Hkv, kv_base, owner, w.rows,
-            ks, vs, status);
-        if (cudaGetLastError() != cudaSuccess) return B2A_ERR_CUDA;
+        if (launch_overlapped(paged_gather_kernel, dim3(w.rows / 16, d.Hkv), dim3(128), 0, stream, t,
+                              static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), d.Hkv,
+                              static_cast<const int*>(kv_base), static_cast<const int*>(owner), w.rows, ks, vs,
+                              status) != cudaSuccess)
+            return B2A_ERR_CUDA;
         // the scratch as a [1, Hkv, rows, 128] f16 tensor
         const int64_t ss[4] = {static_cast<int64_t>(d.Hkv) * w.rows * kHeadDim, static_cast<int64_t>(w.rows) * kHeadDim,
                                kHeadDim, 1};
