@@ -150,6 +150,35 @@ def test_graph_capture_and_replay(b2a):
     assert_close(out, osdpa.sdpa_ref(q2.cpu(), k.cpu(), v.cpu(), causal=True), torch.bfloat16)
 
 
+def test_config2_full_size_properties(b2a):
+    # Llama-3-8B-shaped causal bf16 prefill at full size (B=4, Hq=32, Hkv=8, S=4096, D=128), checked through
+    # properties that do not need the whole oracle: causality (the first rows only see the first keys, so they
+    # equal the oracle on the truncated problem), a late row block against the oracle, V = 1 gives 1,
+    # and run-to-run determinism of the persistent kernel.
+    B, hq, hkv, S, D = 4, 32, 8, 4096, 128
+    gen = torch.Generator().manual_seed(1)
+    q = (torch.randn(B, hq, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    out = b2a.sdpa(qd, kd, vd, causal=True)
+    assert torch.equal(out, b2a.sdpa(qd, kd, vd, causal=True))
+    for b, h in ((0, 0), (3, 31), (1, 14)):
+        hk = h // (hq // hkv)
+        ref = osdpa.sdpa_ref(q[b:b + 1, h:h + 1, :384].float().numpy(), k[b:b + 1, hk:hk + 1, :384].float().numpy(),
+                             v[b:b + 1, hk:hk + 1, :384].float().numpy(), causal=True)
+        assert_close(out[b:b + 1, h:h + 1, :384], ref, torch.bfloat16, f"first rows of ({b},{h})")
+    # rows 3968..4095 of one head against the oracle with an explicit mask (they see all 4096 keys up to their own)
+    b, h, r0 = 2, 9, 3968
+    hk = h // (hq // hkv)
+    keep = (np.arange(S)[None, :] <= (r0 + np.arange(128))[:, None])
+    ref = osdpa.sdpa_ref(q[b:b + 1, h:h + 1, r0:].float().numpy(), k[b:b + 1, hk:hk + 1].float().numpy(),
+                         v[b:b + 1, hk:hk + 1].float().numpy(), mask=keep[None, None])
+    assert_close(out[b:b + 1, h:h + 1, r0:], ref, torch.bfloat16, "last row block")
+    ones = b2a.sdpa(qd, kd, torch.ones_like(vd), causal=True)
+    assert float((ones.float() - 1.0).abs().max()) <= 2.0 ** -8  # P is rounded to bf16 before the PV product
+
+
 def test_host_pipeline_matches_device_call(b2a):
     # host tensors in, host tensor out, batch entries pipelined on three streams: same bits as the plain call
     B, hq, hkv, S, D = 3, 8, 2, 384, 128
