@@ -191,6 +191,30 @@ def timed(fn, steps, warmup, world, stream=None):
     return ms / steps, t0, t1
 
 
+def timed_replay(fn, steps, warmup, world):
+    """Like timed(), but the step is captured once into a CUDA graph and the K timed steps are replays of it - how
+    the plugin's graph runner executes a captured topology (no host-side launch cost in the timed region).  Falls
+    back to plain calls when the capture fails (a collective library that refuses capture, for instance)."""
+    for _ in range(max(1, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+    except Exception:
+        torch.cuda.synchronize()
+        ms, t0, t1 = timed(fn, steps, 1, world)
+        return ms, "plain calls (graph capture failed)"
+    ms, _, _ = timed(graph.replay, steps, 2, world)
+    return ms, "graph replay"
+
+
 def bench_prefill(args, rank, world, local):
     import torch.distributed as dist
     import openvino_contrib_b200 as b2a
@@ -352,7 +376,7 @@ def bench_decode(name, steps, warmup, rank, world):
                             workspace=ws)
         if world > 1 and exchange != "local":  # "local": no exchange at all (diagnosis only; not a valid step)
             gather_heads_rows(out, shard, D, buffer=gathered)
-    ms, _, _ = timed(step, steps, warmup, world)
+    ms, how = timed_replay(step, steps, warmup, world)
     if group is not None:
         torch.cuda.synchronize()
         group.close()
@@ -364,7 +388,8 @@ def bench_decode(name, steps, warmup, rank, world):
             "frac_of_hbm_peak": gbs / (pk["hbm_gbs"] * world), "peak_gbs_per_gpu": pk["hbm_gbs"],
             "peak_source": pk["source"], "cached_tokens": tokens,
             "traffic": NCU_TRAFFIC.get(name) if world == 1 else None, "launches_per_step": (1 if inplace else 3) if group is not None else 2,
-            "output_exchange": exchange + (" (one kernel, in place)" if group is not None and inplace else "")}
+            "output_exchange": exchange + (" (one kernel, in place)" if group is not None and inplace else ""),
+            "timing": how}
 
 
 def bench_mixed(steps, warmup, rank, world):
@@ -404,8 +429,8 @@ def bench_mixed(steps, warmup, rank, world):
     def step():
         b2a.paged_kv_store(k, v, cache, past, sb, bi, bb)
         attend()
-    ms, _, _ = timed(step, steps, warmup, 1)
-    ams, _, _ = timed(attend, steps, 1, 1)
+    ms, how = timed_replay(step, steps, warmup, 1)
+    ams, _ = timed_replay(attend, steps, 1, 1)
     pk = peaks()
     prefill_flops = 8 * 4 * Hq * D * (1024 * 1025 // 2)
     decode_bytes = int(dec_ctx.sum()) * Hkv * 2 * (D + 4)
@@ -415,7 +440,7 @@ def bench_mixed(steps, warmup, rank, world):
     return {"workload": "cfg4", "ms_per_step": ms, "attention_ms": ams, "new_tokens": ntok,
             "prefill_flops": prefill_flops, "decode_kv_bytes": decode_bytes, "kv_store_bytes": store_bytes,
             "tokens_per_s": ntok / (ms * 1e-3), "bar_ms": bar_ms, "bar_over_measured": bar_ms / ams,
-            "launches_per_step": 6 if kvt else 5, "prefill_kv": "de-quantised once into an f16 scratch" if kvt else
+            "launches_per_step": 7 if kvt else 6, "timing": how, "prefill_kv": "de-quantised once into an f16 scratch" if kvt else
             "de-quantised inside the prefill kernel"}
 
 
