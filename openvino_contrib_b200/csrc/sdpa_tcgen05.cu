@@ -1021,6 +1021,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 // Bounded (about a second): a peer that never arrives turns into B2A_DEV_TIMEOUT in the status word.
 __global__ void __launch_bounds__(32) sdpa_peer_wait_kernel(const int32_t* flags, const int world, const int32_t step,
                                                             int32_t* status) {
+    grid_dependency_wait();  // launched while the attention kernel is still running: first let that one finish
     if (static_cast<int>(threadIdx.x) < world) {
         const int32_t* flag = flags + threadIdx.x;
         const long long t0 = clock64();
@@ -1154,8 +1155,10 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
 }
 
 int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, int32_t* status, cudaStream_t stream) {
-    sdpa_peer_wait_kernel<<<1, 32, 0, stream>>>(local_flags, world, step, status);
-    return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+    return launch_overlapped(sdpa_peer_wait_kernel, dim3(1), dim3(32), 0, stream, local_flags, world, step, status) ==
+                   cudaSuccess
+               ? B2A_OK
+               : B2A_ERR_CUDA;
 }
 
 bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* out) {
