@@ -192,27 +192,30 @@ def timed(fn, steps, warmup, world, stream=None):
 
 
 def timed_replay(fn, steps, warmup, world):
-    """Like timed(), but the step is captured once into a CUDA graph and the K timed steps are replays of it - how
-    the plugin's graph runner executes a captured topology (no host-side launch cost in the timed region).  Falls
+    """Like timed(), but the steps are captured into a CUDA graph and the timed region replays it - how the plugin's
+    graph runner executes a captured topology (no host-side launch cost in the timed region).  A graph holds up to
+    25 consecutive steps (a decoder's graph holds one such step per layer), and K steps are K/25 replays.  Falls
     back to plain calls when the capture fails (a collective library that refuses capture, for instance)."""
     for _ in range(max(1, warmup)):
         fn()
     torch.cuda.synchronize()
+    per_graph = max(g for g in range(1, 26) if steps % g == 0)
     try:
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             with torch.cuda.graph(graph, stream=side):
-                fn()
+                for _ in range(per_graph):
+                    fn()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
     except Exception:
         torch.cuda.synchronize()
         ms, t0, t1 = timed(fn, steps, 1, world)
         return ms, "plain calls (graph capture failed)"
-    ms, _, _ = timed(graph.replay, steps, 2, world)
-    return ms, "graph replay"
+    ms, _, _ = timed(graph.replay, steps // per_graph, 2, world)
+    return ms / per_graph, f"graph replay, {per_graph} steps per graph"
 
 
 def bench_prefill(args, rank, world, local):
