@@ -302,6 +302,45 @@ def test_paged_prefill_parity(b2a, dtype):
     assert int(status.item()) & 4  # B2A_DEV_BAD_LEN
 
 
+def test_mixed_step_graph_replay_with_new_lengths(b2a):
+    # a captured mixed step replays correctly after the device tables changed: other histories, and the step's 500
+    # tokens split differently over the sequences (work list and scratch layout are rebuilt on the device)
+    hq, hkv, d = 32, 8, 128
+    w = PagedWorkload([600, 300, 400, 90], [300, 129, 1, 70], hq, hkv, d, seed=41)
+    cache = w.device_cache()
+    past, sb, bi, bb = w.device_tables()
+    q = _round(w.query, torch.bfloat16).cuda()
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    hints = dict(prefill_row_blocks=6, prefill_kv_tokens=1280)
+    ws = torch.empty(b2a.ops.paged_workspace_bytes(torch.bfloat16, cache, hq, 4, 500, 640, 300, 6, 1280),
+                     dtype=torch.uint8, device="cuda")
+    run = lambda stream=None: b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=640, max_q_len=300,
+                                                  out=out, workspace=ws, stream=stream, status=status, **hints)
+    run()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert_close(out, w.reference(q.float().cpu().numpy()), torch.bfloat16)
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            run(s)
+    new_past = np.array([400, 0, 100, 20], np.int32)
+    new_qlen = np.array([129, 300, 70, 1], np.int32)
+    new_sb = np.zeros(5, np.int32)
+    new_sb[1:] = np.cumsum(new_qlen)
+    past.copy_(torch.from_numpy(new_past))
+    sb.copy_(torch.from_numpy(new_sb))
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = opaged.paged_attention_ref(q.float().cpu().numpy(), w.k_cache, w.v_cache, new_past, new_sb, w.bi, w.bb,
+                                     hq, hkv, d, 16)
+    assert_close(out, ref, torch.bfloat16)
+
+
 def test_config4_mixed_step(b2a):
     # 8 prefill sequences of 1024 tokens plus 120 decode sequences with contexts uniform in [256, 4096] (seed 4),
     # bf16 queries, u8 cache, through the operator (store, then attend)
