@@ -46,16 +46,6 @@
 #include "launch.cuh"
 #include "tcgen05.cuh"
 
-#ifndef B2A_TC_SNAKE
-#define B2A_TC_SNAKE 1
-#endif
-#ifndef B2A_TC_ORDER
-#define B2A_TC_ORDER 0
-#endif
-#ifndef B2A_TC_GRID_ALL
-#define B2A_TC_GRID_ALL 0
-#endif
-
 namespace b2a {
 namespace {
 
@@ -436,20 +426,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
         } else {
             const int ctas = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
-#if B2A_TC_SNAKE
             const int idx = k * ctas + ((k & 1) ? ctas - 1 - me : me);
-#else
-            const int idx = k * ctas + me;
-#endif
             if (idx >= total_items) return false;
+            // heaviest row blocks of ALL (batch, KV head) streams first (measured faster than walking one stream
+            // after the other, although that keeps fewer K/V streams in flight)
             const int bh = p.B * p.Hkv;
-#if B2A_TC_ORDER == 0
             pair = pairs - 1 - idx / bh;
             const int y = idx % bh;
-#else
-            pair = pairs - 1 - idx % pairs;
-            const int y = idx / pairs;
-#endif
             it.b = y / p.Hkv;
             it.hk = y % p.Hkv;
         }
@@ -1145,7 +1128,7 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     if (items >= (1LL << 30)) return B2A_ERR_UNSUPPORTED;
     const int sms = device_sm_count();
     if (sms <= 0) return B2A_ERR_CUDA;
-    dim3 grid(static_cast<unsigned>(items < sms || B2A_TC_GRID_ALL ? items : sms));  // persistent CTAs, one per SM
+    dim3 grid(static_cast<unsigned>(items < sms ? items : sms));  // persistent CTAs, one per SM
     static bool configured[2][64] = {};
     auto kern = bf16 ? attn_tc_kernel<true, 0> : attn_tc_kernel<false, 0>;
     const int rc = configure_once(kern, configured[bf16]);
