@@ -264,7 +264,7 @@ void test_paged_op_decode_with_block_manager() {
     auto base = OperationRegistry::getInstance().createOperation(cc, node, ids({0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10}), ids({11}));
     auto op = std::dynamic_pointer_cast<PagedAttentionOp>(base);
     CHECK(op != nullptr);
-    op->SetCapacity(4, nblocks * bs / 2);
+    op->SetCapacity(4, nblocks * bs / 2, /*max_prefill_kv_tokens=*/512);  // room to de-quantise prefill contexts once
     const auto req = op->GetWorkBufferRequest();
     CHECK(req.mutable_sizes.size() == 2);
     DevBuf<uint8_t> ws(req.mutable_sizes[0]), st(req.mutable_sizes[1]);
@@ -281,7 +281,8 @@ void test_paged_op_decode_with_block_manager() {
     std::mt19937 rng(3);
     std::normal_distribution<float> nd;
 
-    // step 0: prefill of 37 / 16 / 5 tokens (general kernel); steps 1..2: one token each (decode kernel)
+    // step 0: prefill of 37 / 16 / 5 tokens (tensor-core kernel over contexts de-quantised once, by the scheduler's
+    // hints); steps 1..2: one token each (decode kernel)
     const int32_t prefill[nseq] = {37, 16, 5};
     const int32_t one[nseq] = {1, 1, 1};
     const int max_tok = 64;
@@ -293,6 +294,8 @@ void test_paged_op_decode_with_block_manager() {
         b2a::StepTables t;
         CHECK(mgr.schedule_step(seq_ids, step == 0 ? prefill : one, nseq, t) == B2A_OK);
         const int ntok = t.num_tokens;
+        if (step == 0) CHECK(t.prefill_row_blocks == 3 && t.prefill_kv_tokens == 3 * 128);
+        op->SetStepHints(t.prefill_row_blocks, t.prefill_kv_tokens);  // what the scheduler knows about this step
         std::vector<uint16_t> q(static_cast<size_t>(max_tok) * Hq * D, 0), k(static_cast<size_t>(max_tok) * Hkv * D, 0),
             v(static_cast<size_t>(max_tok) * Hkv * D, 0);
         for (size_t i = 0; i < static_cast<size_t>(ntok) * Hq * D; ++i) q[i] = f2h(nd(rng));
