@@ -48,8 +48,15 @@ struct DecodeParams {
     PeerPush push;     // world == 0 unless the heads are sharded over several GPUs
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+// The cache is read once per step and is far larger than L2: the copies carry an evict-first policy so that the
+// lines they bring in are the first to go and the step's small re-used data (queries, tables, partials) stays.
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
@@ -160,6 +167,7 @@ __device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* sme
     const size_t head_stride = kChunk;                         // chunks of one block: [Hkv][2112]
     const size_t block_stride = static_cast<size_t>(p.Hkv) * kChunk;
 
+    const uint64_t l2_policy = evict_first_policy();
     auto issue = [&](int i) {
         // stage i % kStages <- block i of this warp; an out-of-range physical index copies nothing
         const int phys = __shfl_sync(0xffffffffu, my_phys, i & 31);
@@ -172,11 +180,11 @@ __device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* sme
                 const int piece = r * 32 + lane;          // 16-byte piece of the 2048 code bytes
                 const int row = piece >> 3, col = piece & 7;
                 const uint32_t off = row * 128 + ((col ^ (row & 7)) << 4);
-                cp_async16(st + off, kc + piece * 16);
-                cp_async16(st + kChunk + off, vc + piece * 16);
+                cp_async16(st + off, kc + piece * 16, l2_policy);
+                cp_async16(st + kChunk + off, vc + piece * 16, l2_policy);
             }
-            if (lane < 4) cp_async16(st + 2048 + lane * 16, kc + 2048 + lane * 16);
-            else if (lane < 8) cp_async16(st + kChunk + 2048 + (lane - 4) * 16, vc + 2048 + (lane - 4) * 16);
+            if (lane < 4) cp_async16(st + 2048 + lane * 16, kc + 2048 + lane * 16, l2_policy);
+            else if (lane < 8) cp_async16(st + kChunk + 2048 + (lane - 4) * 16, vc + 2048 + (lane - 4) * 16, l2_policy);
         }
     };
 
