@@ -623,6 +623,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // running counts over the items of this CTA: K/V tiles issued (ring position) and Q tiles loaded
             int g = 0, issued_k = 0, issued_v = 0, qn[2] = {0, 0};
             bool ok = true;
+            const uint64_t once_policy = l2_evict_first_policy();  // Q tiles are read once
             Item it;
             for (int k = 0; ok && get_item(k, it); ++k) {
                 auto load_q = [&](int X) {
@@ -632,8 +633,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     if (qn[X] > 0 && !mbar_wait(BAR(Q_EMPTY + X), (qn[X] - 1) & 1, abort_flag)) { ok = false; return; }
                     mbar_expect_tx(BAR(Q_FULL + X), kTile);
                     const int row = tok_base + (X ? it.row0B : it.row0A), head = X ? it.headB : it.headA;
-                    tma_load_4d(sQ + X * kTile, &tmQ, BAR(Q_FULL + X), 0, row, head, it.b);
-                    tma_load_4d(sQ + X * kTile + kPanel, &tmQ, BAR(Q_FULL + X), 64, row, head, it.b);
+                    tma_load_4d_hint(sQ + X * kTile, &tmQ, BAR(Q_FULL + X), 0, row, head, it.b, once_policy);
+                    tma_load_4d_hint(sQ + X * kTile + kPanel, &tmQ, BAR(Q_FULL + X), 64, row, head, it.b, once_policy);
                     ++qn[X];
                 };
                 load_q(0);
@@ -957,7 +958,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         if (lane == 0) {
                             const int w = warp & 3;
                             if (peers.world == 0) {
-                                tma_store_4d(&tmO, slab, 64 * half, row0 + 32 * w, head, b);
+                                tma_store_4d_hint(&tmO, slab, 64 * half, row0 + 32 * w, head, b, l2_evict_first_policy());
                             } else {
                                 // the same slab into every rank's buffer, the next rank first so that the ranks do
                                 // not all write to the same peer at the same time; local copy last
