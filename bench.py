@@ -363,7 +363,7 @@ def bench_decode(name, steps, warmup, rank, world):
         exchange = os.environ.get("B2A_BENCH_EXCHANGE", "peer")  # "peer": stores into every rank's memory; "nccl"
         if exchange == "peer":
             try:
-                group = ShardGroup(shard, staging_bytes=n * Hq * D * 2)
+                group = ShardGroup(shard, staging_bytes=2 * n * Hq * D * 2)  # twice the output: low-latency exchange
             except Exception as e:  # CUDA IPC not available in this container: fall back to the library collective
                 exchange = f"nccl (peer mapping failed: {type(e).__name__})"
     # B2A_BENCH_DECODE_INPLACE=1: the group's own buffer, the step is ONE kernel producing the rows in place on every

@@ -186,7 +186,9 @@ int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, c
  *
  * Set-up (allocates; not for the hot path): every rank creates its group, the 64-byte handles of all ranks are
  * exchanged by any host-side means (torch.distributed all_gather, MPI, a file), in rank order, and passed to
- * _connect.  staging_bytes >= num_tokens * Hq_total * D * 2 of the largest step.
+ * _connect.  staging_bytes >= num_tokens * Hq_total * D * 2 of the largest step; with twice that, decode steps use
+ * the low-latency exchange (values travel with the step number in 8-byte words and the receiver polls them: no
+ * flag round trip).
  * ------------------------------------------------------------------------------------------- */
 typedef struct b2a_shard_group b2a_shard_group;
 int b2a_shard_group_create(int rank, int world, size_t staging_bytes, b2a_shard_group** out);

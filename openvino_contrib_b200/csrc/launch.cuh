@@ -33,6 +33,10 @@ struct PeerPush {
     int rank, world;                   // world == 0: not sharded
     int row_elems;                     // elements of one full-width output row (Hq_total * D)
     int col_offset;                    // first column of this rank's heads
+    // Low-latency form (when the staging buffers are twice as large as the output): every pair of 16-bit values
+    // travels as one 8-byte store {two values, step number}, which arrives whole or not at all, so the receiver
+    // simply polls each word for the step number - no fence, no flag round trip, no rendezvous of whole kernels.
+    int ll;
     // Single-kernel step (group_counters != nullptr): the decode kernel's last CTA of every (sequence, KV head)
     // merges that group's splits and stores the result into staging[r][0] of every rank r - the ranks' fixed
     // output buffers, read in place - and the grid's last CTA publishes the step and waits for the other ranks.

@@ -532,6 +532,46 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
     const int nblk = (ctx + kBS - 1) / kBS;
     const bool valid = qlen == 1 && past >= 0 &&
                        nblk <= p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq];
+    if (pushing && p.push.ll) {
+        // one 8-byte word per pair of values: {value d, value d+1, step}.  Every row must arrive on every rank, so
+        // a sequence that is not a plain one-token decode row (or does not sit at row `seq`) sends zeros and is
+        // reported; the receiver polls each word for the step number.
+        const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
+        float r = 0.f;
+        if (valid && tok == seq) {
+            const int blk_lo = first_block_of(ctx, p.sliding_window);
+            const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
+            const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
+            float mc = kNegBig;
+            for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, p.ws_ml[(base + s) * 2]);
+            float o = 0.f, l = 0.f;
+            for (int s = 0; s < nsplit; ++s) {
+                const float f = ex2(p.ws_ml[(base + s) * 2] - mc);
+                o += p.ws_o[(base + s) * kD + d] * f;
+                l += p.ws_ml[(base + s) * 2 + 1] * f;
+            }
+            r = l > 0.f ? o / l : 0.f;
+        } else if (d == 0 && h == 0) {
+            report(p.status, B2A_DEV_BAD_LEN);
+        }
+        const T val = from_f32<T>(r);
+        const uint32_t mine = *reinterpret_cast<const unsigned short*>(&val);
+        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 1);
+        if ((d & 1) == 0) {
+            const size_t at = (static_cast<size_t>(seq) * p.push.row_elems + p.push.col_offset + h * kD + d) >> 1;
+            const uint2 word = make_uint2(mine | (next << 16), static_cast<uint32_t>(epoch));
+            for (int rk = 0; rk < p.push.world; ++rk) reinterpret_cast<uint2*>(p.push.staging[rk][parity])[at] = word;
+        }
+        __syncthreads();
+        if (d == 0) {
+            const int total = static_cast<int>(gridDim.x * gridDim.y);
+            if (atomicAdd(p.push.done_counter, 1) == total - 1) {
+                *p.push.done_counter = 0;
+                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;  // the receiver kernel reads it
+            }
+        }
+        return;
+    }
     if (valid) {
         const int blk_lo = first_block_of(ctx, p.sliding_window);
         const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
@@ -595,6 +635,32 @@ __global__ void __launch_bounds__(256) peer_wait_copy_kernel(const PeerPush push
     for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = src[i];
 }
 
+// Receiver of the low-latency form: one CTA per row polls every 8-byte word of its staging row until it carries this
+// step's number (bounded: B2A_DEV_TIMEOUT after about a second) and writes the two values to the caller's output.
+__global__ void __launch_bounds__(256) peer_ll_copy_kernel(const PeerPush push, uint32_t* out, int pairs_per_row,
+                                                            int32_t* status) {
+    grid_dependency_wait();  // our own merge kernel (it publishes the step number)
+    grid_launch_dependents();
+    const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(push.step_counter));
+    const uint2* src = reinterpret_cast<const uint2*>(push.staging[push.rank][epoch & 1]) +
+                       static_cast<size_t>(blockIdx.x) * pairs_per_row;
+    uint32_t* dst = out + static_cast<size_t>(blockIdx.x) * pairs_per_row;
+    const long long t0 = clock64();
+    bool gave_up = false;
+    for (int i = threadIdx.x; i < pairs_per_row; i += blockDim.x) {
+        uint32_t lo, hi;
+        for (;;) {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "l"(src + i) : "memory");
+            if (hi == epoch || gave_up) break;
+            if (clock64() - t0 > (1LL << 31)) {
+                report(status, B2A_DEV_TIMEOUT);
+                gave_up = true;
+            }
+        }
+        dst[i] = lo;
+    }
+}
+
 template <typename T, int NT, bool kFused>
 int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
     auto kern = paged_decode_kernel<T, NT, kFused>;
@@ -621,9 +687,12 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
         return B2A_ERR_CUDA;
     if (p.push.world > 0) {
         // decode steps carry one token per sequence: row index == sequence index == token index
-        if (launch_overlapped(peer_wait_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push, p.out,
-                              p.push.row_elems * static_cast<int>(sizeof(T)), p.status) != cudaSuccess)
-            return B2A_ERR_CUDA;
+        const cudaError_t e = p.push.ll
+            ? launch_overlapped(peer_ll_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push,
+                                static_cast<uint32_t*>(p.out), p.push.row_elems / 2, p.status)
+            : launch_overlapped(peer_wait_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push, p.out,
+                                p.push.row_elems * static_cast<int>(sizeof(T)), p.status);
+        if (e != cudaSuccess) return B2A_ERR_CUDA;
     }
     return B2A_OK;
 }

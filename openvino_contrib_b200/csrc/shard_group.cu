@@ -137,6 +137,7 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
     push.rank = g->rank;
     push.world = g->world;
     push.row_elems = d.Hq * g->world * d.D;
+    push.ll = !in_place && 2 * static_cast<size_t>(d.num_tokens) * row_bytes <= g->staging_bytes ? 1 : 0;
     push.col_offset = g->rank * d.Hq * d.D;
     const PagedTables t{past_lens, subsequence_begins, block_indices, block_indices_begins,
                         d.num_seqs, d.num_tokens, d.num_blocks_total, d.block_size};

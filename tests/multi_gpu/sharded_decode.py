@@ -38,12 +38,15 @@ def main():
     vc = torch.from_numpy(w.v_cache[:, shard.kv_heads].copy()).cuda()
     cache = b2a.PagedKvCache(kc, vc, shard.hkv_local, d, d, 16, torch.uint8)
     tables = w.device_tables()
-    group = ShardGroup(shard, staging_bytes=n * hq * d * 2)
     ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, shard.hq_local, n, n, max(ctx), 1)),
                      dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    for step in range(3):
-        q_full = torch.from_numpy(w.query * (1.0 + 0.25 * step)).to(torch.float16)
+    # staging of exactly the output size: rows pushed as they are, flags, wait-and-copy; twice the size: the
+    # low-latency exchange (value pairs travel with the step number, the receiver polls the words)
+    for mult in (1, 2):
+      group = ShardGroup(shard, staging_bytes=mult * n * hq * d * 2)
+      for step in range(3):
+        q_full = torch.from_numpy(w.query * (1.0 + 0.25 * step + 0.5 * mult)).to(torch.float16)
         ref = w.reference(q_full.float().numpy())
         q_local = shard.take_q_rows(q_full, d).contiguous().cuda()
         out = torch.zeros(n, hq * d, dtype=torch.float16, device="cuda")
@@ -57,8 +60,8 @@ def main():
                                       max_q_len=1, workspace=ws)
         o_nccl = gather_heads_rows(o_local, shard, d)
         assert torch.equal(o_nccl, out), f"rank {rank} step {step}: differs from the NCCL gather"
-    dist.barrier()
-    group.close()
+      dist.barrier()
+      group.close()
     # the one-kernel step: results produced in place in the group's own buffer on every rank
     group2 = ShardGroup(shard, staging_bytes=n * hq * d * 2)
     for step in range(3):
