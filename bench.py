@@ -32,8 +32,8 @@ PREFILL = dict(B=4, Hq=32, Hkv=8, S=4096, D=128)
 
 # dram__bytes (read + write) per launch from the profiler captures summarised under profiles/ (bytes)
 NCU_TRAFFIC = {
-    "prefill": 515.8e6,   # attn_tc_kernel<bf16, dense>, full workload: profiles/attn_tc_kernel_prefill_cfg2.md
-    "cfg3": 628.7e6,      # paged_decode_kernel<f16, 1>: profiles/paged_decode_kernel_cfg3.md
+    "prefill": 429.2e6,   # attn_tc_kernel<bf16, dense>, full workload: profiles/attn_tc_kernel_prefill_cfg2.md
+    "cfg3": 627.5e6,      # paged_decode_kernel<f16, 1>: profiles/paged_decode_kernel_cfg3.md
 }
 
 
