@@ -515,6 +515,25 @@ __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const Deco
     }
 }
 
+// out[d] of one (sequence, query head) from its split partials: sum_s O_s[d] 2^(m_s - m) / sum_s l_s 2^(m_s - m) with
+// m = max_s m_s.  The (m, l) pairs are read as 8-byte loads and both loops are unrolled so that eight partials are in
+// flight per thread (the loads are independent; only the tiny accumulation is a chain).
+__device__ __forceinline__ float merge_splits(const DecodeParams& p, size_t base, int nsplit, int d) {
+    const float2* ml = reinterpret_cast<const float2*>(p.ws_ml) + base;
+    float mc = kNegBig;
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, ml[s].x);
+    float o = 0.f, l = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) {
+        const float2 v = ml[s];
+        const float f = ex2(v.x - mc);
+        o += p.ws_o[(base + s) * kD + d] * f;
+        l += v.y * f;
+    }
+    return l > 0.f ? o / l : 0.f;
+}
+
 // Merge the split partials of one (sequence, query head): out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
 // With sharded heads the row segment goes to every rank's staging buffer instead, and the last CTA of the grid
 // publishes the step (see PeerPush).
@@ -541,16 +560,7 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
         if (valid && tok == seq) {
             const int blk_lo = first_block_of(ctx, p.sliding_window);
             const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
-            const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
-            float mc = kNegBig;
-            for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, p.ws_ml[(base + s) * 2]);
-            float o = 0.f, l = 0.f;
-            for (int s = 0; s < nsplit; ++s) {
-                const float f = ex2(p.ws_ml[(base + s) * 2] - mc);
-                o += p.ws_o[(base + s) * kD + d] * f;
-                l += p.ws_ml[(base + s) * 2 + 1] * f;
-            }
-            r = l > 0.f ? o / l : 0.f;
+            r = merge_splits(p, (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits, nsplit, d);
         } else if (d == 0 && h == 0) {
             report(p.status, B2A_DEV_BAD_LEN);
         }
@@ -575,16 +585,7 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
     if (valid) {
         const int blk_lo = first_block_of(ctx, p.sliding_window);
         const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
-        const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
-        float mc = kNegBig;
-        for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, p.ws_ml[(base + s) * 2]);
-        float o = 0.f, l = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float f = ex2(p.ws_ml[(base + s) * 2] - mc);
-            o += p.ws_o[(base + s) * kD + d] * f;
-            l += p.ws_ml[(base + s) * 2 + 1] * f;
-        }
-        const T val = from_f32<T>(l > 0.f ? o / l : 0.f);
+        const T val = from_f32<T>(merge_splits(p, (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits, nsplit, d));
         if (!pushing) {
             T* orow = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD;
             orow[d] = val;
