@@ -87,6 +87,7 @@ struct TcPeers {
     int32_t* done_counter;
     int world, rank, head_offset;
     int32_t step;
+    int light_first;  // deal the lightest items first: their output tiles are on the wire while the heavy ones compute
 };
 
 // Work list of the paged front end.  Lengths live on the device, so a one-CTA kernel turns them into the list of
@@ -431,7 +432,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // heaviest row blocks of ALL (batch, KV head) streams first (measured faster than walking one stream
             // after the other, although that keeps fewer K/V streams in flight)
             const int bh = p.B * p.Hkv;
-            pair = pairs - 1 - idx / bh;
+            // With many ranks the step is bound by the exchange of the output tiles, which can only start when the
+            // first items end: then the light items go first (the snake still pairs light with heavy per CTA).
+            pair = peers.light_first ? idx / bh : pairs - 1 - idx / bh;
             const int y = idx % bh;
             it.b = y / p.Hkv;
             it.hk = y % p.Hkv;
@@ -1117,6 +1120,7 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
         peers.rank = peer_out->rank;
         peers.head_offset = peer_out->head_offset;
         peers.step = peer_out->step;
+        peers.light_first = peer_out->world >= 4 ? 1 : 0;
     }
     TcParams p{};
     p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.G = d.Hq / d.Hkv; p.Sq = d.Sq; p.Skv = d.Skv;
