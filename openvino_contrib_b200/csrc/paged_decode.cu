@@ -720,13 +720,13 @@ DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count) {
     long long bpc = (total + target_ctas - 1) / target_ctas;
     bpc = ((bpc + 3) / 4) * 4;
     if (bpc < 96) {
-        // A small step (a head shard of a long-context batch, say): filling every slot with short chunks costs more
-        // in pipeline starts, partials and merge work than it gains - measured on 16 x 32768 tokens of one KV head:
-        // 37 us with 56-block chunks on 592 CTAs, 31 us with 128-block chunks on 256 CTAs.  Keep the chunks long as
-        // long as there are about 1.5 CTAs per SM.
-        const long long min_ctas = static_cast<long long>(sm_count) * 3 / 2;
-        bpc = total / (min_ctas > 0 ? min_ctas : 1);
-        bpc = (bpc / 4) * 4;
+        // A small step (a head shard, say) cannot fill every slot with long chunks.  Short chunks are fine while a
+        // sequence is cut into few of them, but every split costs a pipeline start, a partial and merge work:
+        // measured on one KV head, 16 x 32768 tokens take 37 us as 37 splits of 56 blocks and 31 us as 16 splits of
+        // 128, while 64 ragged sequences of at most 8192 tokens are fastest with their 56-block chunks (10 splits).
+        // So a sequence is cut into at most 16 chunks.
+        const long long floor_bpc = ((nblk_max + 15) / 16 + 3) / 4 * 4;
+        if (bpc < floor_bpc) bpc = floor_bpc;
     }
     if (bpc < 16) bpc = 16;
     if (bpc > 128) bpc = 128;
