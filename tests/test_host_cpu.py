@@ -61,6 +61,28 @@ def test_descriptor_validation_happens_before_any_launch(lib):
     assert lib.b2a_paged_chunk_bytes(_lib.F32, 16, 128) == 0
 
 
+def test_decode_chunk_plan(lib):
+    """The split-K plan as it shows in the workspace size (seqs * Hq * splits * 130 floats), for 148 SMs."""
+    ws = C.c_size_t(0)
+
+    def splits(hq, hkv, seqs, max_ctx):
+        p = _lib.PagedDesc()
+        p.q_dtype, p.kv_dtype = _lib.F16, _lib.U8
+        p.Hq, p.Hkv, p.D, p.Dv, p.block_size = hq, hkv, 128, 128, 16
+        p.num_seqs, p.num_tokens, p.num_blocks_total, p.max_context_len, p.max_q_len = seqs, seqs, 1 << 20, max_ctx, 1
+        assert lib.b2a_paged_workspace_bytes(C.byref(p), 148, C.byref(ws)) == 0
+        per_split = seqs * hq * 130 * 4
+        assert ws.value % per_split == 0
+        return ws.value // per_split
+
+    assert splits(32, 8, 64, 8192) == 4      # 64 ragged sequences: 128-block chunks, the longest sequence in 4
+    assert splits(64, 8, 16, 32768) == 16    # 16 x 32768: 128-block chunks
+    assert splits(8, 1, 16, 32768) == 16     # its one-head shard: still long chunks, at most 16 per sequence
+    assert splits(4, 1, 64, 8192) == 10      # the ragged batch's one-head shard: 56-block chunks fill the slots
+    assert splits(32, 8, 4, 64) == 1         # tiny step: one chunk per sequence
+    assert splits(16, 2, 16, 32768) == 19    # two-head shard: 112-block chunks, one wave of 4 CTAs per SM
+
+
 def test_kv_block_manager_tables():
     from openvino_contrib_b200 import KvBlockManager
     from openvino_contrib_b200._lib import B2AError
