@@ -402,6 +402,7 @@ class KvBlockManager:
         """``prefill_kv_tokens`` hint of the step scheduled last."""
         return self._lib.b2a_kvmgr_last_prefill_kv_tokens(self._h)
 
+    @property
     def last_prefill_row_blocks(self) -> int:
         """``prefill_row_blocks`` hint of the step scheduled last."""
         return self._lib.b2a_kvmgr_last_prefill_row_blocks(self._h)

@@ -95,8 +95,11 @@ def test_kv_block_manager_tables():
     assert past.tolist() == [0, 0, 0] and sb.tolist() == [0, 33, 49, 50]
     assert bb.tolist() == [0, 3, 4, 5] and sorted(bi.tolist()) == [0, 1, 2, 3, 4] and mctx == 33
     assert m.free_blocks == 5 and m.sequence_len(7) == 33
+    # the two hints a step descriptor can carry: 128-row blocks and 128-rounded contexts of the multi-token sequences
+    assert m.last_prefill_row_blocks == 2 and m.last_prefill_kv_tokens == 256
     past, sb, bi2, bb, mctx = m.schedule_step([8, 7], [1, 15])  # decode-like: seq 8 crosses into a new block
     assert past.tolist() == [16, 33] and bb.tolist() == [0, 2, 5] and mctx == 48
+    assert m.last_prefill_row_blocks == 1 and m.last_prefill_kv_tokens == 128  # only the 15-token continuation
     assert bi2[0] == bi[3] and bi2[2:5].tolist() == bi[0:3].tolist() and m.free_blocks == 4
     # all-or-nothing on exhaustion: nothing changes
     with pytest.raises(B2AError) as e:
