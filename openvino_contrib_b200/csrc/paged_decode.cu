@@ -17,7 +17,15 @@
 // with conflict-free 128-bit loads.  Online softmax per warp (row max by warp shuffle), partials of the 4 warps
 // merged in shared memory, one (m, l, O[G][128]) partial per CTA into the workspace; a second kernel merges the
 // splits.  Lengths and tables are read on the device, the grid depends only on max_context_len, so a captured
-// launch stays valid when lengths change.
+// launch stays valid when lengths change.  The split index is the slowest grid dimension (full chunks are dispatched
+// before partial ones), the cache copies carry an evict-first L2 policy, and the merge kernel is launched
+// programmatically dependent.
+//
+// With the heads sharded over several GPUs the merge kernel is also where the outputs are exchanged (PeerPush in
+// launch.cuh): it stores this rank's columns into every rank's staging buffer - as rows plus a flag round, or, when
+// the staging area is large enough, as 8-byte {two values, step number} words that the receiving kernel polls -
+// and a last small kernel copies the complete rows to the caller's output.  paged_decode_kernel<.., kFused = true>
+// is the whole sharded step as one kernel producing the rows in place on every rank.
 #include "launch.cuh"
 
 namespace b2a {
