@@ -30,11 +30,15 @@ sys.path.insert(0, ROOT)
 
 PREFILL = dict(B=4, Hq=32, Hkv=8, S=4096, D=128)
 
-# dram__bytes (read + write) per launch from the profiler captures summarised under profiles/ (bytes)
+# dram__bytes_read + dram__bytes_write per launch, from profiler captures of these kernels on these workloads.
+# They are constants of this file, not measurements of the run that prints them (a profiler cannot run inside a
+# timed benchmark); the line says so next to each figure.
 NCU_TRAFFIC = {
-    "prefill": 429.2e6,   # attn_tc_kernel<bf16, dense>, full workload: profiles/attn_tc_kernel_prefill_cfg2.md
-    "cfg3": 627.5e6,      # paged_decode_kernel<f16, 1>: profiles/paged_decode_kernel_cfg3.md
+    "prefill": 429.2e6,   # attn_tc_kernel<bf16, dense> on the full prefill workload
+    "cfg3": 627.5e6,      # paged_decode_kernel<f16, 1> on the 64-sequence decode
 }
+TRAFFIC_SOURCE = "profiler capture of this kernel on this workload (a constant, not measured in this run)"
+L2_BYTES = 126 * (1 << 20)
 
 
 def peaks():
@@ -236,29 +240,31 @@ def bench_prefill(args, rank, world, local):
     from openvino_contrib_b200.sharding import HeadShard, gather_heads_bhsd, gather_heads_rows  # noqa: F401
     shard = HeadShard(rank, world, Hq, Hkv)
     exchange, group = "none", None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     if world > 1:
-        exchange = os.environ.get("B2A_BENCH_EXCHANGE", "peer")  # "peer": the kernel's epilogue stores to every rank
-        if exchange == "peer":
-            try:
-                from openvino_contrib_b200.sharding import ShardGroup
-                group = ShardGroup(shard, staging_bytes=B * Hq * S * D * 2)
-            except Exception as e:  # CUDA IPC not available: the library collective instead
-                exchange = f"nccl (peer mapping failed: {type(e).__name__})"
+        exchange = "peer stores from the kernel's epilogue"
+        try:
+            from openvino_contrib_b200.sharding import ShardGroup
+            group = ShardGroup(shard, staging_bytes=B * Hq * S * D * 2)
+        except Exception as e:  # CUDA IPC not available: the library collective instead
+            exchange = f"nccl all-gather after the kernel (peer mapping failed: {type(e).__name__})"
     gathered = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device="cuda") if world > 1 and group is None else None
     launches = [0]
 
     def step():
         launches[0] += 1
         if group is not None:
-            return group.sdpa(q, k, v, causal=True)
-        b2a.sdpa(q, k, v, causal=True, out=out)
+            return group.sdpa(q, k, v, causal=True, status=status)
+        b2a.sdpa(q, k, v, causal=True, out=out, status=status)
         if world > 1:
             gather_heads_bhsd(out, shard, buffer=gathered)
+            return gathered
         return out
 
     sampler = ClockSampler(local)
     ms, t0, t1 = timed(step, args.steps, args.warmup, world)
     clocks = sampler.stop(t0, t1)
+    verified = verify_prefill(step, q, k, v, out, shard, status, world)
     n_launch = args.steps
     flops = causal_flops(B, Hq, S, D)
     value = flops / (ms * 1e-3) / 1e12
@@ -271,8 +277,11 @@ def bench_prefill(args, rank, world, local):
     achieved = causal_flops(B, hq_l, S, D) / (kms * 1e-3) / 1e12
     roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
             "frac": achieved / pk["tflops"],
-            "traffic": NCU_TRAFFIC["prefill"] / world if world == 1 else None, "peak_source": pk["source"] + " burst bf16 GEMM",
-            "kernel_ms": kms}
+            "traffic": NCU_TRAFFIC["prefill"] if world == 1 else None,
+            "traffic_source": TRAFFIC_SOURCE if world == 1 else None,
+            "peak_source": pk["source"] + " burst bf16 GEMM", "kernel_ms": kms}
+    if world == 1 and args.only is None:
+        roof["sustained"] = sustained_prefill(kern, causal_flops(B, hq_l, S, D), kms, local, pk)
 
     # end to end through the public API with host buffers: H2D of q,k,v, kernel, D2H of the output
     out_h = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16).pin_memory()
@@ -302,7 +311,41 @@ def bench_prefill(args, rank, world, local):
         dist.barrier()
         group.close()
     return dict(ms=ms, value=value, roofline=roof, e2e=e2e, clocks=clocks, launches=n_launch * (2 if group else 1),
-                exchange=exchange)
+                exchange=exchange, verified=verified)
+
+
+def verify_prefill(step, q, k, v, out, shard, status, world):
+    """After the timed region: the status word is clean, and (N > 1) one more step's full-width result equals, bit for
+    bit, the plain single-GPU kernel run on every rank's shard and all-gathered with NCCL."""
+    import torch.distributed as dist
+    import openvino_contrib_b200 as b2a
+    from openvino_contrib_b200.sharding import gather_heads_bhsd
+    torch.cuda.synchronize()
+    ok = int(status.item()) == 0
+    if world > 1:
+        full = step()
+        b2a.sdpa(q, k, v, causal=True, out=out)
+        ref = gather_heads_bhsd(out, shard)
+        torch.cuda.synchronize()
+        ok = ok and int(status.item()) == 0 and bool(torch.equal(full, ref))
+        t = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = bool(t.item())
+    return ok
+
+
+def sustained_prefill(kern, flops, burst_ms, local, pk, seconds=2.5):
+    """The prefill kernel back to back for a couple of seconds - long enough for the power limit to pull the clock
+    down - with the SM clock sampled meanwhile: the figure to set against the sustained GEMM peak."""
+    n = max(50, int(seconds * 1e3 / burst_ms))
+    sampler = ClockSampler(local, period_s=0.01)
+    ms, t0, t1 = timed(kern, n, 3, 1)
+    clocks = sampler.stop(t0 + 0.5 * (t1 - t0), t1)  # the second half: the clock has settled by then
+    tf = flops / (ms * 1e-3) / 1e12
+    peak = pk.get("tflops_sustained") or pk["tflops"]
+    return {"achieved": tf, "peak": peak, "frac": tf / peak, "launches": n, "seconds": n * ms * 1e-3,
+            "kernel_ms": ms, "sm_mhz_second_half": clocks["sm_mhz"], "reasons": clocks["reasons"],
+            "peak_source": pk["source"] + " bf16 GEMM looped for seconds under the power limit"}
 
 
 def build_decode_problem(n_seqs, ctx_lens, Hq, Hkv, D, seed, device="cuda"):

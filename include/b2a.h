@@ -176,36 +176,57 @@ int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, c
                                 int32_t* status, b2a_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Head-sharded decode over the GPUs of one node (one process per GPU).
+ * Head-sharded attention over the GPUs of one node (one rank per GPU).
  *
  * No counterpart in the reference, which never spans devices (one independent plugin configuration per device
  * id, src/cuda_plugin.cpp:25-32).  Rank r of `world` owns KV heads [r*Hkv/world, (r+1)*Hkv/world) and their query
- * heads; K/V never cross NVLink.  The per-head outputs are exchanged by the merge kernel itself: it stores this
- * rank's columns into a staging buffer on EVERY rank (peer stores over NVLink) and publishes a step flag; a
- * second kernel waits, bounded, for all ranks and copies the full-width rows to `out_full`.
+ * heads; K/V never cross NVLink.  The per-head outputs are exchanged by the kernels that produce them: they store
+ * this rank's part of the result into the group's memory on EVERY rank (peer stores over NVLink); no collective
+ * library is on the data path.
  *
- * Set-up (allocates; not for the hot path): every rank creates its group, the 64-byte handles of all ranks are
- * exchanged by any host-side means (torch.distributed all_gather, MPI, a file), in rank order, and passed to
- * _connect.  staging_bytes >= num_tokens * Hq_total * D * 2 of the largest step; with twice that, decode steps use
- * the low-latency exchange (values travel with the step number in 8-byte words and the receiver polls them: no
- * flag round trip).
+ * Set-up (allocates; not for the hot path): every rank creates its group; when the ranks are processes, the 64-byte
+ * handles of all ranks are exchanged by any host-side means (torch.distributed all_gather, MPI, a file), in rank
+ * order, and passed to _connect; when one process drives several ranks (peer access enabled between their devices)
+ * it passes every rank's b2a_shard_group_output pointer to _connect_pointers instead.
+ * staging_bytes: decode steps into a caller's buffer need 2 * num_tokens * Hq_total * D * 2 of the largest step (the
+ * values travel with the step number in 8-byte words that the receiver polls: no flag round trip), decode steps in
+ * place num_tokens * Hq_total * D * 2, prefill steps the full output.
+ *
+ * Failure handling: every device-side wait on another rank is bounded in wall-clock time (one second unless
+ * _set_wait_ms says otherwise).  When it runs out the kernel returns, the step's result is incomplete and the status
+ * word carries B2A_DEV_TIMEOUT.  After a timeout the ranks' step counters no longer agree: every rank calls
+ * b2a_shard_group_reset (between steps, with a host-side barrier of all ranks before the next step) or the group is
+ * destroyed and rebuilt.
  * ------------------------------------------------------------------------------------------- */
 typedef struct b2a_shard_group b2a_shard_group;
 int b2a_shard_group_create(int rank, int world, size_t staging_bytes, b2a_shard_group** out);
 int b2a_shard_group_handle(const b2a_shard_group* g, unsigned char handle[64]);
 int b2a_shard_group_connect(b2a_shard_group* g, const unsigned char* handles /* world * 64 bytes, rank order */);
+/* Same-process form of _connect: bases[r] = what b2a_shard_group_output returned for rank r's group (bases[rank] is
+ * ignored).  The pointers must be usable from this rank's device (same device, or peer access enabled). */
+int b2a_shard_group_connect_pointers(b2a_shard_group* g, void* const* bases /* world entries, rank order */);
+/* Bound of every device-side wait on another rank for the calls that follow (default 1000 ms). */
+int b2a_shard_group_set_wait_ms(b2a_shard_group* g, int milliseconds);
+/* Synchronises this rank's device, clears the group's flags, counters and staging memory and forgets the kind of
+ * step it served: the state of a fresh group.  Collective in effect, because peers store into this memory: every
+ * rank first lets its own device go idle (cudaDeviceSynchronize), then - after a host-side barrier of all ranks -
+ * calls this, and no rank enqueues a step before a second barrier. */
+int b2a_shard_group_reset(b2a_shard_group* g);
 void b2a_shard_group_destroy(b2a_shard_group* g);
-/* The group's own output buffer on this rank (staging_bytes long, fixed for the group's life).  Passing it as
- * `out_full` to b2a_paged_attention_sharded selects the one-kernel step: the decode kernel's last CTA per
- * (sequence, KV head) merges the splits and stores the rows straight into this buffer on EVERY rank, the grid's last
- * CTA publishes the step and waits (bounded) for the other ranks - one launch, no copy, capturable in a CUDA graph.
- * The rows are then read in place; they stay valid until this rank enqueues its next step on the group. */
+/* The group's own memory on this rank (fixed for the group's life).  Passing it as `out_full` to
+ * b2a_paged_attention_sharded selects the in-place step: the rows are stored straight into this buffer on EVERY
+ * rank, the kernel's last CTA publishes the step and waits (bounded) for the other ranks - one launch, no copy,
+ * capturable in a CUDA graph.  The rows are then read in place; they stay valid until this rank enqueues its next
+ * step on the group. */
 int b2a_shard_group_output(const b2a_shard_group* g, void** out);
 /* Decode step on this rank's heads (`local_desc` carries the LOCAL Hq and Hkv; query [num_tokens, Hq_local*D];
  * caches hold the local KV heads), output exchanged as above: out_full [num_tokens, Hq_local*world*D] is complete
- * on every rank when the stream reaches the end of the call's work.  Decode shapes only (as
+ * on every rank when the stream reaches the end of the call's work.  The decode kernel's last CTA of every
+ * (sequence, KV head) merges the splits and sends the rows; with a caller's `out_full` a second small kernel polls
+ * the arriving words and fills it (two launches per step, capturable).  Decode shapes only (as
  * b2a_paged_attention_noalloc); workspace as b2a_paged_workspace_bytes(local_desc).  All ranks must call it the
- * same number of times; a rank that never arrives makes the others report B2A_DEV_TIMEOUT after about a second. */
+ * same number of times; a rank that never arrives makes the others report B2A_DEV_TIMEOUT when the wait bound
+ * runs out. */
 int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_desc, const void* query,
                                 const void* k_cache, const void* v_cache, const int32_t* past_lens,
                                 const int32_t* subsequence_begins, const int32_t* block_indices,

@@ -52,6 +52,9 @@ SIGNATURES = {
     "b2a_shard_group_create": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]),
     "b2a_shard_group_handle": (C.c_int, [C.c_void_p, C.c_char_p]),
     "b2a_shard_group_connect": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "b2a_shard_group_connect_pointers": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b2a_shard_group_set_wait_ms": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2a_shard_group_reset": (C.c_int, [C.c_void_p]),
     "b2a_shard_group_destroy": (None, [C.c_void_p]),
     "b2a_shard_group_output": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "b2a_paged_attention_sharded": (C.c_int, [C.c_void_p, C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p,

@@ -1,4 +1,5 @@
 // extern "C" entry points of libb2a.so: host-side validation and dispatch, nothing else.
+#include <atomic>
 #include <cmath>
 #include <cstring>
 
@@ -7,14 +8,32 @@
 namespace b2a {
 
 int device_sm_count() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    if (dev >= 0 && dev < 64) {
+        const int c = cached[dev].load(std::memory_order_relaxed);
+        if (c > 0) return c;
+    }
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    if (dev >= 0 && dev < 64) cached[dev] = n;
+    if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_relaxed);
     return n;
+}
+
+int resolve_paged_desc(const b2a_paged_desc* desc, b2a_paged_desc& d) {
+    if (desc == nullptr) return B2A_ERR_NULL;
+    d = *desc;
+    if (d.q_dtype != B2A_F32 && d.q_dtype != B2A_F16 && d.q_dtype != B2A_BF16) return B2A_ERR_DTYPE;
+    if (d.kv_dtype != B2A_U8 && d.kv_dtype != B2A_F16 && d.kv_dtype != B2A_BF16) return B2A_ERR_DTYPE;
+    if (d.Hq <= 0 || d.Hkv <= 0 || d.D <= 0 || d.Dv <= 0 || d.block_size <= 0) return B2A_ERR_DIM;
+    if (d.Hq % d.Hkv != 0 || d.Hq > 65535) return B2A_ERR_DIM;
+    if (d.num_seqs < 0 || d.num_seqs > 65535 || d.num_tokens < 0 || d.num_blocks_total < 0) return B2A_ERR_DIM;
+    if (d.max_context_len < 0 || d.max_q_len < 0 || d.sliding_window < 0) return B2A_ERR_DIM;
+    if (d.kv_dtype == B2A_U8 && ((d.block_size * d.D) % 2 != 0 || (d.block_size * d.Dv) % 2 != 0)) return B2A_ERR_ALIGN;
+    if (!(d.scale >= 0.f) || std::isinf(d.scale)) return B2A_ERR_DIM;
+    if (d.scale == 0.f) d.scale = 1.0f / std::sqrt(static_cast<float>(d.D));
+    return B2A_OK;
 }
 
 namespace {
@@ -64,21 +83,6 @@ int resolve_sdpa(const b2a_sdpa_desc* desc, SdpaResolved& r) {
     if (all_zero(r.vs)) contiguous(r.vs, d.B, d.Hkv, d.Skv, d.Dv);
     if (all_zero(r.os)) contiguous(r.os, d.B, d.Hq, d.Sq, d.Dv);
     if (r.qs[3] != 1 || r.ks[3] != 1 || r.vs[3] != 1 || r.os[3] != 1) return B2A_ERR_ALIGN;
-    return B2A_OK;
-}
-
-int resolve_paged(const b2a_paged_desc* desc, b2a_paged_desc& d) {
-    if (desc == nullptr) return B2A_ERR_NULL;
-    d = *desc;
-    if (d.q_dtype != B2A_F32 && d.q_dtype != B2A_F16 && d.q_dtype != B2A_BF16) return B2A_ERR_DTYPE;
-    if (d.kv_dtype != B2A_U8 && d.kv_dtype != B2A_F16 && d.kv_dtype != B2A_BF16) return B2A_ERR_DTYPE;
-    if (d.Hq <= 0 || d.Hkv <= 0 || d.D <= 0 || d.Dv <= 0 || d.block_size <= 0) return B2A_ERR_DIM;
-    if (d.Hq % d.Hkv != 0 || d.Hq > 65535) return B2A_ERR_DIM;
-    if (d.num_seqs < 0 || d.num_seqs > 65535 || d.num_tokens < 0 || d.num_blocks_total < 0) return B2A_ERR_DIM;
-    if (d.max_context_len < 0 || d.max_q_len < 0 || d.sliding_window < 0) return B2A_ERR_DIM;
-    if (d.kv_dtype == B2A_U8 && ((d.block_size * d.D) % 2 != 0 || (d.block_size * d.Dv) % 2 != 0)) return B2A_ERR_ALIGN;
-    if (!(d.scale >= 0.f) || std::isinf(d.scale)) return B2A_ERR_DIM;
-    if (d.scale == 0.f) d.scale = 1.0f / std::sqrt(static_cast<float>(d.D));
     return B2A_OK;
 }
 
@@ -154,7 +158,7 @@ size_t b2a_paged_chunk_bytes(int32_t kv_dtype, int32_t block_size, int32_t d) {
 int b2a_paged_workspace_bytes(const b2a_paged_desc* desc, int sm_count, size_t* out_bytes) {
     if (out_bytes == nullptr) return B2A_ERR_NULL;
     b2a_paged_desc d;
-    const int rc = resolve_paged(desc, d);
+    const int rc = resolve_paged_desc(desc, d);
     if (rc != B2A_OK) return rc;
     if (sm_count <= 0) sm_count = device_sm_count();
     if (sm_count <= 0) sm_count = 148;
@@ -173,7 +177,7 @@ int b2a_paged_kv_store(const b2a_paged_desc* desc, const void* key, const void* 
                        const int32_t* past_lens, const int32_t* subsequence_begins, const int32_t* block_indices,
                        const int32_t* block_indices_begins, int32_t* status, b2a_stream_t stream) {
     b2a_paged_desc d;
-    const int rc = resolve_paged(desc, d);
+    const int rc = resolve_paged_desc(desc, d);
     if (rc != B2A_OK) return rc;
     if (d.num_tokens == 0 || d.num_seqs == 0) return B2A_OK;
     if (key == nullptr || value == nullptr || k_cache == nullptr || v_cache == nullptr || past_lens == nullptr ||
@@ -190,7 +194,7 @@ int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const voi
                         const int32_t* block_indices_begins, void* out, void* workspace, size_t workspace_bytes,
                         int32_t* status, b2a_stream_t stream) {
     b2a_paged_desc d;
-    const int rc = resolve_paged(desc, d);
+    const int rc = resolve_paged_desc(desc, d);
     if (rc != B2A_OK) return rc;
     if (d.num_tokens == 0 || d.num_seqs == 0) return B2A_OK;
     if (query == nullptr || k_cache == nullptr || v_cache == nullptr || out == nullptr || past_lens == nullptr ||
@@ -229,7 +233,7 @@ int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, c
                                 const int32_t* block_indices, const int32_t* block_indices_begins, void* out,
                                 int32_t* status, b2a_stream_t stream) {
     b2a_paged_desc d;
-    const int rc = resolve_paged(desc, d);
+    const int rc = resolve_paged_desc(desc, d);
     if (rc != B2A_OK) return rc;
     if (d.num_tokens == 0 || d.num_seqs == 0) return B2A_OK;
     if (query == nullptr || k_cache == nullptr || v_cache == nullptr || out == nullptr || past_lens == nullptr ||

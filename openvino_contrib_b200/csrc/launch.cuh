@@ -18,32 +18,32 @@ int paged_generic_launch(const b2a_paged_desc& d, const void* query, const void*
 int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* value, void* k_cache, void* v_cache,
                           const PagedTables& t, int32_t* status, cudaStream_t stream);
 
-// Head-sharded decode across the GPUs of a node: where the merge kernel sends a rank's output columns.
-// Every rank owns two full-width staging buffers (alternating by step), an array of per-source-rank flags and two
-// counters, all inside one allocation that its peers map through CUDA IPC.  The merge kernel of rank r stores its
-// columns into the staging buffer of EVERY rank (plain peer stores over NVLink), and its last CTA publishes the
-// step number in every rank's flags[r]; a second kernel on each rank waits (bounded) until all flags show the
-// step and copies the completed rows to the caller's output.  No collective library call is on the path.
+// Head-sharded decode across the GPUs of a node: where the decode kernel delivers a rank's output columns.
+// Every rank owns two full-width staging buffers, flag arrays and counters, all inside one allocation that its peers
+// map (shard_group.cu).  The decode kernel of rank r merges the splits of a (sequence, KV head) in the CTA that
+// finished last (ticket counters) and stores the rows into the memory of EVERY rank - plain peer stores over NVLink;
+// no collective library call is on the path.
 constexpr int kMaxShardWorld = 8;
 struct PeerPush {
     void* staging[kMaxShardWorld][2];  // [rank][step parity]: that rank's staging buffers as mapped here
-    int32_t* flags[kMaxShardWorld];    // [rank]: that rank's flags array (one int per source rank)
-    int32_t* step_counter;             // local: number of steps published so far
-    int32_t* done_counter;             // local: merge CTAs finished in the current step (self-resetting)
+    int32_t* flags[kMaxShardWorld];    // [rank]: that rank's "step published" flags (one int per source rank)
+    int32_t* step_counter;             // local: number of steps completed so far
+    int32_t* done_counter;             // local: CTAs finished in the current step (self-resetting)
     int rank, world;                   // world == 0: not sharded
     int row_elems;                     // elements of one full-width output row (Hq_total * D)
     int col_offset;                    // first column of this rank's heads
-    // Low-latency form (when the staging buffers are twice as large as the output): every pair of 16-bit values
-    // travels as one 8-byte store {two values, step number}, which arrives whole or not at all, so the receiver
-    // simply polls each word for the step number - no fence, no flag round trip, no rendezvous of whole kernels.
+    // ll != 0, low-latency form (caller's output buffer; staging buffers twice as large as the output): every pair of
+    // 16-bit values travels as one 8-byte store {two values, step number} into staging[r][step parity], which arrives
+    // whole or not at all, so the receiving kernel simply polls each word for the step number - no fence, no flag
+    // round trip, no rendezvous of whole kernels.
+    // ll == 0, in place: the rows go into staging[r][0] of every rank r - the ranks' fixed output buffers, read where
+    // they are.  A rank announces in started[r][rank] that it has begun step s, i.e. that its readers of step s-1 are
+    // done; nobody stores into a rank's buffer for step s before that; the grid's last CTA publishes the step in
+    // flags[r][rank] and waits for the other ranks.
     int ll;
-    // Single-kernel step (group_counters != nullptr): the decode kernel's last CTA of every (sequence, KV head)
-    // merges that group's splits and stores the result into staging[r][0] of every rank r - the ranks' fixed
-    // output buffers, read in place - and the grid's last CTA publishes the step and waits for the other ranks.
-    // A rank announces in started[r][rank] that it has begun step s, i.e. that its readers of step s-1 are done;
-    // nobody stores into a rank's buffer for step s before that.
-    int32_t* group_counters;           // local: one per (sequence, KV head), self-resetting
+    int32_t* group_counters;           // local: one ticket counter per (sequence, KV head), self-resetting
     int32_t* started[kMaxShardWorld];  // [rank]: that rank's array of "rank i has begun step s" (one int per source rank)
+    long long wait_ns;                 // bound of every wait on another rank, in nanoseconds of wall-clock time
 };
 
 // paged_decode.cu — split-K decode over a u8 cache (D = Dv = 128, block 16, one query token per sequence)
@@ -81,11 +81,13 @@ struct TcPeerOut {
     int hq_total;                      // heads of the full output
     int head_offset;                   // first head of this rank
     int32_t step;                      // value published when the step is complete (increases by one per step)
+    long long wait_ns;                 // bound of the wait for the other ranks, nanoseconds of wall-clock time
 };
 int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
                    const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
                    cudaStream_t stream, const TcPeerOut* peers = nullptr);
-int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, int32_t* status, cudaStream_t stream);
+int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, long long wait_ns, int32_t* status,
+                          cudaStream_t stream);
 
 // the same kernel body over a paged u8 cache: the multi-token sequences of a step (sequences with one new token are
 // left to the decode kernel, which in turn skips the others)
@@ -95,5 +97,8 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
                     const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream);
 
 int device_sm_count();
+
+// api.cu — validation of a paged descriptor shared by the entry points (fills the default scale)
+int resolve_paged_desc(const b2a_paged_desc* desc, b2a_paged_desc& out);
 
 }  // namespace b2a

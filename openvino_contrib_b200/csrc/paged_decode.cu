@@ -21,11 +21,13 @@
 // before partial ones), the cache copies carry an evict-first L2 policy, and the merge kernel is launched
 // programmatically dependent.
 //
-// With the heads sharded over several GPUs the merge kernel is also where the outputs are exchanged (PeerPush in
-// launch.cuh): it stores this rank's columns into every rank's staging buffer - as rows plus a flag round, or, when
-// the staging area is large enough, as 8-byte {two values, step number} words that the receiving kernel polls -
-// and a last small kernel copies the complete rows to the caller's output.  paged_decode_kernel<.., kFused = true>
-// is the whole sharded step as one kernel producing the rows in place on every rank.
+// With the heads sharded over several GPUs the decode kernel also merges and sends (PeerPush in launch.cuh): the
+// last CTA of every (sequence, KV head) to finish - a ticket counter in the shard group's memory - merges that
+// group's partials and stores the rows into every rank's memory, either as 8-byte {two values, step number} words
+// that a small receiving kernel polls and copies to the caller's output, or in place into the ranks' fixed output
+// buffers behind a "step begun" / "step published" flag protocol.  No separate merge launch in either form.
+#include <atomic>
+
 #include "launch.cuh"
 
 namespace b2a {
@@ -112,15 +114,16 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 __device__ __forceinline__ float h2_lo(uint32_t v) { return __half2float(__ushort_as_half(v & 0xFFFFu)); }
 __device__ __forceinline__ float h2_hi(uint32_t v) { return __half2float(__ushort_as_half(v >> 16)); }
 
+// two consecutive query values, as loaded (f16 or bf16 bits), to half2 bits
 template <typename T>
-__device__ __forceinline__ uint32_t load_q_pair(const T* p);  // two consecutive query values as half2 bits
+__device__ __forceinline__ uint32_t q_word_to_h2(uint32_t w);
 template <>
-__device__ __forceinline__ uint32_t load_q_pair<__half>(const __half* p) {
-    return *reinterpret_cast<const uint32_t*>(p);
+__device__ __forceinline__ uint32_t q_word_to_h2<__half>(uint32_t w) {
+    return w;
 }
 template <>
-__device__ __forceinline__ uint32_t load_q_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
-    return pack_h2(__bfloat162float(p[0]), __bfloat162float(p[1]));
+__device__ __forceinline__ uint32_t q_word_to_h2<__nv_bfloat16>(uint32_t w) {
+    return pack_h2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 
 __device__ __forceinline__ int first_block_of(int ctx, int sliding_window) {
@@ -128,40 +131,67 @@ __device__ __forceinline__ int first_block_of(int ctx, int sliding_window) {
     return first_pos / kBS;
 }
 
-// The walk over this CTA's chunk of one (sequence, KV head).  Returns false when the CTA has nothing to do (idle or
-// multi-token sequence, chunk past the context, inconsistent tables - reported); otherwise its partial is in the
-// workspace, `nsplit` is the number of CTAs of this sequence that write one, `tok` the sequence's token row.
-template <typename T, int NT>
-__device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out) {
+// What a CTA found when it looked at its (sequence, KV head, split).
+enum ChunkState {
+    kChunkIdle = 0,     // nothing to do: a split past the end of the context (no partial, no ticket)
+    kChunkWorked = 1,   // its partial is in the workspace
+    kChunkNotRow = 2,   // the sequence is not a one-token decode row (a mixed step's prefill sequence, an idle slot)
+    kChunkInvalid = 3   // inconsistent tables (reported)
+};
+
+// The walk over this CTA's chunk of one (sequence, KV head).  On kChunkWorked its partial is in the workspace, `nsplit`
+// is the number of CTAs of this sequence that write one and `tok` the sequence's token row.  With kRowIsSeq the
+// token row must equal the sequence index (the sharded exchange addresses rows by sequence), else kChunkInvalid.
+template <typename T, int NT, bool kRowIsSeq>
+__device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out) {
     const int hk = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tid4 = lane & 3;
 
+    // A CTA's start is a chain of dependent global loads (tables -> block ids -> cache rows), and in a step that
+    // fills the GPU only once nothing hides it.  So the chain is kept as short as it can be: the five table entries
+    // are requested together, the query rows right behind them, then the block ids, then the first cache stages;
+    // the query fragments are put together while those are in flight.
     const int tok = p.t.subsequence_begins[seq];
-    const int qlen = p.t.subsequence_begins[seq + 1] - tok;
-    if (qlen != 1) return false;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
+    const int tok_end = p.t.subsequence_begins[seq + 1];
     const int past = p.t.past_lens[seq];
+    const int bib0 = p.t.block_indices_begins[seq];
+    const int bib1 = p.t.block_indices_begins[seq + 1];
+    if (tok_end - tok != 1) return kChunkNotRow;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
     const int ctx = past + 1;  // the query token sits at position `past` and sees 0..past
     const int nblk = (ctx + kBS - 1) / kBS;
-    if (past < 0 || nblk > p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq]) {
+    if (past < 0 || nblk > bib1 - bib0 || tok < 0 || tok >= p.t.num_tokens || (kRowIsSeq && tok != seq)) {
         if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return false;
+        return kChunkInvalid;
     }
     const int first_pos = p.sliding_window > 0 ? max(0, ctx - p.sliding_window) : 0;
     const int blk_lo = first_block_of(ctx, p.sliding_window);
     if (nblk - blk_lo > p.max_splits * p.blocks_per_cta) {  // context longer than the max_context_len the grid was sized for
         if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return false;
+        return kChunkInvalid;
     }
     nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
     tok_out = tok;
     const int my_lo = blk_lo + split * p.blocks_per_cta;
     const int my_hi = min(nblk, my_lo + p.blocks_per_cta);
-    if (my_lo >= my_hi) return false;
+    if (my_lo >= my_hi) return kChunkIdle;
+
+    // ---- query rows of this thread's heads as loaded: head nt*8 + gid, elements tid4*32 .. +31 (64 bytes)
+    const T* qrow = reinterpret_cast<const T*>(p.query) + (static_cast<size_t>(tok) * p.Hq + hk * p.G) * kD;
+    uint4 qraw[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int n = nt * 8 + gid;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            qraw[nt][c] = make_uint4(0u, 0u, 0u, 0u);
+            if (n < p.G) qraw[nt][c] = reinterpret_cast<const uint4*>(qrow + n * kD + tid4 * 32)[c];
+        }
+    }
 
     // blocks of this warp: my_lo + warp + 4*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
     const int n_w = (my_hi - my_lo - warp + kWarps - 1) / kWarps;
-    const int32_t* btab = p.t.block_indices + p.t.block_indices_begins[seq];
+    const int32_t* btab = p.t.block_indices + bib0;
     int my_phys = 0;
     if (lane < n_w) {
         my_phys = btab[my_lo + warp + kWarps * lane];
@@ -196,25 +226,29 @@ __device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* sme
         }
     };
 
+    // ---- pipeline prologue: the first stages are on their way before the query is touched
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < n_w) issue(s);
+        cp_async_commit();
+    }
+
     // ---- query fragments (B operand of QK^T) and per-head sums of Q
-    const T* qrow = reinterpret_cast<const T*>(p.query) + (static_cast<size_t>(tok) * p.Hq + hk * p.G) * kD;
     uint32_t qf[NT][8][2];
     float qsum_a[NT], qsum_b[NT];  // heads nt*8 + 2*tid4 and + 1
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const int n = nt * 8 + gid;
         float part = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            uint32_t b0 = 0, b1 = 0;
-            if (n < p.G) {
-                const T* src = qrow + n * kD + tid4 * 32 + 4 * j;
-                b0 = load_q_pair<T>(src);
-                b1 = load_q_pair<T>(src + 2);
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t w[4] = {qraw[nt][c].x, qraw[nt][c].y, qraw[nt][c].z, qraw[nt][c].w};
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {  // j = 2c + hf covers elements 4j .. 4j+3 of the thread's 32
+                const uint32_t b0 = q_word_to_h2<T>(w[2 * hf]), b1 = q_word_to_h2<T>(w[2 * hf + 1]);
+                qf[nt][2 * c + hf][0] = b0;
+                qf[nt][2 * c + hf][1] = b1;
+                part += h2_lo(b0) + h2_hi(b0) + h2_lo(b1) + h2_hi(b1);
             }
-            qf[nt][j][0] = b0;
-            qf[nt][j][1] = b1;
-            part += h2_lo(b0) + h2_hi(b0) + h2_lo(b1) + h2_hi(b1);
         }
         part += __shfl_xor_sync(0xffffffffu, part, 1);
         part += __shfl_xor_sync(0xffffffffu, part, 2);  // sum of Q[head nt*8+gid][:]
@@ -230,13 +264,6 @@ __device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* sme
         l_a[nt] = l_b[nt] = corr_a[nt] = corr_b[nt] = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[nt][j][0] = acc[nt][j][1] = acc[nt][j][2] = acc[nt][j][3] = 0.f;
-    }
-
-    // ---- pipeline prologue
-#pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
-        if (s < n_w) issue(s);
-        cp_async_commit();
     }
 
     const int sw_k = (gid & 7);  // swizzle key of rows gid and gid+8
@@ -407,7 +434,7 @@ __device__ __forceinline__ bool decode_chunk(const DecodeParams& p, uint8_t* sme
             p.ws_ml[slot * 2 + 1] = l;
         }
     }
-    return true;
+    return kChunkWorked;
 }
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
@@ -418,26 +445,32 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// wall-clock nanoseconds: waits on other GPUs are bounded in real time, whatever the SM clock does
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 template <typename T>
-__device__ __forceinline__ uint2 pack4(float a, float b, float c, float d);
+__device__ __forceinline__ uint32_t pack2(float a, float b);
 template <>
-__device__ __forceinline__ uint2 pack4<__half>(float a, float b, float c, float d) {
-    return make_uint2(pack_h2(a, b), pack_h2(c, d));
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    return pack_h2(a, b);
 }
 template <>
-__device__ __forceinline__ uint2 pack4<__nv_bfloat16>(float a, float b, float c, float d) {
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-    return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Bounded wait on `n` flags (one thread per flag) until each shows `epoch`; B2A_DEV_TIMEOUT after about a second.
-__device__ __forceinline__ void wait_flags(const int32_t* flags, int n, int32_t epoch, int32_t* status) {
+// Bounded wait on `n` flags (one thread per flag) until each shows `epoch`; B2A_DEV_TIMEOUT after `limit_ns`.
+__device__ __forceinline__ void wait_flags(const int32_t* flags, int n, int32_t epoch, long long limit_ns, int32_t* status) {
     if (static_cast<int>(threadIdx.x) < n) {
         const int32_t* flag = flags + threadIdx.x;
-        const long long t0 = clock64();
+        const long long t0 = global_ns();
         while (ld_acquire_sys(flag) - epoch < 0) {
-            if (clock64() - t0 > (1LL << 31)) {
+            if (global_ns() - t0 > limit_ns) {
                 report(status, B2A_DEV_TIMEOUT);
                 break;
             }
@@ -445,27 +478,132 @@ __device__ __forceinline__ void wait_flags(const int32_t* flags, int n, int32_t 
     }
 }
 
-// The whole decode step in one launch, for sharded heads (PeerPush with group_counters).  After its chunk, a CTA
-// takes a ticket of its (sequence, KV head); the CTA that gets the last ticket merges the group's partials - 32
-// threads per query head, four heads at a time, every split's 16-byte piece requested before any is used - and
-// stores the normalised rows into the output buffer of every rank.  The grid's last CTA then publishes the step and
-// waits for the other ranks' steps, so the output is complete on this rank when the kernel ends.
-template <typename T, int NT, bool kFused>
+// Merge of the split partials of one (sequence, KV head) by the CTA that finished last, and delivery of the rows.
+// kDims consecutive output columns per thread (4: 32 threads per head, four heads per round; 8: 16 threads per head,
+// eight heads per round - taken for groups of more than four heads so that one round covers the group).  The
+// partials come from L2 (other CTAs wrote them); eight splits are requested at a time before any is used.  The
+// arithmetic is that of paged_decode_merge_kernel, operation for operation (maximum over all splits first, then the
+// weighted sums in split order, one division per value), so a sharded step gives the bits of the single-GPU path.
+//   kLL  : every pair of 16-bit values travels as one 8-byte store {two values, step number} into staging[r][parity]
+//          of every rank r; such a store arrives whole or not at all, so the receiver simply polls the word.
+//   !kLL : the rows are stored as they are - into staging[r][0] of every rank (the ranks' fixed output buffers), or,
+//          without a group, into the caller's output.
+template <typename T, int kDims, bool kLL>
+__device__ __forceinline__ void merge_and_deliver(const DecodeParams& p, int seq, int hk, int tok, int nsplit,
+                                                  int32_t epoch) {
+    constexpr int kVec = kDims / 4;            // float4 loads per split
+    constexpr int kLanes = kD / kDims;         // threads per head
+    constexpr int kHeadsPerRound = (kWarps * 32) / kLanes;
+    constexpr int kBatch = 8;
+    const int tid = threadIdx.x;
+    const int d0 = (tid % kLanes) * kDims;
+    for (int g = tid / kLanes; g < p.G; g += kHeadsPerRound) {
+        const int h = hk * p.G + g;
+        const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
+        const float2* mlp = reinterpret_cast<const float2*>(p.ws_ml) + base;
+        float l = 0.f, o[kDims];
+#pragma unroll
+        for (int i = 0; i < kDims; ++i) o[i] = 0.f;
+        float2 ml[kBatch];
+        float4 v[kBatch][kVec];
+        auto load_batch = [&](int s0) {
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int sp = min(s0 + i, nsplit - 1);  // the tail repeats the last split (dropped below)
+                ml[i] = __ldcg(mlp + sp);
+#pragma unroll
+                for (int q = 0; q < kVec; ++q)
+                    v[i][q] = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (base + sp) * kD + d0) + q);
+            }
+        };
+        load_batch(0);
+        float mc = kNegBig;
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) mc = fmaxf(mc, ml[i].x);
+#pragma unroll 8
+        for (int sp = kBatch; sp < nsplit; ++sp) mc = fmaxf(mc, __ldcg(mlp + sp).x);
+        for (int s0 = 0; s0 < nsplit; s0 += kBatch) {
+            if (s0 > 0) load_batch(s0);
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                if (s0 + i < nsplit) {
+                    const float f = ex2(ml[i].x - mc);
+                    l += ml[i].y * f;
+#pragma unroll
+                    for (int q = 0; q < kVec; ++q) {
+                        o[4 * q + 0] += v[i][q].x * f;
+                        o[4 * q + 1] += v[i][q].y * f;
+                        o[4 * q + 2] += v[i][q].z * f;
+                        o[4 * q + 3] += v[i][q].w * f;
+                    }
+                }
+            }
+        }
+        const bool nz = l > 0.f;
+        uint32_t w[kDims / 2];
+#pragma unroll
+        for (int i = 0; i < kDims / 2; ++i) w[i] = pack2<T>(nz ? o[2 * i] / l : 0.f, nz ? o[2 * i + 1] / l : 0.f);
+        if constexpr (kLL) {
+            const size_t at = (static_cast<size_t>(seq) * p.push.row_elems + p.push.col_offset + h * kD + d0) >> 1;
+            const int parity = epoch & 1;
+            for (int r = 0; r < p.push.world; ++r) {
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint2*>(p.push.staging[r][parity]) + at);
+#pragma unroll
+                for (int q = 0; q < kDims / 4; ++q)
+                    dst[q] = make_uint4(w[2 * q], static_cast<uint32_t>(epoch), w[2 * q + 1], static_cast<uint32_t>(epoch));
+            }
+        } else if (p.push.world > 0) {
+            const size_t at = static_cast<size_t>(tok) * p.push.row_elems + p.push.col_offset + h * kD + d0;
+            for (int r = 0; r < p.push.world; ++r) {
+                uint2* dst = reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.push.staging[r][0]) + at);
+#pragma unroll
+                for (int q = 0; q < kDims / 4; ++q) dst[q] = make_uint2(w[2 * q], w[2 * q + 1]);
+            }
+        } else {
+            uint2* dst = reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD + d0);
+#pragma unroll
+            for (int q = 0; q < kDims / 4; ++q) dst[q] = make_uint2(w[2 * q], w[2 * q + 1]);
+        }
+    }
+}
+
+// Low-latency form, a sequence whose row cannot be computed (inconsistent tables: reported): every rank's receiver
+// still waits for the row's words, so zeros are sent in their place.
+__device__ __forceinline__ void send_zero_row_segment(const DecodeParams& p, int seq, int hk, int32_t epoch) {
+    const int words = p.G * kD / 2;  // 8-byte words of this KV head's segment of the row
+    const size_t at = (static_cast<size_t>(seq) * p.push.row_elems + p.push.col_offset + hk * p.G * kD) >> 1;
+    const uint2 word = make_uint2(0u, static_cast<uint32_t>(epoch));
+    for (int r = 0; r < p.push.world; ++r) {
+        uint2* dst = reinterpret_cast<uint2*>(p.push.staging[r][epoch & 1]) + at;
+        for (int i = threadIdx.x; i < words; i += kWarps * 32) dst[i] = word;
+    }
+}
+
+// kMode 0: the CTA leaves its partial in the workspace and paged_decode_merge_kernel follows (single GPU).
+// kMode 1, 2: the whole step of a head shard in this launch (PeerPush).  After its chunk a CTA takes a ticket of its
+// (sequence, KV head); the CTA that gets the last ticket merges the group's partials and delivers the rows to every
+// rank - mode 1 as low-latency words for the receiving kernel, mode 2 in place: there the rows land in the ranks'
+// fixed output buffers, so a rank first announces that it has begun the step (its readers of the previous output are
+// done), nobody stores before every rank has, and the grid's last CTA publishes the step and waits for the other
+// ranks' steps, so that the output is complete on this rank when the kernel ends.
+template <typename T, int NT, int kMode>
 __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     int nsplit = 0, tok = 0;
     grid_dependency_wait();     // the cache rows of this step's new tokens and the query come from earlier kernels
-    grid_launch_dependents();   // the merge kernel's CTAs may take their seats while this grid drains
-    if constexpr (!kFused) {
-        decode_chunk<T, NT>(p, smem, nsplit, tok);
+    grid_launch_dependents();   // the next kernel's CTAs may take their seats while this grid drains
+    if constexpr (kMode == 0) {
+        decode_chunk<T, NT, false>(p, smem, nsplit, tok);
     } else {
+        constexpr bool kLL = kMode == 1;
         __shared__ int s_role;
         const int tid = threadIdx.x, hk = blockIdx.x, seq = blockIdx.y;
         const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
+        if (!kLL && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
             st_release_sys(p.push.started[tid] + p.push.rank, epoch);  // this rank's readers of the previous step are done
-        const bool worked = decode_chunk<T, NT>(p, smem, nsplit, tok);
-        if (worked) {
+        const ChunkState state = decode_chunk<T, NT, kLL>(p, smem, nsplit, tok);
+        if (tid == 0) s_role = 0;
+        if (state == kChunkWorked) {
             __threadfence();  // this CTA's partial before its ticket
             __syncthreads();
             if (tid == 0) {
@@ -476,57 +614,61 @@ __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const Deco
             }
             __syncthreads();
             if (s_role == 1) {
-                __threadfence();
-                wait_flags(p.push.started[p.push.rank], p.push.world, epoch, p.status);  // every rank has begun this step
-                __syncthreads();
-                const int d4 = (tid & 31) * 4;
-                for (int g = tid >> 5; g < p.G; g += kWarps) {
-                    const int h = hk * p.G + g;
-                    const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
-                    float mc = kNegBig;
-                    for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, __ldcg(p.ws_ml + (base + s) * 2));
-                    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, l = 0.f;
-#pragma unroll 4
-                    for (int s = 0; s < nsplit; ++s) {
-                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (base + s) * 2));
-                        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (base + s) * kD + d4));
-                        const float f = ex2(ml.x - mc);
-                        o0 += v.x * f;
-                        o1 += v.y * f;
-                        o2 += v.z * f;
-                        o3 += v.w * f;
-                        l += ml.y * f;
-                    }
-                    const bool nz = l > 0.f;
-                    const uint2 val = pack4<T>(nz ? o0 / l : 0.f, nz ? o1 / l : 0.f, nz ? o2 / l : 0.f, nz ? o3 / l : 0.f);
-                    const size_t at = static_cast<size_t>(tok) * p.push.row_elems + p.push.col_offset + h * kD + d4;
-                    for (int r = 0; r < p.push.world; ++r)
-                        *reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.push.staging[r][0]) + at) = val;
+                __threadfence();  // the other CTAs' partials after the ticket
+                if (!kLL) {
+                    wait_flags(p.push.started[p.push.rank], p.push.world, epoch, p.push.wait_ns, p.status);  // every rank has begun this step
+                    __syncthreads();
                 }
+                if (p.G > 4) merge_and_deliver<T, 8, kLL>(p, seq, hk, tok, nsplit, epoch);
+                else merge_and_deliver<T, 4, kLL>(p, seq, hk, tok, nsplit, epoch);
+                if (!kLL) __threadfence_system();  // this CTA's peer stores before its arrival below
             }
+        } else if (kLL && (state == kChunkInvalid || state == kChunkNotRow) && blockIdx.z == 0) {
+            if (state == kChunkNotRow && tid == 0) report(p.status, B2A_DEV_BAD_LEN);
+            send_zero_row_segment(p, seq, hk, epoch);
         }
-        if (worked && s_role == 1) __threadfence_system();  // this CTA's peer stores before its arrival
         __syncthreads();
         if (tid == 0) {
             const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
             const bool last = atomicAdd(p.push.done_counter, 1) == total - 1;
             if (last) {
-                *p.push.done_counter = 0;
-                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;
-                __threadfence_system();
-                for (int r = 0; r < p.push.world; ++r) st_release_sys(p.push.flags[r] + p.push.rank, epoch);
+                *p.push.done_counter = 0;  // every CTA has arrived: ready for the next step
+                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;  // read by the next kernel on the stream
+                if (!kLL) {
+                    __threadfence_system();
+                    for (int r = 0; r < p.push.world; ++r) st_release_sys(p.push.flags[r] + p.push.rank, epoch);
+                }
             }
             s_role = last ? 2 : 0;
         }
-        __syncthreads();
-        if (s_role == 2) wait_flags(p.push.flags[p.push.rank], p.push.world, epoch, p.status);
+        if (!kLL) {
+            __syncthreads();
+            if (s_role == 2) wait_flags(p.push.flags[p.push.rank], p.push.world, epoch, p.push.wait_ns, p.status);
+        }
     }
 }
 
-// out[d] of one (sequence, query head) from its split partials: sum_s O_s[d] 2^(m_s - m) / sum_s l_s 2^(m_s - m) with
+// Merge the split partials of one (sequence, query head): out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m) with
 // m = max_s m_s.  The (m, l) pairs are read as 8-byte loads and both loops are unrolled so that eight partials are in
 // flight per thread (the loads are independent; only the tiny accumulation is a chain).
-__device__ __forceinline__ float merge_splits(const DecodeParams& p, size_t base, int nsplit, int d) {
+template <typename T>
+__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodeParams p) {
+    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    grid_dependency_wait();  // the partials
+    grid_launch_dependents();
+    const int tok = p.t.subsequence_begins[seq];
+    const int qlen = p.t.subsequence_begins[seq + 1] - tok;
+    const int past = p.t.past_lens[seq];
+    const int ctx = past + 1;
+    const int nblk = (ctx + kBS - 1) / kBS;
+    const int blk_lo = first_block_of(ctx, p.sliding_window);
+    // the same conditions under which the decode kernel wrote partials
+    const bool valid = qlen == 1 && past >= 0 && tok >= 0 && tok < p.t.num_tokens &&
+                       nblk <= p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq] &&
+                       nblk - blk_lo <= p.max_splits * p.blocks_per_cta;
+    if (!valid) return;
+    const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
+    const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
     const float2* ml = reinterpret_cast<const float2*>(p.ws_ml) + base;
     float mc = kNegBig;
 #pragma unroll 8
@@ -539,129 +681,29 @@ __device__ __forceinline__ float merge_splits(const DecodeParams& p, size_t base
         o += p.ws_o[(base + s) * kD + d] * f;
         l += v.y * f;
     }
-    return l > 0.f ? o / l : 0.f;
+    T* orow = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD;
+    orow[d] = from_f32<T>(l > 0.f ? o / l : 0.f);
 }
 
-// Merge the split partials of one (sequence, query head): out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
-// With sharded heads the row segment goes to every rank's staging buffer instead, and the last CTA of the grid
-// publishes the step (see PeerPush).
-template <typename T>
-__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodeParams p) {
-    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
-    grid_dependency_wait();  // the partials
-    grid_launch_dependents();
-    const bool pushing = p.push.world > 0;
-    const int parity = pushing ? ((*reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1) & 1) : 0;
-    const int tok = p.t.subsequence_begins[seq];
-    const int qlen = p.t.subsequence_begins[seq + 1] - tok;
-    const int past = p.t.past_lens[seq];
-    const int ctx = past + 1;
-    const int nblk = (ctx + kBS - 1) / kBS;
-    const bool valid = qlen == 1 && past >= 0 &&
-                       nblk <= p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq];
-    if (pushing && p.push.ll) {
-        // one 8-byte word per pair of values: {value d, value d+1, step}.  Every row must arrive on every rank, so
-        // a sequence that is not a plain one-token decode row (or does not sit at row `seq`) sends zeros and is
-        // reported; the receiver polls each word for the step number.
-        const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
-        float r = 0.f;
-        if (valid && tok == seq) {
-            const int blk_lo = first_block_of(ctx, p.sliding_window);
-            const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
-            r = merge_splits(p, (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits, nsplit, d);
-        } else if (d == 0 && h == 0) {
-            report(p.status, B2A_DEV_BAD_LEN);
-        }
-        const T val = from_f32<T>(r);
-        const uint32_t mine = *reinterpret_cast<const unsigned short*>(&val);
-        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 1);
-        if ((d & 1) == 0) {
-            const size_t at = (static_cast<size_t>(seq) * p.push.row_elems + p.push.col_offset + h * kD + d) >> 1;
-            const uint2 word = make_uint2(mine | (next << 16), static_cast<uint32_t>(epoch));
-            for (int rk = 0; rk < p.push.world; ++rk) reinterpret_cast<uint2*>(p.push.staging[rk][parity])[at] = word;
-        }
-        __syncthreads();
-        if (d == 0) {
-            const int total = static_cast<int>(gridDim.x * gridDim.y);
-            if (atomicAdd(p.push.done_counter, 1) == total - 1) {
-                *p.push.done_counter = 0;
-                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;  // the receiver kernel reads it
-            }
-        }
-        return;
-    }
-    if (valid) {
-        const int blk_lo = first_block_of(ctx, p.sliding_window);
-        const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
-        const T val = from_f32<T>(merge_splits(p, (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits, nsplit, d));
-        if (!pushing) {
-            T* orow = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(tok) * p.Hq + h) * kD;
-            orow[d] = val;
-        } else {
-            const size_t at = static_cast<size_t>(tok) * p.push.row_elems + p.push.col_offset + h * kD + d;
-            for (int r = 0; r < p.push.world; ++r) reinterpret_cast<T*>(p.push.staging[r][parity])[at] = val;
-        }
-    }
-    if (pushing) {
-        __threadfence_system();  // this CTA's peer stores are ordered before its arrival below
-        __syncthreads();
-        if (d == 0) {
-            const int total = static_cast<int>(gridDim.x * gridDim.y);
-            if (atomicAdd(p.push.done_counter, 1) == total - 1) {
-                *p.push.done_counter = 0;  // every CTA has arrived: ready for the next step
-                const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
-                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;
-                __threadfence_system();
-                for (int r = 0; r < p.push.world; ++r) st_release_sys(p.push.flags[r] + p.push.rank, epoch);
-            }
-        }
-    }
-}
-
-// Second half of the exchange: wait until every rank has published the current step, then copy this rank's staging
-// rows to the caller's output.  One CTA per row; the wait is bounded (about a second) and reports
-// B2A_DEV_TIMEOUT instead of hanging when a peer never arrives.
-__global__ void __launch_bounds__(256) peer_wait_copy_kernel(const PeerPush push, void* out, int row_bytes,
-                                                              int32_t* status) {
-    grid_dependency_wait();  // our own merge kernel
-    grid_launch_dependents();
-    const int32_t epoch = *reinterpret_cast<volatile int32_t*>(push.step_counter);  // published by our own merge
-    const int parity = epoch & 1;
-    if (static_cast<int>(threadIdx.x) < push.world) {
-        const int32_t* flag = push.flags[push.rank] + threadIdx.x;
-        const long long t0 = clock64();
-        while (ld_acquire_sys(flag) - epoch < 0) {
-            if (clock64() - t0 > (1LL << 31)) {
-                report(status, B2A_DEV_TIMEOUT);
-                break;
-            }
-        }
-    }
-    __syncthreads();
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(push.staging[push.rank][parity]) +
-                                                      static_cast<size_t>(blockIdx.x) * row_bytes);
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(out) + static_cast<size_t>(blockIdx.x) * row_bytes);
-    for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = src[i];
-}
-
-// Receiver of the low-latency form: one CTA per row polls every 8-byte word of its staging row until it carries this
-// step's number (bounded: B2A_DEV_TIMEOUT after about a second) and writes the two values to the caller's output.
+// Receiver of the low-latency exchange: one CTA per row polls every 8-byte word of its staging row until it carries
+// this step's number (bounded in real time: B2A_DEV_TIMEOUT after push.wait_ns) and writes the two values to the
+// caller's output.
 __global__ void __launch_bounds__(256) peer_ll_copy_kernel(const PeerPush push, uint32_t* out, int pairs_per_row,
                                                             int32_t* status) {
-    grid_dependency_wait();  // our own merge kernel (it publishes the step number)
+    grid_dependency_wait();  // our own decode kernel (its last CTA publishes the step number)
     grid_launch_dependents();
     const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(push.step_counter));
     const uint2* src = reinterpret_cast<const uint2*>(push.staging[push.rank][epoch & 1]) +
                        static_cast<size_t>(blockIdx.x) * pairs_per_row;
     uint32_t* dst = out + static_cast<size_t>(blockIdx.x) * pairs_per_row;
-    const long long t0 = clock64();
+    const long long t0 = global_ns();
     bool gave_up = false;
     for (int i = threadIdx.x; i < pairs_per_row; i += blockDim.x) {
         uint32_t lo, hi;
         for (;;) {
             asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "l"(src + i) : "memory");
             if (hi == epoch || gave_up) break;
-            if (clock64() - t0 > (1LL << 31)) {
+            if (global_ns() - t0 > push.wait_ns) {
                 report(status, B2A_DEV_TIMEOUT);
                 gave_up = true;
             }
@@ -670,16 +712,16 @@ __global__ void __launch_bounds__(256) peer_ll_copy_kernel(const PeerPush push, 
     }
 }
 
-template <typename T, int NT, bool kFused>
+template <typename T, int NT, int kMode>
 int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
-    auto kern = paged_decode_kernel<T, NT, kFused>;
-    static bool configured[64] = {};  // per device; setting the attribute twice is harmless
+    auto kern = paged_decode_kernel<T, NT, kMode>;
+    static std::atomic<bool> configured[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
             return B2A_ERR_CUDA;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     // the split index is the slowest-varying one: every sequence's first chunks (always full) are dispatched before
     // anybody's last chunk (partial or empty), which shortens the tail of a step with uneven contexts
@@ -689,21 +731,21 @@ int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
 
 template <typename T, int NT>
 int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
-    if (p.push.world > 0 && p.push.group_counters != nullptr) return launch_kernel<T, NT, true>(p, num_seqs, stream);
-    const int rc = launch_kernel<T, NT, false>(p, num_seqs, stream);
-    if (rc != B2A_OK) return rc;
-    if (launch_overlapped(paged_decode_merge_kernel<T>, dim3(p.Hq, num_seqs), dim3(kD), 0, stream, p) != cudaSuccess)
-        return B2A_ERR_CUDA;
     if (p.push.world > 0) {
+        if (!p.push.ll) return launch_kernel<T, NT, 2>(p, num_seqs, stream);
+        const int rc = launch_kernel<T, NT, 1>(p, num_seqs, stream);
+        if (rc != B2A_OK) return rc;
         // decode steps carry one token per sequence: row index == sequence index == token index
-        const cudaError_t e = p.push.ll
-            ? launch_overlapped(peer_ll_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push,
-                                static_cast<uint32_t*>(p.out), p.push.row_elems / 2, p.status)
-            : launch_overlapped(peer_wait_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push, p.out,
-                                p.push.row_elems * static_cast<int>(sizeof(T)), p.status);
-        if (e != cudaSuccess) return B2A_ERR_CUDA;
+        return launch_overlapped(peer_ll_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push,
+                                 static_cast<uint32_t*>(p.out), p.push.row_elems / 2, p.status) == cudaSuccess
+                   ? B2A_OK
+                   : B2A_ERR_CUDA;
     }
-    return B2A_OK;
+    const int rc = launch_kernel<T, NT, 0>(p, num_seqs, stream);
+    if (rc != B2A_OK) return rc;
+    return launch_overlapped(paged_decode_merge_kernel<T>, dim3(p.Hq, num_seqs), dim3(kD), 0, stream, p) == cudaSuccess
+               ? B2A_OK
+               : B2A_ERR_CUDA;
 }
 
 }  // namespace
@@ -787,14 +829,16 @@ int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePla
                                         int32_t* status, cudaStream_t stream) {
     if (plan.workspace_bytes > static_cast<size_t>(B2A_BUILTIN_SCRATCH_BYTES)) return B2A_ERR_SCRATCH_LIMIT;
     // `g_decode_scratch` as written in host code is only a handle for the runtime; the address the kernels can
-    // use is looked up once per device, with that device current, and remembered.
-    static void* device_address[64] = {};
+    // use is looked up once per device, with that device current, and remembered (several host threads may get
+    // here at once: they would all store the same value).  The remembered address does not survive a
+    // cudaDeviceReset of that device.
+    static std::atomic<void*> device_address[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
-    void* scratch = (dev >= 0 && dev < 64) ? device_address[dev] : nullptr;
+    void* scratch = (dev >= 0 && dev < 64) ? device_address[dev].load(std::memory_order_acquire) : nullptr;
     if (scratch == nullptr) {
         if (cudaGetSymbolAddress(&scratch, g_decode_scratch) != cudaSuccess || scratch == nullptr) return B2A_ERR_CUDA;
-        if (dev >= 0 && dev < 64) device_address[dev] = scratch;
+        if (dev >= 0 && dev < 64) device_address[dev].store(scratch, std::memory_order_release);
     }
     return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, scratch, status, stream);
 }

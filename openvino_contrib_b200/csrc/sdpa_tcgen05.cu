@@ -5,8 +5,9 @@
 //     staged by TMA;
 //   1 paged, de-quantising in the kernel (PagedAttentionExtension, sequences with two or more new tokens): Q rows
 //     come from the step's [tokens, Hq*128] matrix, K/V from the u8 block pool through the block table - a producer
-//     warpgroup de-quantises 128-token tiles ((code - zp) * scale, f16: queries, keys, values and P are all f16 in
-//     the paged modes) straight into the swizzled shared-memory layout the tensor core reads;
+//     warpgroup de-quantises 128-token tiles ((code - zp) * scale in float32, rounded once to f16: queries, keys,
+//     values and P are all f16 in the paged modes) straight into the swizzled shared-memory layout the tensor core
+//     reads;
 //   2 paged, gathered: paged_gather_kernel has de-quantised the contexts of the step's multi-token sequences once
 //     into an f16 scratch (a row range per sequence), and K/V tiles are staged from there by TMA like dense ones.
 //     Taken when the caller passes the scheduler's bound on those contexts (b2a_paged_desc.prefill_kv_tokens).
@@ -204,35 +205,6 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-// exp2 of two values on the FMA pipe.  The special-function unit delivers 16 exp2 per clock and SM, which is as
-// much time as the tensor core needs for the two matrix products of a tile; moving part of the exponentials to
-// ordinary arithmetic can take the softmax off the critical path.  Measured on B200 with one softmax warp per
-// tile and scheduler partition, the extra issue slots cost as much as the special-function time they save, so
-// the share is 0 by default (B2A_TC_POLY_PER4 selects 0..4 of every 4 element pairs).
-// x = n + f with n = round(x) (magic-number add), 2^f on [-0.5, 0.5] by a degree-3 minimax polynomial (relative
-// error 7.5e-5, far below the 2^-9 rounding of P to bf16), 2^n by adding n to the exponent field.  Inputs are
-// clamped at -126 so that -inf and very negative scores give a harmless 2^-126 instead of a wrapped exponent.
-#ifndef B2A_TC_POLY_PER4
-#define B2A_TC_POLY_PER4 0
-#endif
-constexpr int kPolyPer4 = B2A_TC_POLY_PER4;
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-    float x0, x1;
-    f2_unpack(x2, x0, x1);
-    const uint64_t xc = f2_pack(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-    const uint64_t t2 = f2_add(xc, f2_pack(kMagic, kMagic));
-    const uint64_t n2 = f2_add(t2, f2_pack(-kMagic, -kMagic));
-    const uint64_t f2v = f2_fma(n2, f2_pack(-1.0f, -1.0f), xc);
-    uint64_t r2 = f2_fma(f2v, f2_pack(0.0551716685f, 0.0551716685f), f2_pack(0.2426111251f, 0.2426111251f));
-    r2 = f2_fma(r2, f2v, f2_pack(0.6932609677f, 0.6932609677f));
-    r2 = f2_fma(r2, f2v, f2_pack(0.9999280572f, 0.9999280572f));
-    float r0, r1, t0, t1;
-    f2_unpack(r2, r0, r1);
-    f2_unpack(t2, t0, t1);
-    p0 = __int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
-}
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if constexpr (kBf16) {
@@ -251,38 +223,24 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
     }
 }
 
-// Optional cycle trace of the first CTA (compile with -DB2A_TC_TRACE): clock64() at fixed points of the softmax
-// warp 0 of tile A (slots j*8 + k) and of the MMA thread (slots 1024 + j*8 + k) for the first 64 key steps.
-#ifdef B2A_TC_TRACE
-__device__ long long g_tc_trace[2048];
-#define TC_TRACE(base, j, k)                                                                                       \
-    do {                                                                                                           \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64) g_tc_trace[(base) + (j)*8 + (k)] = clock64(); \
-    } while (0)
-#else
-#define TC_TRACE(base, j, k) \
-    do {                     \
-    } while (0)
-#endif
-
-// De-quantise the 16 codes of one 16-byte piece to f16 and store them as two 16-byte chunks of a swizzled tile row.
-// All in packed f16: 0x64XX is 1024 + XX, so a byte permute makes two halves at once; subtracting 1024 and then the
-// zero-point is exact (both differences are representable), the multiplication by the scale rounds once - the same
-// value as (code - zp) * scale computed in float32 and rounded to f16.  scale and zp arrive as the raw f16 bits the
-// cache stores.
+// De-quantise the 16 codes of one 16-byte piece: (code - zp) * scale in float32, as the decode kernel and the CPU
+// restatement compute it - the difference is exact in float32 (an integer below 256 minus an f16 value), the product
+// rounds once - and then one rounding to f16, the operand format of the tensor core.  0x4B0000XX is 2^23 + XX as a
+// float, so a byte permute and one exact subtraction turn a code into its float value.  scale and zp arrive as the
+// raw f16 bits the cache stores; a zero scale with zero codes (positions past the context) gives exact zeros.
 __device__ __forceinline__ void dequant16_f16(uint4 w, unsigned short scale_bits, unsigned short zp_bits, uint32_t (&outw)[8]) {
     const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-    const __half2 sc2 = __half2half2(__ushort_as_half(scale_bits));
-    const __half2 zp2 = __half2half2(__ushort_as_half(zp_bits));
-    const uint32_t k1024_bits = 0x64006400u;
-    const __half2 k1024 = *reinterpret_cast<const __half2*>(&k1024_bits);
+    const float sc = __half2float(__ushort_as_half(scale_bits));
+    const float zp = __half2float(__ushort_as_half(zp_bits));
+    constexpr float k2p23 = 8388608.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t lo = __byte_perm(words[i], 0x64646464u, 0x4140), hi = __byte_perm(words[i], 0x64646464u, 0x4342);
-        const __half2 x01 = __hmul2(__hsub2(__hsub2(*reinterpret_cast<const __half2*>(&lo), k1024), zp2), sc2);
-        const __half2 x23 = __hmul2(__hsub2(__hsub2(*reinterpret_cast<const __half2*>(&hi), k1024), zp2), sc2);
-        outw[2 * i] = *reinterpret_cast<const uint32_t*>(&x01);
-        outw[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&x23);
+        const float c0 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7650)) - k2p23;
+        const float c1 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7651)) - k2p23;
+        const float c2 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7652)) - k2p23;
+        const float c3 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7653)) - k2p23;
+        outw[2 * i] = pack2<false>((c0 - zp) * sc, (c1 - zp) * sc);
+        outw[2 * i + 1] = pack2<false>((c2 - zp) * sc, (c3 - zp) * sc);
     }
 }
 // ... and store them as two 16-byte chunks of a swizzled shared-memory tile row
@@ -723,7 +681,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 for (int j = 0; ok && j < nmax; ++j) {
                     const int g = g0 + j, stv = g & 1;
                     if (!mbar_wait(BAR(V_FULL + stv), (g >> 1) & 1, abort_flag)) { ok = false; break; }
-                    TC_TRACE(1024, j, 0);
                     bool k_next_ready = false;
 #pragma unroll
                     for (int X = 0; X < 2; ++X) {
@@ -731,7 +688,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         if (ok && j < nkvX) {
                             const int par = (sx[X] + j) & 1;
                             if (!mbar_wait(BAR(P_HALF + X), par, abort_flag)) { ok = false; break; }
-                            TC_TRACE(1024, j, 1 + 2 * X);
                             tc_fence_after();
                             issue_pv(X, stv, j > 0, 0);
                             if (!mbar_wait(BAR(P_READY + X), par, abort_flag)) { ok = false; break; }
@@ -749,7 +705,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             mma_commit(BAR(S_FULL + X));
                             if (j + 2 == nkvX) mma_commit(BAR(Q_EMPTY + X));
                         }
-                        TC_TRACE(1024, j, 2 + 2 * X);
                     }
                     if (!ok) break;
                     mma_commit(BAR(V_EMPTY + stv));
@@ -798,13 +753,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // every lane takes the same decision, so the warp-collective TMEM instructions stay converged
                 ok = __all_sync(0xffffffffu, mbar_wait(BAR(S_FULL + X), (sxb + j) & 1, abort_flag));
                 if (!ok) break;
-                if (threadIdx.x == 0) TC_TRACE(0, j, 0);
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) tmem_ld32(tS + 32 * q, s[q]);
                 tmem_wait_ld();
-                if (threadIdx.x == 0) TC_TRACE(0, j, 1);
                 const int key0 = j * kBN;
                 if (j >= jb) {
                     const int row_pos = row_pos0 + r;  // last key position this row may see (causal)
@@ -828,7 +781,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
                 const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
                 const float m_cand = mx * c;
-                if (threadIdx.x == 0) TC_TRACE(0, j, 2);
                 const bool need = (j == 0) || (m_cand > m_used + kLazyThreshold);
                 const bool need_any = __any_sync(0xffffffffu, need);
                 float alpha = 1.f;
@@ -847,15 +799,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1])), c2, nm2);
-                        float p0, p1;
-                        if ((i & 3) < kPolyPer4) {
-                            exp2_poly2(x2, p0, p1);  // FMA pipe
-                        } else {
-                            float x0, x1;
-                            f2_unpack(x2, x0, x1);
-                            p0 = ex2f(x0);  // MUFU
-                            p1 = ex2f(x1);
-                        }
+                        float x0, x1;
+                        f2_unpack(x2, x0, x1);
+                        const float p0 = ex2f(x0), p1 = ex2f(x1);
                         sum2[i & 3] = f2_add(sum2[i & 3], f2_pack(p0, p1));
                         pk[i] = pack2<kKvBf16>(p0, p1);
                     }
@@ -872,7 +818,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), a0, a1);
                     l += a0 + a1;
                 }
-                if (threadIdx.x == 0) TC_TRACE(0, j, 3);
                 if (need_any && j > 0) {
                     // O_X still holds the old scale; PV_X(j-1) must have landed before it is touched
                     ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (sxb + j - 1) & 1, abort_flag));
@@ -894,7 +839,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(BAR(P_READY + X));
-                if (threadIdx.x == 0) TC_TRACE(0, j, 4);
             }
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(BAR(O_DONE + X), (sxb + nkv - 1) & 1, abort_flag));
             sxb += nkv;
@@ -1005,18 +949,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 }
 
 // Stream-ordered wait for the other ranks of a head-sharded prefill step: returns when every flag shows `step`.
-// Bounded (about a second): a peer that never arrives turns into B2A_DEV_TIMEOUT in the status word.
+// Bounded in wall-clock time: a peer that never arrives turns into B2A_DEV_TIMEOUT in the status word.
 __global__ void __launch_bounds__(32) sdpa_peer_wait_kernel(const int32_t* flags, const int world, const int32_t step,
-                                                            int32_t* status) {
+                                                            const long long wait_ns, int32_t* status) {
     grid_dependency_wait();  // launched while the attention kernel is still running: first let that one finish
     if (static_cast<int>(threadIdx.x) < world) {
         const int32_t* flag = flags + threadIdx.x;
-        const long long t0 = clock64();
+        long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
         for (;;) {
             int32_t v;
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
             if (v - step >= 0) break;
-            if (clock64() - t0 > (1LL << 31)) {
+            long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > wait_ns) {
                 report(status, B2A_DEV_TIMEOUT);
                 break;
             }
@@ -1142,8 +1089,9 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
 }
 
-int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, int32_t* status, cudaStream_t stream) {
-    return launch_overlapped(sdpa_peer_wait_kernel, dim3(1), dim3(32), 0, stream, local_flags, world, step, status) ==
+int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, long long wait_ns, int32_t* status,
+                          cudaStream_t stream) {
+    return launch_overlapped(sdpa_peer_wait_kernel, dim3(1), dim3(32), 0, stream, local_flags, world, step, wait_ns, status) ==
                    cudaSuccess
                ? B2A_OK
                : B2A_ERR_CUDA;
@@ -1262,9 +1210,3 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
 }
 
 }  // namespace b2a
-
-#ifdef B2A_TC_TRACE
-extern "C" int b2a_debug_tc_trace(long long* host_out, int n) {
-    return cudaMemcpyFromSymbol(host_out, b2a::g_tc_trace, sizeof(long long) * static_cast<size_t>(n)) == cudaSuccess ? 0 : 6;
-}
-#endif

@@ -1,12 +1,11 @@
-// Head-sharded decode across the GPUs of one node without a collective library on the data path.
+// Head-sharded attention across the GPUs of one node without a collective library on the data path.
 //
-// A shard group is one device allocation per rank, [staging 0 | staging 1 | flags | counters], exported with CUDA
-// IPC and mapped by every peer.  b2a_paged_attention_sharded runs the split-K decode on this rank's KV heads; its
-// merge kernel stores the rank's output columns into every rank's staging buffer over NVLink and publishes the step
-// in every rank's flags; peer_wait_copy_kernel then waits (bounded) for all ranks and copies the full-width rows to
-// the caller's output (see PeerPush in launch.cuh, kernels in paged_decode.cu).
-// b2a_sdpa_forward_sharded does the same for prefill: the tensor-core kernel's epilogue stores each output tile into
-// every rank's buffer (TcPeerOut in launch.cuh), and the result is read in place.
+// A shard group is one device allocation per rank, [staging 0 | staging 1 | flags | counters | tickets], which every
+// peer maps - through CUDA IPC when the ranks are processes, by pointer when one process drives several ranks.
+// b2a_paged_attention_sharded runs the split-K decode on this rank's KV heads; the decode kernel itself merges the
+// splits and stores the rank's output columns into every rank's memory over NVLink (PeerPush in launch.cuh, kernels
+// in paged_decode.cu).  b2a_sdpa_forward_sharded does the same for prefill: the tensor-core kernel's epilogue stores
+// each output tile into every rank's buffer (TcPeerOut in launch.cuh), and the result is read in place.
 // The reference never spans devices (one independent plugin configuration per device id,
 // modules/nvidia_plugin/src/cuda_plugin.cpp:25-32), so nothing here has a counterpart there.
 #include <cmath>
@@ -29,7 +28,9 @@ struct b2a_shard_group {
     int rank = 0, world = 1, device = 0;
     size_t staging_bytes = 0;  // one staging buffer
     char* base[b2a::kMaxShardWorld] = {};  // [rank]: that rank's allocation as mapped in this process
+    bool ipc_mapped[b2a::kMaxShardWorld] = {};  // base[r] came from cudaIpcOpenMemHandle (closed on destroy)
     bool connected = false;
+    long long wait_ns = 1000000000LL;  // bound of every device-side wait on another rank
     int mode = kModeUnset;       // a group serves one kind of step: the two kinds alternate the staging halves differently
     int32_t prefill_step = 0;    // host-side count of prefill steps
     size_t total_bytes() const { return 2 * staging_bytes + kFlagsBytes + kCountersBytes + kGroupCounters * sizeof(int32_t); }
@@ -76,8 +77,43 @@ int b2a_shard_group_connect(b2a_shard_group* g, const unsigned char* handles) {
         void* p = nullptr;
         if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return B2A_ERR_CUDA;
         g->base[r] = static_cast<char*>(p);
+        g->ipc_mapped[r] = true;
     }
     g->connected = true;
+    return B2A_OK;
+}
+
+int b2a_shard_group_connect_pointers(b2a_shard_group* g, void* const* bases) {
+    if (g == nullptr || bases == nullptr) return B2A_ERR_NULL;
+    for (int r = 0; r < g->world; ++r) {
+        if (r == g->rank) continue;
+        if (bases[r] == nullptr) return B2A_ERR_NULL;
+        if (g->base[r] != nullptr && g->base[r] != bases[r]) return B2A_ERR_UNSUPPORTED;  // already connected elsewhere
+        g->base[r] = static_cast<char*>(bases[r]);
+    }
+    g->connected = true;
+    return B2A_OK;
+}
+
+int b2a_shard_group_set_wait_ms(b2a_shard_group* g, int milliseconds) {
+    if (g == nullptr) return B2A_ERR_NULL;
+    if (milliseconds <= 0) return B2A_ERR_DIM;
+    g->wait_ns = static_cast<long long>(milliseconds) * 1000000LL;
+    return B2A_OK;
+}
+
+int b2a_shard_group_reset(b2a_shard_group* g) {
+    if (g == nullptr) return B2A_ERR_NULL;
+    int prev = 0;
+    if (cudaGetDevice(&prev) != cudaSuccess || cudaSetDevice(g->device) != cudaSuccess) return B2A_ERR_CUDA;
+    // everything this rank enqueued has finished (with or without a timeout) before its memory is wiped
+    const bool ok = cudaDeviceSynchronize() == cudaSuccess &&
+                    cudaMemset(g->base[g->rank], 0, g->total_bytes()) == cudaSuccess &&
+                    cudaDeviceSynchronize() == cudaSuccess;
+    cudaSetDevice(prev);
+    if (!ok) return B2A_ERR_CUDA;
+    g->mode = kModeUnset;
+    g->prefill_step = 0;
     return B2A_OK;
 }
 
@@ -91,7 +127,8 @@ void b2a_shard_group_destroy(b2a_shard_group* g) {
     if (g == nullptr) return;
     for (int r = 0; r < g->world; ++r) {
         if (g->base[r] == nullptr) continue;
-        if (r == g->rank) cudaFree(g->base[r]); else cudaIpcCloseMemHandle(g->base[r]);
+        if (r == g->rank) cudaFree(g->base[r]);
+        else if (g->ipc_mapped[r]) cudaIpcCloseMemHandle(g->base[r]);
     }
     delete g;
 }
@@ -104,21 +141,23 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
     using namespace b2a;
     if (g == nullptr || local_desc == nullptr) return B2A_ERR_NULL;
     if (!g->connected) return B2A_ERR_UNSUPPORTED;
-    b2a_paged_desc d = *local_desc;
-    if (d.scale == 0.f && d.D > 0) d.scale = 1.0f / sqrtf(static_cast<float>(d.D));
+    b2a_paged_desc d;
+    const int rc = resolve_paged_desc(local_desc, d);  // the same validation as the single-GPU entry points
+    if (rc != B2A_OK) return rc;
     if (d.num_tokens == 0 || d.num_seqs == 0) return B2A_OK;
     if (query == nullptr || k_cache == nullptr || v_cache == nullptr || out_full == nullptr || past_lens == nullptr ||
         subsequence_begins == nullptr || block_indices == nullptr || block_indices_begins == nullptr)
         return B2A_ERR_NULL;
-    if (d.Hq <= 0 || d.Hkv <= 0 || d.Hq % d.Hkv != 0 || d.num_seqs > 65535 || d.max_context_len <= 0) return B2A_ERR_DIM;
+    if (d.max_context_len <= 0) return B2A_ERR_DIM;
     if (!paged_decode_supported(d)) return B2A_ERR_UNSUPPORTED;  // decode steps only
     // out_full == the group's own buffer (b2a_shard_group_output): results are produced in place by one kernel
     const bool in_place = out_full == static_cast<void*>(g->base[g->rank]);
     const int want = in_place ? kModeDecodeInPlace : kModeDecode;
     if (g->mode != kModeUnset && g->mode != want) return B2A_ERR_UNSUPPORTED;
-    if (in_place && static_cast<size_t>(d.num_seqs) * d.Hkv > kGroupCounters) return B2A_ERR_CAPACITY;
+    if (static_cast<size_t>(d.num_seqs) * d.Hkv > kGroupCounters) return B2A_ERR_CAPACITY;
     const size_t row_bytes = static_cast<size_t>(d.Hq) * g->world * d.D * 2;
-    if (static_cast<size_t>(d.num_tokens) * row_bytes > g->staging_bytes) return B2A_ERR_CAPACITY;
+    // in place: the rows themselves; caller's buffer: every pair of values travels with the step number (8 bytes)
+    if ((in_place ? 1 : 2) * static_cast<size_t>(d.num_tokens) * row_bytes > g->staging_bytes) return B2A_ERR_CAPACITY;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (!al(k_cache) || !al(v_cache) || !al(query) || !al(out_full) || !al(workspace)) return B2A_ERR_ALIGN;
     const int sms = device_sm_count();
@@ -137,12 +176,13 @@ int b2a_paged_attention_sharded(b2a_shard_group* g, const b2a_paged_desc* local_
     push.rank = g->rank;
     push.world = g->world;
     push.row_elems = d.Hq * g->world * d.D;
-    push.ll = !in_place && 2 * static_cast<size_t>(d.num_tokens) * row_bytes <= g->staging_bytes ? 1 : 0;
+    push.ll = in_place ? 0 : 1;
     push.col_offset = g->rank * d.Hq * d.D;
+    push.wait_ns = g->wait_ns;
+    push.group_counters = reinterpret_cast<int32_t*>(counters + kCountersBytes);
     const PagedTables t{past_lens, subsequence_begins, block_indices, block_indices_begins,
                         d.num_seqs, d.num_tokens, d.num_blocks_total, d.block_size};
     if (in_place) {
-        push.group_counters = reinterpret_cast<int32_t*>(counters + kCountersBytes);
         for (int r = 0; r < g->world; ++r)
             push.started[r] = reinterpret_cast<int32_t*>(g->base[r] + 2 * g->staging_bytes) + kStartedFlagOffset;
     }
@@ -155,7 +195,7 @@ int b2a_sdpa_forward_sharded(b2a_shard_group* g, const b2a_sdpa_desc* local_desc
                              const void* v, void** out_full, int32_t* status, b2a_stream_t stream) {
     using namespace b2a;
     if (g == nullptr || local_desc == nullptr || out_full == nullptr) return B2A_ERR_NULL;
-    if (!g->connected || g->mode == kModeDecode) return B2A_ERR_UNSUPPORTED;
+    if (!g->connected || (g->mode != kModeUnset && g->mode != kModePrefill)) return B2A_ERR_UNSUPPORTED;
     b2a_sdpa_desc d = *local_desc;
     if (d.dtype != B2A_F16 && d.dtype != B2A_BF16) return B2A_ERR_UNSUPPORTED;
     if (d.B <= 0 || d.Hq <= 0 || d.Hkv <= 0 || d.Sq <= 0 || d.Skv <= 0 || d.Hq % d.Hkv != 0) return B2A_ERR_DIM;
@@ -193,12 +233,13 @@ int b2a_sdpa_forward_sharded(b2a_shard_group* g, const b2a_sdpa_desc* local_desc
     po.hq_total = hq_total;
     po.head_offset = g->rank * d.Hq;
     po.step = step;
+    po.wait_ns = g->wait_ns;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     int rc = sdpa_tc_launch(d, qs, ks, vs, os, q, k, v, mine, status, s, &po);
     if (rc != B2A_OK) return rc;
     g->mode = kModePrefill;
     g->prefill_step = step;
-    rc = sdpa_peer_wait_launch(po.flags[g->rank], g->world, step, status, s);
+    rc = sdpa_peer_wait_launch(po.flags[g->rank], g->world, step, g->wait_ns, status, s);
     if (rc != B2A_OK) return rc;
     *out_full = mine;
     return B2A_OK;

@@ -104,9 +104,9 @@ class ShardGroup:
     """Python face of ``b2a_shard_group``: staging buffers on every rank, mapped into every process with CUDA IPC.
 
     The 64-byte handles travel through ``torch.distributed`` (any backend) at set-up; after that a decode step
-    involves no collective call: ``paged_attention`` enqueues the split-K decode of the local heads, a merge
-    kernel that stores this rank's output columns on every rank and a kernel that waits for all ranks and fills
-    ``out_full``.
+    involves no collective call: ``paged_attention`` enqueues the split-K decode of the local heads - whose last CTA
+    per (sequence, KV head) merges the splits and stores this rank's output columns on every rank - and a small
+    kernel that polls the arriving words and fills ``out_full``.
     """
 
     def __init__(self, shard: HeadShard, staging_bytes: int, group=None):
@@ -133,6 +133,23 @@ class ShardGroup:
             self._lib.b2a_shard_group_destroy(self._h)
             self._h = None
 
+    def set_wait_ms(self, milliseconds: int) -> None:
+        """Bound of every device-side wait on another rank (default one second); when it runs out the step's kernels
+        return and the status word carries ``DEV_TIMEOUT``."""
+        from . import _lib
+        _lib.check(self._lib.b2a_shard_group_set_wait_ms(self._h, int(milliseconds)), "b2a_shard_group_set_wait_ms")
+
+    def reset(self, group=None) -> None:
+        """Back to the state of a fresh group, on all ranks together (after a timeout the ranks' step counters no
+        longer agree).  Call it on every rank, between steps."""
+        from . import _lib
+        torch.cuda.synchronize()
+        if self.shard.world > 1:
+            dist.barrier(group=group)   # every rank's device is idle: nobody stores into a peer any more
+        _lib.check(self._lib.b2a_shard_group_reset(self._h), "b2a_shard_group_reset")
+        if self.shard.world > 1:
+            dist.barrier(group=group)
+
     def __del__(self):
         self.close()
 
@@ -144,7 +161,8 @@ class ShardGroup:
 
         With ``out_full=None`` the step is a single kernel that produces the rows in the group's own buffer on every
         rank; the returned tensor is a view of that buffer (valid until the next step on this group).  With a
-        caller's ``out_full`` the rows are exchanged through staging buffers and copied there.
+        caller's ``out_full`` the rows travel as 8-byte {two values, step number} words through staging buffers of
+        twice the output size and a second kernel copies them there.
         """
         from . import _lib
         from .ops import _paged_desc, _ptr, _stream_ptr

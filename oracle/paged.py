@@ -83,11 +83,11 @@ def paged_attention_ref(query, k_cache, v_cache, past_lens, subsequence_begins, 
         ctx = past + qlen
         kk = gather_sequence(k_cache, s, ctx, block_indices, block_indices_begins, d, block_size)
         vv = gather_sequence(v_cache, s, ctx, block_indices, block_indices_begins, d, block_size)
-        kk = np.repeat(kk, g, axis=0)  # [Hq, ctx, D]
-        vv = np.repeat(vv, g, axis=0)
-        qs = np.transpose(q[b:e], (1, 0, 2))  # [Hq, qlen, D]
-        sc = np.matmul(qs, np.swapaxes(kk, -1, -2)) * np.float32(scale)  # [Hq, qlen, ctx]
-        pos_q = past + np.arange(qlen)[:, None]
+        # the g query heads of a KV head share its keys and values (grouped-query attention): they are stacked
+        # along the row axis instead of repeating K and V g times
+        qs = np.transpose(q[b:e], (1, 0, 2)).reshape(hkv, g * qlen, d)  # [Hkv, g*qlen, D], row = head-in-group * qlen + i
+        sc = np.matmul(qs, np.swapaxes(kk, -1, -2)) * np.float32(scale)  # [Hkv, g*qlen, ctx]
+        pos_q = np.tile(past + np.arange(qlen), g)[:, None]
         pos_k = np.arange(ctx)[None, :]
         keep = pos_k <= pos_q
         if sliding_window and sliding_window > 0:
@@ -95,7 +95,7 @@ def paged_attention_ref(query, k_cache, v_cache, past_lens, subsequence_begins, 
         sc = np.where(keep[None], sc, np.float32(-np.inf))
         mx = sc.max(axis=-1, keepdims=True)
         p = np.exp(sc - mx)
-        o = np.matmul(p / p.sum(axis=-1, keepdims=True), vv)  # [Hq, qlen, D]
+        o = np.matmul(p / p.sum(axis=-1, keepdims=True), vv).reshape(hq, qlen, d)  # [Hq, qlen, D]
         out[b:e] = np.transpose(o, (1, 0, 2))
     return out.reshape(-1, hq * d)
 

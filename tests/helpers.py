@@ -26,7 +26,7 @@ class PagedWorkload:
     """A seeded paged-attention problem: pools filled by the ORACLE's quantiser, tables, queries."""
 
     def __init__(self, context_lens, q_lens, hq, hkv, d, block_size=16, seed=0, table_seed=3, spare_blocks=2,
-                 q_scale=1.0, value_fn=None):
+                 q_scale=1.0, value_fn=None, key_fn=None):
         self.hq, self.hkv, self.d, self.bs = hq, hkv, d, block_size
         self.ctx = np.asarray(context_lens, dtype=np.int64)      # context INCLUDING this step's tokens
         self.qlen = np.asarray(q_lens, dtype=np.int32)
@@ -34,7 +34,8 @@ class PagedWorkload:
         assert (self.past >= 0).all()
         rng = np.random.default_rng(seed)
         self.bi, self.bb, self.nb = opaged.build_block_tables(self.ctx, block_size, table_seed, spare_blocks)
-        self.rows_k = [rng.standard_normal((int(c), hkv, d), dtype=np.float32) for c in self.ctx]
+        self.rows_k = [(key_fn(s, int(c)) if key_fn else rng.standard_normal((int(c), hkv, d), dtype=np.float32))
+                       for s, c in enumerate(self.ctx)]
         self.rows_v = [(value_fn(s, int(c)) if value_fn else rng.standard_normal((int(c), hkv, d), dtype=np.float32))
                        for s, c in enumerate(self.ctx)]
         self.sb = np.zeros(len(self.ctx) + 1, dtype=np.int32)

@@ -5,7 +5,8 @@ the NCCL all-gather of the same shards.  Launch:
         tests/multi_gpu/sharded_decode.py
 
 Every rank builds the same full problem from one seed, keeps its KV heads, runs three steps (the exchange
-alternates two staging buffers, so odd and even steps are both exercised) and checks the full-width output.
+alternates two staging buffers, so odd and even steps are both exercised) and checks the full-width output
+against the oracle, against the NCCL gather of the plain kernel and between the ranks.
 NVLS is not needed and left off.
 """
 import os
@@ -41,12 +42,11 @@ def main():
     ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, shard.hq_local, n, n, max(ctx), 1)),
                      dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    # staging of exactly the output size: rows pushed as they are, flags, wait-and-copy; twice the size: the
-    # low-latency exchange (value pairs travel with the step number, the receiver polls the words)
-    for mult in (1, 2):
-      group = ShardGroup(shard, staging_bytes=mult * n * hq * d * 2)
-      for step in range(3):
-        q_full = torch.from_numpy(w.query * (1.0 + 0.25 * step + 0.5 * mult)).to(torch.float16)
+    # a caller's output buffer: the decode kernel's last CTA per (sequence, KV head) merges and sends the value pairs
+    # with the step number, the receiving kernel polls the words (staging of twice the output size)
+    group = ShardGroup(shard, staging_bytes=2 * n * hq * d * 2)
+    for step in range(3):
+        q_full = torch.from_numpy(w.query * (1.0 + 0.25 * step)).to(torch.float16)
         ref = w.reference(q_full.float().numpy())
         q_local = shard.take_q_rows(q_full, d).contiguous().cuda()
         out = torch.zeros(n, hq * d, dtype=torch.float16, device="cuda")
@@ -55,13 +55,28 @@ def main():
         torch.cuda.synchronize()
         assert int(status.item()) == 0, f"rank {rank} step {step}: status {int(status.item())}"
         assert_close(out, ref, torch.float16, f"rank {rank} step {step}")
-        # and bit-identical to the NCCL path over the same shards
+        # and bit-identical to the NCCL all-gather of the plain kernel's shards (the in-kernel merge performs the
+        # merge kernel's arithmetic operation for operation)
         o_local = b2a.paged_attention(q_local, cache, *tables, hq=shard.hq_local, max_context_len=max(ctx),
                                       max_q_len=1, workspace=ws)
         o_nccl = gather_heads_rows(o_local, shard, d)
         assert torch.equal(o_nccl, out), f"rank {rank} step {step}: differs from the NCCL gather"
-      dist.barrier()
-      group.close()
+        # every rank holds the same bits
+        mine = out.clone()
+        dist.broadcast(mine, src=0)
+        assert torch.equal(mine, out), f"rank {rank} step {step}: ranks disagree"
+    # a sequence with inconsistent tables arrives as zeros on every rank and is reported; no rank waits for ever
+    bad = tables[0].clone()
+    bad[1] = -3
+    out = torch.full((n, hq * d), 3.0, dtype=torch.float16, device="cuda")
+    group.paged_attention(q_local, cache, bad, *tables[1:], max_context_len=max(ctx), out_full=out, workspace=ws,
+                          status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4 and float(out[1].float().abs().max()) == 0.0, f"rank {rank}: bad row"
+    assert_close(out[2:], ref[2:], torch.float16, f"rank {rank}: rows next to the bad one")
+    status.zero_()
+    dist.barrier()
+    group.close()
     # the one-kernel step: results produced in place in the group's own buffer on every rank
     group2 = ShardGroup(shard, staging_bytes=n * hq * d * 2)
     for step in range(3):

@@ -51,6 +51,42 @@ def test_two_rank_head_sharding(tmp_path):
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
 
 
+def _absent_worker(rank, world, port, out_dir):
+    """Rank 1 never posts its shard: rank 0's all-gather must end with an error inside the process-group timeout
+    instead of waiting for ever - the host-side half of failure detection (the device-side half is the bounded
+    wait of the peer-store exchange)."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    from openvino_contrib_b200.sharding import HeadShard, gather_heads_rows
+    shard = HeadShard(rank, world, 8, 4)
+    mine = torch.full((3, shard.hq_local * 16), float(rank))
+    if rank == 0:
+        t0 = time.time()
+        try:
+            gather_heads_rows(mine, shard, 16)
+            verdict = "completed"          # must not happen: the other rank never joined
+        except Exception as e:             # gloo reports the timeout as a RuntimeError / DistBackendError
+            verdict = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
+        open(os.path.join(out_dir, "verdict"), "w").write(verdict)
+    else:
+        time.sleep(6.0)                    # stays alive, between steps, and simply never calls the collective
+    # no destroy_process_group: its own barrier would wait for the rank that left the protocol
+
+
+def test_absent_rank_ends_the_gather_with_an_error(tmp_path):
+    world = 2
+    ctx = mp.spawn(_absent_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=False)
+    ctx.join(timeout=60)
+    for p in ctx.processes:
+        if p.is_alive():
+            p.terminate()
+    verdict = (tmp_path / "verdict").read_text()
+    assert verdict.startswith("error after"), verdict
+    assert float(verdict.split()[2][:-2]) < 30.0
+
+
 def test_shard_rejects_uneven_split():
     import pytest
     from openvino_contrib_b200.sharding import HeadShard

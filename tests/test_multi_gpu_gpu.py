@@ -8,13 +8,21 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port() -> str:
+    """A port nobody listens on right now (two jobs on one shared host must not meet on a fixed one)."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return str(s.getsockname()[1])
+
+
 @pytest.mark.gpu
 def test_sharded_decode_two_gpus():
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", os.path.join(ROOT, "tests", "multi_gpu", "sharded_decode.py")]
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "multi_gpu", "sharded_decode.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
     print(r.stdout[-3000:], r.stderr[-3000:])
     assert r.returncode == 0 and "sharded decode ok on 2 GPUs" in r.stdout
@@ -26,7 +34,7 @@ def test_sharded_prefill_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29534", os.path.join(ROOT, "tests", "multi_gpu", "sharded_prefill.py")]
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "multi_gpu", "sharded_prefill.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
     print(r.stdout[-3000:], r.stderr[-3000:])
     assert r.returncode == 0 and "sharded prefill ok on 2 GPUs" in r.stdout

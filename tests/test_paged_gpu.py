@@ -236,10 +236,9 @@ def test_config3_shape_against_oracle(b2a):
     assert_close(out, w.reference(q.float().numpy()), torch.float16)
 
 
-def test_config5_shape_properties(b2a):
-    # batch 16 x context 32768, Hq 64 / Hkv 8: too large for the numpy oracle in seconds, so check properties:
-    # (1) constant V per (sequence, head) is reproduced; (2) a window equal to the context changes nothing;
-    # (3) sequence 0 alone (oracle-checked) equals row 0 of the batch.
+def _config5_problem(b2a, value_fn):
+    """Batch 16 x context 32768, Hq 64 / Hkv 8, pools filled through the library's own store path in slices
+    (exercises kv_store at scale); keys N(0,1), values from ``value_fn(first position, positions per sequence)``."""
     hq, hkv, d, bs, n, ctxlen = 64, 8, 128, 16, 16, 32768
     nblk = ctxlen // bs
     gen = torch.Generator(device="cuda").manual_seed(5)
@@ -248,26 +247,58 @@ def test_config5_shape_properties(b2a):
     bi = perm.cuda()
     bb = (torch.arange(n + 1, dtype=torch.int32) * nblk).cuda()
     sb = torch.arange(n + 1, dtype=torch.int32).cuda()
-    # fill through the library's own store path in slices (exercises kv_store at scale)
     step = 4096
     for p0 in range(0, ctxlen, step):
         key = torch.randn(n * step, hkv * d, generator=gen, device="cuda", dtype=torch.float16)
-        hv = torch.arange(hkv, device="cuda", dtype=torch.float16).repeat_interleave(d)[None] * 0.125
-        sv = torch.arange(n, device="cuda", dtype=torch.float16).repeat_interleave(step)[:, None] * 0.0625
-        val = (hv + sv - 0.5).contiguous()
+        val = value_fn(gen, n, step, hkv, d)
         past = torch.full((n,), p0, dtype=torch.int32, device="cuda")
         sbs = (torch.arange(n + 1, dtype=torch.int32) * step).cuda()
         b2a.paged_kv_store(key, val, cache, past, sbs, bi, bb)
     past = torch.full((n,), ctxlen - 1, dtype=torch.int32, device="cuda")
     q = torch.randn(n, hq * d, generator=gen, device="cuda", dtype=torch.float16)
+    return cache, q, past, sb, bi, bb
+
+
+def test_config5_shape_against_oracle(b2a):
+    # The long-context batch at full size with random keys AND values.  Two complete sequences (32768 tokens x 64
+    # heads each) are checked against the oracle: their blocks are copied out of the pool into a compact one-sequence
+    # pool with an identity block table, which the oracle then walks exactly as it would the large one.
+    hq, hkv, d, bs, n, ctxlen = 64, 8, 128, 16, 16, 32768
+    nblk = ctxlen // bs
+    rand_v = lambda gen, n_, step, hkv_, d_: torch.randn(n_ * step, hkv_ * d_, generator=gen, device="cuda",
+                                                          dtype=torch.float16)
+    cache, q, past, sb, bi, bb = _config5_problem(b2a, rand_v)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1, status=status)
+    assert int(status.item()) == 0
+    one = lambda a: np.asarray(a, dtype=np.int32)
+    for s in (0, 11):
+        phys = bi[s * nblk:(s + 1) * nblk].long()
+        k_small, v_small = cache.k[phys].cpu().numpy(), cache.v[phys].cpu().numpy()
+        ref = opaged.paged_attention_ref(q[s:s + 1].float().cpu().numpy(), k_small, v_small, one([ctxlen - 1]),
+                                         one([0, 1]), np.arange(nblk, dtype=np.int32), one([0, nblk]), hq, hkv, d, bs)
+        assert_close(out[s:s + 1], ref, torch.float16, f"sequence {s}")
+    # a sliding window equal to the context changes nothing
+    out_w = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1,
+                                sliding_window=ctxlen)
+    assert torch.equal(out, out_w)
+
+
+def test_config5_shape_constant_values(b2a):
+    # the same shape with V constant per (sequence, head): every output row must reproduce its constant, whatever
+    # the scores are - a check of all 16 x 64 rows that needs no oracle
+    hq, hkv, d, n, ctxlen = 64, 8, 128, 16, 32768
+
+    def const_v(gen, n_, step, hkv_, d_):
+        hv = torch.arange(hkv_, device="cuda", dtype=torch.float16).repeat_interleave(d_)[None] * 0.125
+        sv = torch.arange(n_, device="cuda", dtype=torch.float16).repeat_interleave(step)[:, None] * 0.0625
+        return (hv + sv - 0.5).contiguous()
+    cache, q, past, sb, bi, bb = _config5_problem(b2a, const_v)
     out = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1)
     o = out.float().reshape(n, hkv, hq // hkv, d)
     expect = (torch.arange(hkv, device="cuda").float()[None, :, None, None] * 0.125
               + torch.arange(n, device="cuda").float()[:, None, None, None] * 0.0625 - 0.5)
     assert torch.allclose(o, expect.expand_as(o), atol=2e-3)
-    out_w = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq, max_context_len=ctxlen, max_q_len=1,
-                                sliding_window=ctxlen)
-    assert torch.equal(out, out_w)
 
 
 # ---------------------------------------------------------------- multi-token rows on the tensor-core kernel
@@ -339,6 +370,35 @@ def test_mixed_step_graph_replay_with_new_lengths(b2a):
     ref = opaged.paged_attention_ref(q.float().cpu().numpy(), w.k_cache, w.v_cache, new_past, new_sb, w.bi, w.bb,
                                      hq, hkv, d, 16)
     assert_close(out, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_rows_far_from_zero(b2a, dtype):
+    # Rows that sit far from zero have zero-points of thousands (mean 8, deviation 0.1: zp around -2500; the
+    # mirrored rows: +2700), where a de-quantiser that subtracts in f16 would be off by whole code steps.  A mixed
+    # step (two prefills, a continuation, decode rows) through both prefill variants and the decode kernel.
+    past = np.array([0, 300, 1000, 5, 0], np.int32)
+    qlen = np.array([260, 130, 1, 1, 128], np.int32)
+    hq, hkv, d = 32, 8, 128
+    rows = lambda sign: (lambda s, c: (sign * 8.0 + 0.1 * np.random.default_rng(1000 + s).standard_normal(
+        (c, hkv, d))).astype(np.float32))
+    w = PagedWorkload(past + qlen, qlen, hq, hkv, d, seed=33, key_fn=rows(1.0), value_fn=rows(-1.0), q_scale=0.25)
+    zp = oquant.chunk_views(w.k_cache, 16, d)[2]
+    assert np.abs(zp[w.bi[0]].astype(np.float32)).max() > 2048  # the case is what it claims to be
+    q = _round(w.query, dtype)
+    ref = w.reference(q.float().numpy())
+    ctx = past + qlen
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kw = dict(hq=hq, max_context_len=int(ctx.max()), max_q_len=int(qlen.max()), status=status)
+    out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), **kw)
+    hint_rb = int(sum((int(x) + 127) // 128 for x in qlen if x >= 2))
+    hint_kv = int(sum((int(c) + 127) // 128 * 128 for c, x in zip(ctx, qlen) if x >= 2))
+    out2 = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), prefill_row_blocks=hint_rb,
+                               prefill_kv_tokens=hint_kv, **kw)
+    assert int(status.item()) == 0
+    assert_close(out, ref, dtype, "prefill contexts de-quantised in the kernel")
+    assert_close(out2, ref, dtype, "prefill contexts de-quantised once")
+    assert torch.equal(out, out2)
 
 
 def test_config4_mixed_step(b2a):

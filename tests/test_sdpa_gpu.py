@@ -179,6 +179,23 @@ def test_config2_full_size_properties(b2a):
     assert float((ones.float() - 1.0).abs().max()) <= 2.0 ** -8  # P is rounded to bf16 before the PV product
 
 
+def test_config2_full_size_planes_against_oracle(b2a):
+    # the same full-size problem: four complete (batch, head) planes - all 4096 rows over all their keys, one per
+    # batch entry, over four different KV heads and positions in the group - against the oracle
+    B, hq, hkv, S, D = 4, 32, 8, 4096, 128
+    gen = torch.Generator().manual_seed(1)
+    q = (torch.randn(B, hq, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), causal=True, status=status).cpu()
+    assert int(status.item()) == 0
+    for b, h in ((0, 0), (1, 13), (2, 22), (3, 31)):
+        hk = h // (hq // hkv)
+        ref = osdpa.sdpa_ref(q[b:b + 1, h:h + 1], k[b:b + 1, hk:hk + 1], v[b:b + 1, hk:hk + 1], causal=True)
+        assert_close(out[b:b + 1, h:h + 1], ref, torch.bfloat16, f"plane ({b},{h})")
+
+
 def test_host_pipeline_matches_device_call(b2a):
     # host tensors in, host tensor out, batch entries pipelined on three streams: same bits as the plain call
     B, hq, hkv, S, D = 3, 8, 2, 384, 128
