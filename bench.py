@@ -1,13 +1,15 @@
 #!/usr/bin/env python
 """Benchmark of the attention path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b2a|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b2a|reference] [--only NAME]
 
 Prints ONE JSON line (rank 0).  The headline workload is the Llama-3-8B-shaped causal bf16 prefill SDPA
 (B=4, Hq=32, Hkv=8, S=4096, D=128); the same line carries the paged-decode half of the metric (KV GB/s on the
 64-sequence u8-cache decode and on the 16 x 32768 long-context decode) under "decode".  With N > 1 the heads are
-sharded over the ranks (Hkv/N KV heads each, no K/V crosses NVLink) and the per-head outputs are all-gathered
-with NCCL inside the timed step.
+sharded over the ranks (Hkv/N KV heads each, no K/V crosses NVLink) and the per-head outputs are exchanged inside
+the timed step by the kernels that produce them (peer stores over NVLink).  Every workload checks its own result
+after the timed region - the device status word, and at N > 1 the full-width output against the single-GPU kernels
+on each rank's shard gathered with NCCL - and reports it as "verified"; a failed check makes the exit code 1.
 
 `--impl reference` times the CPU restatement of the reference's dense attention (oracle port, all host threads)
 on a bounded slice of the same workload.
@@ -195,7 +197,7 @@ def timed(fn, steps, warmup, world, stream=None):
     return ms / steps, t0, t1
 
 
-def timed_replay(fn, steps, warmup, world):
+def timed_replay(fn, steps, warmup, world, multiple_of=1):
     """Like timed(), but the steps are captured into a CUDA graph and the timed region replays it - how the plugin's
     graph runner executes a captured topology (no host-side launch cost in the timed region).  A graph holds up to
     25 consecutive steps (a decoder's graph holds one such step per layer), and K steps are K/25 replays.  Falls
@@ -203,7 +205,10 @@ def timed_replay(fn, steps, warmup, world):
     for _ in range(max(1, warmup)):
         fn()
     torch.cuda.synchronize()
-    per_graph = max(g for g in range(1, 26) if steps % g == 0)
+    # steps per graph: a divisor of the step count, a multiple of `multiple_of` (steps that walk through several
+    # pools come back to the first pool at the start of every replay)
+    steps = -(-steps // multiple_of) * multiple_of
+    per_graph = max(g for g in range(multiple_of, max(26, multiple_of + 1), multiple_of) if steps % g == 0)
     try:
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
@@ -219,7 +224,7 @@ def timed_replay(fn, steps, warmup, world):
         ms, t0, t1 = timed(fn, steps, 1, world)
         return ms, "plain calls (graph capture failed)"
     ms, _, _ = timed(graph.replay, steps // per_graph, 2, world)
-    return ms / per_graph, f"graph replay, {per_graph} steps per graph"
+    return ms / per_graph, f"graph replay, {per_graph} steps per graph, {steps} steps timed"
 
 
 def bench_prefill(args, rank, world, local):
@@ -381,7 +386,12 @@ def build_decode_problem(n_seqs, ctx_lens, Hq, Hkv, D, seed, device="cuda"):
 
 
 def bench_decode(name, steps, warmup, rank, world):
-    """Paged decode, u8 KV: 'cfg3' = 64 sequences with contexts U[512, 8192]; 'cfg5' = 16 x 32768, Hq 64."""
+    """Paged decode, u8 KV: 'cfg3' = 64 sequences with contexts U[512, 8192]; 'cfg5' = 16 x 32768, Hq 64.
+
+    A head shard of the cache can be small enough to sit in the 126 MB L2, which a serving step never enjoys (the
+    cache of a decoder is read once per layer and step).  So when one rank's share is below four times the L2
+    size, several pools with different contents and block tables are built and the steps walk through them in turn:
+    every step finds its pool evicted."""
     import torch.distributed as dist
     import openvino_contrib_b200 as b2a
     if name == "cfg3":
@@ -392,50 +402,74 @@ def bench_decode(name, steps, warmup, rank, world):
         ctx = np.full(n, 32768)
     D = 128
     hkv_l, hq_l = Hkv // world, Hq // world
-    cache, q, past, sb, bi, bb = build_decode_problem(n, ctx, hq_l, hkv_l, D, seed=3 + rank)
+    tokens = int(ctx.sum())
+    kv_bytes = tokens * Hkv * 2 * (D + 4)  # whole job: all ranks' heads
+    per_rank = kv_bytes // world
+    n_pools = 1 if per_rank >= 4 * L2_BYTES else -(-4 * L2_BYTES // per_rank)
+    pools = [build_decode_problem(n, ctx, hq_l, hkv_l, D, seed=3 + rank + 100 * i) for i in range(n_pools)]
     maxc = int(ctx.max())
     out = torch.empty(n, hq_l * D, dtype=torch.float16, device="cuda")
-    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, cache, hq_l, n, n, maxc, 1)),
+    ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.float16, pools[0][0], hq_l, n, n, maxc, 1)),
                      dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     from openvino_contrib_b200.sharding import HeadShard, ShardGroup, gather_heads_rows
     shard = HeadShard(rank, world, Hq, Hkv)
     gathered = torch.empty(world * n, hq_l * D, dtype=torch.float16, device="cuda") if world > 1 else None
     exchange = "none"
     group = None
     if world > 1:
-        exchange = os.environ.get("B2A_BENCH_EXCHANGE", "peer")  # "peer": stores into every rank's memory; "nccl"
-        if exchange == "peer":
-            try:
-                group = ShardGroup(shard, staging_bytes=2 * n * Hq * D * 2)  # twice the output: low-latency exchange
-            except Exception as e:  # CUDA IPC not available in this container: fall back to the library collective
-                exchange = f"nccl (peer mapping failed: {type(e).__name__})"
-    # B2A_BENCH_DECODE_INPLACE=1: the group's own buffer, the step is ONE kernel producing the rows in place on every
-    # rank; 0: decode + merge-and-push + wait-and-copy kernels into a caller's buffer
-    inplace = os.environ.get("B2A_BENCH_DECODE_INPLACE", "0") == "1"  # measured at N=2: 0.118 ms (three kernels) vs 0.125 ms
-    out_full = None if inplace or group is None else torch.empty(n, Hq * D, dtype=torch.float16, device="cuda")
+        exchange = "peer stores from the decode kernel (8-byte value pairs with the step number), polled by a receiving kernel"
+        try:
+            group = ShardGroup(shard, staging_bytes=2 * n * Hq * D * 2)
+        except Exception as e:  # CUDA IPC not available in this container: fall back to the library collective
+            exchange = f"nccl all-gather after the kernels (peer mapping failed: {type(e).__name__})"
+    out_full = torch.empty(n, Hq * D, dtype=torch.float16, device="cuda") if group is not None else None
+    turn = [0]
 
     def step():
+        cache, q, past, sb, bi, bb = pools[turn[0] % n_pools]
+        turn[0] += 1
         if group is not None:
-            group.paged_attention(q, cache, past, sb, bi, bb, max_context_len=maxc, out_full=out_full, workspace=ws)
-            return
+            group.paged_attention(q, cache, past, sb, bi, bb, max_context_len=maxc, out_full=out_full, workspace=ws,
+                                  status=status)
+            return out_full
         b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1, out=out,
-                            workspace=ws)
-        if world > 1 and exchange != "local":  # "local": no exchange at all (diagnosis only; not a valid step)
-            gather_heads_rows(out, shard, D, buffer=gathered)
-    ms, how = timed_replay(step, steps, warmup, world)
+                            workspace=ws, status=status)
+        if world > 1:
+            return gather_heads_rows(out, shard, D, buffer=gathered)
+        return out
+    ms, how = timed_replay(step, steps, warmup, world, multiple_of=n_pools)
+    # after the timed region: a clean status word, and (N > 1) one more step on every pool compared, bit for bit, with
+    # the plain single-GPU kernels on each rank's shard all-gathered by NCCL
+    torch.cuda.synchronize()
+    verified = int(status.item()) == 0
+    if world > 1:
+        for i in range(n_pools):
+            turn[0] = i
+            full = step().clone()
+            cache, q, past, sb, bi, bb = pools[i]
+            o = b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1)
+            ref = gather_heads_rows(o, shard, D)
+            torch.cuda.synchronize()
+            verified = verified and int(status.item()) == 0 and bool(torch.equal(full, ref))
+        t = torch.tensor([1 if verified else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        verified = bool(t.item())
     if group is not None:
         torch.cuda.synchronize()
+        dist.barrier()
         group.close()
-    tokens = int(ctx.sum())
-    kv_bytes = tokens * Hkv * 2 * (D + 4)  # whole job: all ranks' heads
     pk = peaks()
     gbs = kv_bytes / (ms * 1e-3) / 1e9
     return {"workload": name, "kv_gbs": gbs, "ms_per_step": ms, "kv_bytes_per_step": kv_bytes,
             "frac_of_hbm_peak": gbs / (pk["hbm_gbs"] * world), "peak_gbs_per_gpu": pk["hbm_gbs"],
-            "peak_source": pk["source"], "cached_tokens": tokens,
-            "traffic": NCU_TRAFFIC.get(name) if world == 1 else None, "launches_per_step": (1 if inplace else 3) if group is not None else 2,
-            "output_exchange": exchange + (" (one kernel, in place)" if group is not None and inplace else ""),
-            "timing": how}
+            "peak_source": pk["source"], "cached_tokens": tokens, "verified": verified,
+            "l2": (f"{n_pools} pools of {per_rank / 1e6:.0f} MB per GPU walked in turn: every step reads a pool that "
+                   f"the steps in between evicted" if n_pools > 1 else
+                   f"{per_rank / 1e6:.0f} MB of cache per GPU and step, read once, evict-first: nothing of it survives in the 126 MB L2"),
+            "traffic": NCU_TRAFFIC.get(name) if world == 1 else None,
+            "traffic_source": TRAFFIC_SOURCE if world == 1 and name in NCU_TRAFFIC else None,
+            "launches_per_step": 2, "output_exchange": exchange, "timing": how}
 
 
 def bench_mixed(steps, warmup, rank, world):
@@ -463,8 +497,6 @@ def bench_mixed(steps, warmup, rank, world):
     out = torch.empty(ntok, Hq * D, dtype=torch.bfloat16, device="cuda")
     rb = int(sum((int(x) + 127) // 128 for x in qlen if x >= 2))  # what the scheduler knows (KvBlockManager reports it)
     kvt = int(sum((int(c) + 127) // 128 * 128 for c, x in zip(ctx, qlen) if x >= 2))  # likewise
-    if os.environ.get("B2A_BENCH_NO_GATHER") == "1":
-        kvt = 0
     ws = torch.empty(max(16, b2a.ops.paged_workspace_bytes(torch.bfloat16, cache, Hq, n, ntok, 4096, 1024, rb, kvt)),
                      dtype=torch.uint8, device="cuda")
 
@@ -510,11 +542,12 @@ def run_b2a(args):
             dist.barrier()
             dist.destroy_process_group()
         return
+    failed = False
     pre = bench_prefill(args, rank, world, local)
     decode = {}
     if args.only is None:
         for name in ("cfg3", "cfg5"):
-            decode[name] = bench_decode(name, max(args.steps, 20), max(args.warmup, 3), rank, world)
+            decode[name] = bench_decode(name, max(args.steps, 24), max(args.warmup, 3), rank, world)
         if world == 1:
             decode["cfg4"] = bench_mixed(max(args.steps, 20), max(args.warmup, 3), rank, world)
     cpu = None
@@ -533,13 +566,19 @@ def run_b2a(args):
                        if world > 1 else "single GPU",
                        "l2": "inputs + outputs (335 MB) exceed the 126 MB L2; no flush between steps"},
             "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["launches"],
-            "clocks": pre["clocks"], "decode": decode,
+            "clocks": pre["clocks"], "verified": pre["verified"], "decode": decode,
         }
         print(json.dumps(line))
+        if not pre["verified"] or not all(d.get("verified", True) for d in decode.values()):
+            print("bench.py: a workload's result did not verify (status word or comparison with the single-GPU "
+                  "kernels)", file=sys.stderr)
+            failed = True
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        sys.exit(1)
 
 
 def main():
