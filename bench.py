@@ -291,11 +291,11 @@ def bench_prefill(args, rank, world, local):
     # end to end through the public API with host buffers: H2D of q,k,v, kernel, D2H of the output
     out_h = torch.empty(B, hq_l, S, D, dtype=torch.bfloat16).pin_memory()
 
-    pipe = b2a.HostSdpaPipeline(B, hq_l, hkv_l, S, S, D, torch.bfloat16) if world == 1 else None
+    pipe = b2a.HostSdpaPipeline(B, hq_l, hkv_l, S, S, D, torch.bfloat16, causal=True) if world == 1 else None
 
     def e2e_step():
         if pipe is not None:  # upload, kernel and download of successive batch entries overlap on three streams
-            pipe(q_h, k_h, v_h, out_h, causal=True)
+            pipe(q_h, k_h, v_h, out_h)
             return
         qd, kd, vd = q_h.cuda(non_blocking=True), k_h.cuda(non_blocking=True), v_h.cuda(non_blocking=True)
         if group is not None:
@@ -309,7 +309,8 @@ def bench_prefill(args, rank, world, local):
     h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
     e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": out_h.numel() * 2, "ms_per_step": ems,
-           "api": "HostSdpaPipeline (per-batch-entry upload / kernel / download on three streams)" if pipe is not None
+           "api": f"C++ HostSdpaRunner: pinned upload, SdpaOp::Execute and download per (batch entry, KV head) piece "
+                  f"({pipe.pieces} pieces) on three streams" if pipe is not None
            else "sdpa on device copies of the host tensors"}
     if group is not None:
         torch.cuda.synchronize()

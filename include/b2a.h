@@ -271,6 +271,70 @@ int b2a_kvmgr_schedule_step(b2a_kvmgr* m, const int64_t* seq_ids, const int32_t*
                             int32_t block_indices_capacity, int32_t* block_indices_begins,
                             int32_t* num_block_indices, int32_t* max_context_len);
 
+/* ---------------------------------------------------------------------------------------------
+ * ScaledDotProductAttention on HOST tensors: what the plugin does for a model whose inputs and outputs live in host
+ * memory - ParameterOp uploads (src/ops/parameter.cpp:24-33), the operation runs, ResultOp downloads
+ * (src/ops/result.cpp:28-43) - with the three overlapped: the problem is cut into pieces of a few KV heads of one batch entry,
+ * and the upload of piece i+1, the operation on piece i and the download of piece i-1 run at the same time on three
+ * streams.  The operation is the C++ SdpaOp, created through the operation registry, executed once per piece; called
+ * again with the same four tensors, the whole step is captured into a CUDA graph once and replayed from then on.
+ * _create allocates (device tensors for the shapes given, streams, events); _run only enqueues: q, k, v, out are
+ * host pointers in [B, H, S, D] layout (pinned, or the copies serialise), the work is ordered after what `stream`
+ * holds and `stream` waits for the last download.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct b2a_host_sdpa b2a_host_sdpa;
+/* kv_heads_per_piece: KV heads (with the query heads that read them) per piece, a divisor of Hkv; 0 = chosen so that a
+ * piece uploads at least 8 MB (much smaller copies do not reach the bus's bandwidth). */
+int b2a_host_sdpa_create(int32_t dtype, int32_t B, int32_t Hq, int32_t Hkv, int32_t Sq, int32_t Skv, int32_t D,
+                         int32_t causal, int32_t kv_heads_per_piece, b2a_host_sdpa** out);
+int b2a_host_sdpa_run(b2a_host_sdpa* h, const void* q, const void* k, const void* v, void* out, b2a_stream_t stream);
+int b2a_host_sdpa_pieces(const b2a_host_sdpa* h);
+void b2a_host_sdpa_destroy(b2a_host_sdpa* h);
+
+/* ---------------------------------------------------------------------------------------------
+ * KV cache of a STATEFUL model kept in the paged pool.
+ *
+ * Takes the place of CudaVariableState (src/cuda_variable_state.hpp:31-183) for the two variables - K and V, each a
+ * dense [B, Hkv, T, D] tensor - that a ReadValue / Concat / Assign model keeps per attention layer
+ * (src/ops/read_value.cpp:31-72, src/ops/assign.cpp:29-56, src/kernels/concat.cu:16-32), with the bytes living in the
+ * block pool the paged kernels read: Assign(Concat(ReadValue, new)) becomes _append (the new rows are quantised into
+ * their blocks; the past is not copied), ReadValue -> attention becomes _last_step (pools + step tables in
+ * PagedAttentionExtension's operand order).  reset / set_state / get_state keep their meaning for the user-facing
+ * API (src/cuda_variable_state.hpp:62-105); _export / _import move the exact pool image, for fixtures.
+ * One object = one layer, B sequences of equal length.  _create, _set_state, _get_state, _export, _import allocate
+ * and synchronise (slow paths); _append, _read_dense and _last_step only enqueue.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct b2a_kvstate b2a_kvstate;
+typedef struct b2a_kvstate_step {
+    const void *k_cache, *v_cache;                                                           /* device pools */
+    const int32_t *past_lens, *subsequence_begins, *block_indices, *block_indices_begins;   /* device tables */
+    int32_t num_seqs, num_tokens, num_blocks_total, max_context_len, max_q_len;
+    int32_t prefill_row_blocks, prefill_kv_tokens;                                           /* b2a_paged_desc hints */
+} b2a_kvstate_step;
+/* kv_dtype: pool element type (B2A_U8 | B2A_F16 | B2A_BF16); x_dtype: the variable's element type (B2A_F32 | B2A_F16 |
+ * B2A_BF16); max_step_tokens bounds q_len of one _append. */
+int b2a_kvstate_create(int32_t kv_dtype, int32_t x_dtype, int32_t batch, int32_t hkv, int32_t d, int32_t block_size,
+                       int32_t num_blocks, int32_t max_step_tokens, b2a_kvstate** out);
+void b2a_kvstate_destroy(b2a_kvstate* s);
+int32_t b2a_kvstate_length(const b2a_kvstate* s); /* T: positions held per sequence */
+int b2a_kvstate_reset(b2a_kvstate* s);
+/* k_host / v_host: HOST tensors [B, Hkv, T, D] of x_dtype.  _get_state wants T == b2a_kvstate_length; a u8 pool
+ * returns the de-quantised values (code - zp) * scale, i.e. what the attention kernels compute with. */
+int b2a_kvstate_set_state(b2a_kvstate* s, const void* k_host, const void* v_host, int32_t T, b2a_stream_t stream);
+int b2a_kvstate_get_state(const b2a_kvstate* s, void* k_host, void* v_host, int32_t T, b2a_stream_t stream);
+/* k_new / v_new: DEVICE tensors [B, Hkv, q_len, D] of x_dtype.  B2A_ERR_CAPACITY (nothing changed) when the pool is
+ * exhausted. */
+int b2a_kvstate_append(b2a_kvstate* s, const void* k_new, const void* v_new, int32_t q_len, int32_t* status,
+                       b2a_stream_t stream);
+/* The variable itself as a dense DEVICE tensor [B, Hkv, T, D] (what ReadValueOp would have copied out). */
+int b2a_kvstate_read_dense(const b2a_kvstate* s, void* k_dev, void* v_dev, int32_t T, int32_t* status,
+                           b2a_stream_t stream);
+/* Pools and tables of the last _append (valid until the next _append / _set_state / _reset / _import). */
+int b2a_kvstate_last_step(const b2a_kvstate* s, b2a_kvstate_step* out);
+size_t b2a_kvstate_export_bytes(const b2a_kvstate* s);
+int b2a_kvstate_export(const b2a_kvstate* s, void* host_blob, size_t bytes, b2a_stream_t stream);
+int b2a_kvstate_import(b2a_kvstate* s, const void* host_blob, size_t bytes, b2a_stream_t stream);
+
 const char* b2a_status_string(int status);
 int b2a_version(void);
 

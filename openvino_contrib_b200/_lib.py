@@ -62,6 +62,22 @@ SIGNATURES = {
                                               C.c_size_t, C.c_void_p, C.c_void_p]),
     "b2a_sdpa_forward_sharded": (C.c_int, [C.c_void_p, C.POINTER(SdpaDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                            C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p]),
+    "b2a_host_sdpa_create": (C.c_int, [C.c_int32] * 9 + [C.POINTER(C.c_void_p)]),
+    "b2a_host_sdpa_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2a_host_sdpa_pieces": (C.c_int, [C.c_void_p]),
+    "b2a_host_sdpa_destroy": (None, [C.c_void_p]),
+    "b2a_kvstate_create": (C.c_int, [C.c_int32] * 8 + [C.POINTER(C.c_void_p)]),
+    "b2a_kvstate_destroy": (None, [C.c_void_p]),
+    "b2a_kvstate_length": (C.c_int32, [C.c_void_p]),
+    "b2a_kvstate_reset": (C.c_int, [C.c_void_p]),
+    "b2a_kvstate_set_state": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "b2a_kvstate_get_state": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "b2a_kvstate_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b2a_kvstate_read_dense": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b2a_kvstate_last_step": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b2a_kvstate_export_bytes": (C.c_size_t, [C.c_void_p]),
+    "b2a_kvstate_export": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b2a_kvstate_import": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b2a_kvmgr_create": (C.c_int, [C.c_int32, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p)]),
     "b2a_kvmgr_destroy": (None, [C.c_void_p]),
     "b2a_kvmgr_add_sequence": (C.c_int, [C.c_void_p, C.c_int64]),

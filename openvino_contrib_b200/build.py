@@ -25,8 +25,11 @@ NVCC_FLAGS = [
 ]
 
 CU_SOURCES = ["csrc/api.cu", "csrc/attn_generic.cu", "csrc/paged_kv_store.cu", "csrc/paged_decode.cu",
-              "csrc/sdpa_tcgen05.cu", "csrc/shard_group.cu"]
-CXX_SOURCES = ["host/kv_block_manager.cpp"]
+              "csrc/sdpa_tcgen05.cu", "csrc/shard_group.cu", "csrc/paged_kv_state.cu"]
+# host side in the library: the block manager, the operator classes (registered with the operation registry when the
+# library is loaded) and the host-tensor pipeline built on them
+CXX_SOURCES = ["host/kv_block_manager.cpp", "host/attention_ops.cpp", "host/host_pipeline.cpp",
+               "host/kv_pool_state.cpp"]
 
 
 def nvcc() -> str:
@@ -81,7 +84,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-HOST_TEST_SOURCES = ["host/attention_ops.cpp", "host/host_tests.cpp"]
+HOST_TEST_SOURCES = ["host/host_tests.cpp"]
 HOST_TESTS = os.path.join(BUILD, "host_tests")
 
 

@@ -88,6 +88,19 @@ int resolve_sdpa(const b2a_sdpa_desc* desc, SdpaResolved& r) {
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// One event per host thread and device, created at the thread's first mixed step on that device and kept: it is
+// recorded and waited for within one call, so calls of different threads never share one.
+cudaEvent_t step_join_event() {
+    thread_local cudaEvent_t events[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (events[dev] == nullptr && cudaEventCreateWithFlags(&events[dev], cudaEventDisableTiming) != cudaSuccess) {
+        events[dev] = nullptr;
+        (void)cudaGetLastError();
+    }
+    return events[dev];
+}
+
 PagedTables tables_of(const b2a_paged_desc& d, const int32_t* past_lens, const int32_t* subsequence_begins,
                       const int32_t* block_indices, const int32_t* block_indices_begins) {
     return PagedTables{past_lens, subsequence_begins, block_indices, block_indices_begins,
@@ -220,10 +233,16 @@ int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const voi
         const size_t list_at = (plan.workspace_bytes + 15) & ~static_cast<size_t>(15);
         if (workspace == nullptr || workspace_bytes < list_at + paged_tc_plan_bytes(d)) return B2A_ERR_WORKSPACE;
         if (!aligned(workspace, 16)) return B2A_ERR_ALIGN;
+        // The persistent prefill kernel leaves whole SMs free for the decode rows, which then run beside it.  An
+        // event recorded right behind it lets the step's last kernel wait for it explicitly.
+        cudaEvent_t join = step_join_event();
+        bool beside = false;
         const int rc2 = paged_tc_launch(d, query, k_cache, v_cache, t, out, static_cast<char*>(workspace) + list_at,
-                                        status, s);
+                                        status, s, join != nullptr ? &beside : nullptr);
         if (rc2 != B2A_OK) return rc2;
-        return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, workspace, status, s);
+        if (beside && cudaEventRecord(join, s) != cudaSuccess) return B2A_ERR_CUDA;
+        return paged_decode_launch(d, plan, query, k_cache, v_cache, t, out, workspace, status, s, nullptr,
+                                   beside ? join : nullptr);
     }
     return paged_generic_launch(d, query, k_cache, v_cache, t, out, status, s);
 }

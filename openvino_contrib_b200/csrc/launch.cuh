@@ -55,9 +55,14 @@ struct DecodePlan {
 bool paged_decode_supported(const b2a_paged_desc& d);   // a pure decode step
 bool paged_decode_geometry_ok(const b2a_paged_desc& d); // the kernel's shape limits, whatever the step's mix
 DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count);
+// beside_predecessor != nullptr: the kernel before this launch on the stream is the prefill kernel of the same mixed
+// step, which has already waited for everything the decode rows read (cache, tables, query) and writes nothing they
+// touch; the event was recorded right behind it.  The decode kernel then starts as soon as that kernel's CTAs are
+// seated, on the SMs it leaves free, instead of after it, and does not wait for it.  The merge kernel is launched
+// the ordinary way behind a wait on the event, so it - and whatever follows it on the stream - comes after both.
 int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
                         const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
-                        cudaStream_t stream, const PeerPush* push = nullptr);
+                        cudaStream_t stream, const PeerPush* push = nullptr, cudaEvent_t beside_predecessor = nullptr);
 
 // Same launch with the split-K partials in the library's built-in device array instead of a caller workspace.
 int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query,
@@ -93,8 +98,11 @@ int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, l
 // left to the decode kernel, which in turn skips the others)
 bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* out);
 size_t paged_tc_plan_bytes(const b2a_paged_desc& d);  // scratch for the device-built work list
+// decode_may_overlap (optional, out): true when the attention kernel just launched leaves whole SMs free for the decode
+// rows of the same step, which the caller then launches with paged_decode_launch(..., beside_predecessor = true)
 int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
-                    const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream);
+                    const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream,
+                    bool* decode_may_overlap = nullptr);
 
 int device_sm_count();
 

@@ -37,9 +37,12 @@ constexpr int kD = 128;
 constexpr int kBS = 16;
 constexpr int kChunk = kBS * (kD + 4);   // 2112 bytes: 2048 codes, 16 f16 scales, 16 f16 zero-points
 constexpr int kStage = 2 * kChunk;       // K chunk then V chunk
-constexpr int kWarps = 4;
-constexpr int kStages = 3;
-constexpr int kSmemBytes = kWarps * kStages * kStage;
+constexpr int kStages = 3;                // copy stages per warp
+// Warps per CTA: 4 when the grid fills every SM four CTAs deep (16 warps per SM hide one another's latencies).  A grid
+// of at most two CTAs per SM - a head shard of a step - would leave each warp alone with its chain of dependent
+// instructions per block (measured: 5.3 TB/s instead of 7), so its CTAs take 8 warps over the same blocks.
+constexpr int kWarpsFew = 4, kWarpsMany = 8;
+constexpr int smem_bytes(int warps) { return warps * kStages * kStage; }
 constexpr float kNegBig = -1.0e30f;      // finite "minus infinity" for the running max (keeps exp2 arguments NaN-free)
 
 struct DecodeParams {
@@ -55,6 +58,8 @@ struct DecodeParams {
     int sliding_window;
     float scale_log2;  // softmax scale * log2(e)
     int32_t* status;
+    int beside_predecessor;      // see paged_decode_launch: no wait for the kernel before this one
+    cudaEvent_t predecessor_done;  // host side only: completes with that kernel
     PeerPush push;     // world == 0 unless the heads are sharded over several GPUs
 };
 
@@ -142,7 +147,7 @@ enum ChunkState {
 // The walk over this CTA's chunk of one (sequence, KV head).  On kChunkWorked its partial is in the workspace, `nsplit`
 // is the number of CTAs of this sequence that write one and `tok` the sequence's token row.  With kRowIsSeq the
 // token row must equal the sequence index (the sharded exchange addresses rows by sequence), else kChunkInvalid.
-template <typename T, int NT, bool kRowIsSeq>
+template <typename T, int NT, bool kRowIsSeq, int kWarps>
 __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out) {
     const int hk = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -189,7 +194,7 @@ __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_
         }
     }
 
-    // blocks of this warp: my_lo + warp + 4*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
+    // blocks of this warp: my_lo + warp + kWarps*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
     const int n_w = (my_hi - my_lo - warp + kWarps - 1) / kWarps;
     const int32_t* btab = p.t.block_indices + bib0;
     int my_phys = 0;
@@ -409,9 +414,9 @@ __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_
     }
     __syncthreads();
 
-    // ---- merge the 4 warps: thread = column d
-    const int d = tid;
-    for (int g = 0; g < p.G; ++g) {
+    // ---- merge the warps: thread = (column d, one of the heads taken per round)
+    const int d = tid % kD;
+    for (int g = tid / kD; g < p.G; g += kWarps * 32 / kD) {
         float mw[kWarps], mc = kNegBig;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
@@ -488,7 +493,7 @@ __device__ __forceinline__ void wait_flags(const int32_t* flags, int n, int32_t 
 //          of every rank r; such a store arrives whole or not at all, so the receiver simply polls the word.
 //   !kLL : the rows are stored as they are - into staging[r][0] of every rank (the ranks' fixed output buffers), or,
 //          without a group, into the caller's output.
-template <typename T, int kDims, bool kLL>
+template <typename T, int kDims, bool kLL, int kWarps>
 __device__ __forceinline__ void merge_and_deliver(const DecodeParams& p, int seq, int hk, int tok, int nsplit,
                                                   int32_t epoch) {
     constexpr int kVec = kDims / 4;            // float4 loads per split
@@ -575,7 +580,7 @@ __device__ __forceinline__ void send_zero_row_segment(const DecodeParams& p, int
     const uint2 word = make_uint2(0u, static_cast<uint32_t>(epoch));
     for (int r = 0; r < p.push.world; ++r) {
         uint2* dst = reinterpret_cast<uint2*>(p.push.staging[r][epoch & 1]) + at;
-        for (int i = threadIdx.x; i < words; i += kWarps * 32) dst[i] = word;
+        for (int i = threadIdx.x; i < words; i += blockDim.x) dst[i] = word;
     }
 }
 
@@ -586,14 +591,16 @@ __device__ __forceinline__ void send_zero_row_segment(const DecodeParams& p, int
 // fixed output buffers, so a rank first announces that it has begun the step (its readers of the previous output are
 // done), nobody stores before every rank has, and the grid's last CTA publishes the step and waits for the other
 // ranks' steps, so that the output is complete on this rank when the kernel ends.
-template <typename T, int NT, int kMode>
-__global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const DecodeParams p) {
+template <typename T, int NT, int kMode, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) paged_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     int nsplit = 0, tok = 0;
-    grid_dependency_wait();     // the cache rows of this step's new tokens and the query come from earlier kernels
+    // the cache rows of this step's new tokens and the query come from earlier kernels (beside the prefill kernel of
+    // a mixed step there is nothing to wait for: that kernel waited for them already and is not waited for itself)
+    if (!p.beside_predecessor) grid_dependency_wait();
     grid_launch_dependents();   // the next kernel's CTAs may take their seats while this grid drains
     if constexpr (kMode == 0) {
-        decode_chunk<T, NT, false>(p, smem, nsplit, tok);
+        decode_chunk<T, NT, false, kWarps>(p, smem, nsplit, tok);
     } else {
         constexpr bool kLL = kMode == 1;
         __shared__ int s_role;
@@ -601,50 +608,58 @@ __global__ void __launch_bounds__(kWarps * 32, 4) paged_decode_kernel(const Deco
         const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
         if (!kLL && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
             st_release_sys(p.push.started[tid] + p.push.rank, epoch);  // this rank's readers of the previous step are done
-        const ChunkState state = decode_chunk<T, NT, kLL>(p, smem, nsplit, tok);
+        const ChunkState state = decode_chunk<T, NT, kLL, kWarps>(p, smem, nsplit, tok);
         if (tid == 0) s_role = 0;
         if (state == kChunkWorked) {
-            __threadfence();  // this CTA's partial before its ticket
-            __syncthreads();
+            __syncthreads();  // every thread's part of the partial is written ...
             if (tid == 0) {
+                __threadfence();  // ... and, through the barrier, ordered before this thread's ticket
                 int32_t* ctr = p.push.group_counters + seq * p.Hkv + hk;
                 const bool last = atomicAdd(ctr, 1) == nsplit - 1;
-                if (last) *ctr = 0;
+                if (last) {
+                    *ctr = 0;
+                    __threadfence();  // the other CTAs' partials after the ticket
+                }
                 s_role = last ? 1 : 0;
             }
             __syncthreads();
             if (s_role == 1) {
-                __threadfence();  // the other CTAs' partials after the ticket
                 if (!kLL) {
                     wait_flags(p.push.started[p.push.rank], p.push.world, epoch, p.push.wait_ns, p.status);  // every rank has begun this step
                     __syncthreads();
                 }
-                if (p.G > 4) merge_and_deliver<T, 8, kLL>(p, seq, hk, tok, nsplit, epoch);
-                else merge_and_deliver<T, 4, kLL>(p, seq, hk, tok, nsplit, epoch);
+                // columns per thread such that one round covers a group of up to eight heads where the CTA has the threads
+                if constexpr (kWarps == kWarpsFew) {
+                    if (p.G > 4) merge_and_deliver<T, 8, kLL, kWarps>(p, seq, hk, tok, nsplit, epoch);
+                    else merge_and_deliver<T, 4, kLL, kWarps>(p, seq, hk, tok, nsplit, epoch);
+                } else {
+                    merge_and_deliver<T, 4, kLL, kWarps>(p, seq, hk, tok, nsplit, epoch);
+                }
                 if (!kLL) __threadfence_system();  // this CTA's peer stores before its arrival below
             }
         } else if (kLL && (state == kChunkInvalid || state == kChunkNotRow) && blockIdx.z == 0) {
             if (state == kChunkNotRow && tid == 0) report(p.status, B2A_DEV_BAD_LEN);
             send_zero_row_segment(p, seq, hk, epoch);
         }
-        __syncthreads();
-        if (tid == 0) {
-            const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
-            const bool last = atomicAdd(p.push.done_counter, 1) == total - 1;
-            if (last) {
-                *p.push.done_counter = 0;  // every CTA has arrived: ready for the next step
-                *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;  // read by the next kernel on the stream
-                if (!kLL) {
+        if constexpr (!kLL) {
+            // in place: the grid's last CTA publishes the step on every rank and waits for theirs
+            __syncthreads();
+            if (tid == 0) {
+                const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
+                const bool last = atomicAdd(p.push.done_counter, 1) == total - 1;
+                if (last) {
+                    *p.push.done_counter = 0;  // every CTA has arrived: ready for the next step
+                    *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;
                     __threadfence_system();
                     for (int r = 0; r < p.push.world; ++r) st_release_sys(p.push.flags[r] + p.push.rank, epoch);
                 }
+                s_role = last ? 2 : 0;
             }
-            s_role = last ? 2 : 0;
-        }
-        if (!kLL) {
             __syncthreads();
             if (s_role == 2) wait_flags(p.push.flags[p.push.rank], p.push.world, epoch, p.push.wait_ns, p.status);
         }
+        // (low-latency form: nothing to publish - the words carry the step number, and the receiving kernel, which
+        // is the step's last, counts the step)
     }
 }
 
@@ -687,46 +702,68 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
 
 // Receiver of the low-latency exchange: one CTA per row polls every 8-byte word of its staging row until it carries
 // this step's number (bounded in real time: B2A_DEV_TIMEOUT after push.wait_ns) and writes the two values to the
-// caller's output.
+// caller's output.  It is the last kernel of the step, so its last CTA counts the step: the decode kernel before it
+// and this kernel read the same counter value.
 __global__ void __launch_bounds__(256) peer_ll_copy_kernel(const PeerPush push, uint32_t* out, int pairs_per_row,
                                                             int32_t* status) {
-    grid_dependency_wait();  // our own decode kernel (its last CTA publishes the step number)
+    grid_dependency_wait();  // our own decode kernel (its CTAs read the step counter that this kernel advances)
     grid_launch_dependents();
-    const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(push.step_counter));
-    const uint2* src = reinterpret_cast<const uint2*>(push.staging[push.rank][epoch & 1]) +
-                       static_cast<size_t>(blockIdx.x) * pairs_per_row;
-    uint32_t* dst = out + static_cast<size_t>(blockIdx.x) * pairs_per_row;
+    const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(push.step_counter) + 1);
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(push.staging[push.rank][epoch & 1]) +
+                                                      static_cast<size_t>(blockIdx.x) * pairs_per_row);
+    uint2* dst = reinterpret_cast<uint2*>(out + static_cast<size_t>(blockIdx.x) * pairs_per_row);
     const long long t0 = global_ns();
     bool gave_up = false;
-    for (int i = threadIdx.x; i < pairs_per_row; i += blockDim.x) {
-        uint32_t lo, hi;
+    for (int i = threadIdx.x; i < pairs_per_row / 2; i += blockDim.x) {  // two words per load (rows are multiples of 256 bytes)
+        uint32_t a, ea, b, eb;
         for (;;) {
-            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "l"(src + i) : "memory");
-            if (hi == epoch || gave_up) break;
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(a), "=r"(ea), "=r"(b), "=r"(eb)
+                         : "l"(src + i)
+                         : "memory");
+            if ((ea == epoch && eb == epoch) || gave_up) break;
             if (global_ns() - t0 > push.wait_ns) {
                 report(status, B2A_DEV_TIMEOUT);
                 gave_up = true;
             }
         }
-        dst[i] = lo;
+        dst[i] = make_uint2(a, b);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (atomicAdd(push.done_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+            *push.done_counter = 0;
+            *reinterpret_cast<volatile int32_t*>(push.step_counter) = static_cast<int32_t>(epoch);
+        }
     }
 }
 
-template <typename T, int NT, int kMode>
-int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
-    auto kern = paged_decode_kernel<T, NT, kMode>;
+template <typename T, int NT, int kMode, int kWarps>
+int launch_kernel_w(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
+    auto kern = paged_decode_kernel<T, NT, kMode, kWarps>;
     static std::atomic<bool> configured[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return B2A_ERR_CUDA;
     if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kWarps)) != cudaSuccess)
             return B2A_ERR_CUDA;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     // the split index is the slowest-varying one: every sequence's first chunks (always full) are dispatched before
     // anybody's last chunk (partial or empty), which shortens the tail of a step with uneven contexts
     dim3 grid(p.Hkv, num_seqs, p.max_splits);
-    return launch_overlapped(kern, grid, dim3(kWarps * 32), kSmemBytes, stream, p) == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+    return launch_overlapped(kern, grid, dim3(kWarps * 32), smem_bytes(kWarps), stream, p) == cudaSuccess ? B2A_OK
+                                                                                                             : B2A_ERR_CUDA;
+}
+
+template <typename T, int NT, int kMode>
+int launch_kernel(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
+    const long long ctas = static_cast<long long>(p.Hkv) * num_seqs * p.max_splits;
+    const int sms = device_sm_count();
+    if constexpr (NT == 1) {  // (groups of more than eight query heads keep the one variant)
+        if (sms > 0 && ctas <= 2LL * sms) return launch_kernel_w<T, NT, kMode, kWarpsMany>(p, num_seqs, stream);
+    }
+    return launch_kernel_w<T, NT, kMode, kWarpsFew>(p, num_seqs, stream);
 }
 
 template <typename T, int NT>
@@ -743,6 +780,13 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
     }
     const int rc = launch_kernel<T, NT, 0>(p, num_seqs, stream);
     if (rc != B2A_OK) return rc;
+    if (p.beside_predecessor) {
+        // an ordinary launch behind a wait for the prefill kernel: it starts when the decode kernel AND the kernel it
+        // ran beside have completed, which closes the step for whatever comes next on the stream
+        if (cudaStreamWaitEvent(stream, p.predecessor_done, 0) != cudaSuccess) return B2A_ERR_CUDA;
+        paged_decode_merge_kernel<T><<<dim3(p.Hq, num_seqs), dim3(kD), 0, stream>>>(p);
+        return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
+    }
     return launch_overlapped(paged_decode_merge_kernel<T>, dim3(p.Hq, num_seqs), dim3(kD), 0, stream, p) == cudaSuccess
                ? B2A_OK
                : B2A_ERR_CUDA;
@@ -790,9 +834,11 @@ DecodePlan paged_decode_plan(const b2a_paged_desc& d, int sm_count) {
 
 int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const void* query, const void* k_cache,
                         const void* v_cache, const PagedTables& t, void* out, void* workspace, int32_t* status,
-                        cudaStream_t stream, const PeerPush* push) {
+                        cudaStream_t stream, const PeerPush* push, cudaEvent_t beside_predecessor) {
     DecodeParams p{};
     if (push != nullptr) p.push = *push;
+    p.beside_predecessor = beside_predecessor != nullptr && push == nullptr ? 1 : 0;
+    p.predecessor_done = beside_predecessor;
     p.query = query;
     p.k_cache = static_cast<const uint8_t*>(k_cache);
     p.v_cache = static_cast<const uint8_t*>(v_cache);

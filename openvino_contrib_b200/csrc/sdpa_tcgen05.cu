@@ -95,21 +95,36 @@ struct TcPeers {
 // (sequence, tile pair) items that have work; the attention grid is then sized by a host-side bound on the item
 // count (exact when the caller passes the scheduler's hint) instead of max_q_len x num_seqs, which for a step with
 // a few long prefills and many decode sequences would be almost all empty CTAs.
-constexpr int kPlanHeaderInts = 4;
+constexpr int kPlanHeaderInts = 4;  // [0] items in the list (per KV head), [1] CTAs of the attention kernel that take items
+// A mixed step runs its prefill rows (tensor-bound) and its decode rows (HBM-bound) at the same time: the attention
+// kernel keeps only as many SMs as its share of the step's work needs and the decode kernel, launched as soon as
+// those CTAs are seated, takes the rest (and the others as they come free).  The share is worked out here from the
+// tables: item-steps of the work list against cached bytes of the one-token sequences, each divided by what one SM
+// gets through per microsecond (measured on a step of eight 1024-token prefills beside 120 decode sequences: about
+// 3.4 us per item-step of two 128 x 128 tiles over 128 keys at the efficiency of short items; about 63 bytes per
+// nanosecond of u8 cache per SM while the SMs that decode are a minority).
+constexpr float kUsPerItemStep = 3.4f;
+constexpr float kDecodeBytesPerNsPerSm = 63.f;
+constexpr float kHbmBytesPerNs = 6500.f;
 // With `owner` given the kernel also lays out the gathered K/V scratch: every multi-token sequence gets a row range
 // of roundup(context, 128) rows (kv_base[seq]; allocation order is whatever the atomics make it), and owner[g] names
 // the sequence that 128-row group g belongs to (-1: nobody), which is how paged_gather_kernel finds its work.
-__global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t, const int G, const int capacity,
-                                                            int* plan, int32_t* status, int* kv_base, int* owner,
-                                                            const int owner_groups) {
+__global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t, const int G, const int Hkv,
+                                                            const int capacity, int* plan, int32_t* status,
+                                                            int* kv_base, int* owner, const int owner_groups,
+                                                            const int attention_ctas, const int share_with_decode) {
     // The list is sorted by weight (key steps of the pair's later tile, clamped to 255), heaviest first: a counting
     // sort in three passes over the sequences - histogram, bucket offsets, scatter.
     constexpr int kBuckets = 256;
-    __shared__ int s_hist[kBuckets], s_count, s_groups;
+    __shared__ int s_hist[kBuckets], s_count, s_groups, s_steps;
+    __shared__ unsigned long long s_decode_blocks;
     grid_dependency_wait();  // earlier kernels may still read the previous step's list and scratch layout
     grid_launch_dependents();
     for (int i = threadIdx.x; i < kBuckets; i += blockDim.x) s_hist[i] = 0;
-    if (threadIdx.x == 0) s_count = s_groups = 0;
+    if (threadIdx.x == 0) {
+        s_count = s_groups = s_steps = 0;
+        s_decode_blocks = 0ull;
+    }
     if (owner != nullptr)
         for (int g = threadIdx.x; g < owner_groups; g += blockDim.x) owner[g] = -1;
     __syncthreads();
@@ -121,11 +136,19 @@ __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t,
     };
     for (int s = threadIdx.x; s < t.num_seqs; s += blockDim.x) {
         const int qlen = t.subsequence_begins[s + 1] - t.subsequence_begins[s];
+        if (qlen == 1 && t.past_lens[s] >= 0)
+            atomicAdd(&s_decode_blocks, static_cast<unsigned long long>(t.past_lens[s] / t.block_size + 1));
         if (qlen < 2) continue;
         const int past = max(0, t.past_lens[s]);
         const int pairs = (((qlen + 127) / 128) * G + 1) / 2;
         atomicAdd(&s_count, pairs);
-        for (int i = 0; i < pairs; ++i) atomicAdd(&s_hist[weight(past, qlen, i)], 1);
+        int steps = 0;
+        for (int i = 0; i < pairs; ++i) {
+            const int w = weight(past, qlen, i);
+            atomicAdd(&s_hist[w], 1);
+            steps += w;
+        }
+        atomicAdd(&s_steps, steps);
         if (owner != nullptr) {
             const int groups = t.past_lens[s] < 0 ? 0 : (past + qlen + 127) / 128;
             const int g0 = atomicAdd(&s_groups, groups);
@@ -168,6 +191,20 @@ __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t,
             report(status, B2A_DEV_BAD_LEN);
             plan[0] = 0;  // nothing is computed from a scratch that does not hold every sequence
         }
+        // how many of the attention kernel's CTAs take items (the others leave at once and free their SMs)
+        int ctas = attention_ctas;
+        if (share_with_decode && s_decode_blocks > 0ull && attention_ctas > 1) {
+            const float prefill_sm_us = static_cast<float>(s_steps) * Hkv * kUsPerItemStep;
+            const float decode_bytes = static_cast<float>(s_decode_blocks) * Hkv * 2.f * kCacheChunk;
+            const float decode_sm_us = decode_bytes / (kDecodeBytesPerNsPerSm * 1000.f);
+            const float share = prefill_sm_us / (prefill_sm_us + decode_sm_us);
+            ctas = static_cast<int>(ceilf(share * attention_ctas));
+            // the decode rows cannot use more SMs than it takes to saturate the memory system
+            const int decode_max = static_cast<int>(kHbmBytesPerNs / kDecodeBytesPerNsPerSm);
+            ctas = max(ctas, attention_ctas - decode_max);
+            ctas = min(max(ctas, 1), attention_ctas);
+        }
+        plan[1] = ctas;
     }
 }
 
@@ -324,6 +361,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     constexpr bool kKvBf16 = kPaged ? false : kBf16;  // element format of the K/V tiles and of P
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // A kernel launched programmatically dependent on this one (the decode kernel of a mixed step) may take the SMs
+    // this grid leaves free as soon as every CTA is seated.
+    grid_launch_dependents();
 
     // ---- work items.  An item is a pair of tiles of one KV head.  Rows are numbered inside the sequence (paged) or
     // the tensor (dense); `pos_base` is the key position the first row of the problem may see up to, `kv_limit` the
@@ -338,9 +378,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     int seq = 0, tok_base = 0, nrows_total = 0, pos_base = 0, kv_limit = 0;
     bool causal = true;
     int nrb = 0, tiles = 0, pairs = 0, total_items = 0;
+    int active_ctas = static_cast<int>(gridDim.x);  // CTAs that take items
     if constexpr (kPaged) {
         total_items = p.plan[0] * p.Hkv;  // the grid is only a bound on the number of items
         if (kDequant && static_cast<int>(blockIdx.x * gridDim.y + blockIdx.y) >= total_items) return;
+        if constexpr (kGathered) {
+            // the plan kernel decides how many CTAs the prefill rows keep; the others give their SM to the decode rows
+            active_ctas = min(max(p.plan[1], 1), static_cast<int>(gridDim.x));
+            if (static_cast<int>(blockIdx.x) >= active_ctas) return;
+        }
     } else {
         nrows_total = p.Sq;
         kv_limit = p.Skv;
@@ -358,7 +404,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (k > 0) return false;
                 idx = static_cast<int>(blockIdx.x * gridDim.y + blockIdx.y);
             } else {
-                const int ctas = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
+                const int ctas = active_ctas, me = static_cast<int>(blockIdx.x);
                 idx = k * ctas + ((k & 1) ? ctas - 1 - me : me);
             }
             if (idx >= total_items) return false;
@@ -1145,7 +1191,8 @@ TcWorkspace tc_workspace(const b2a_paged_desc& d) {
 size_t paged_tc_plan_bytes(const b2a_paged_desc& d) { return tc_workspace(d).total; }
 
 int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_cache, const void* v_cache,
-                    const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream) {
+                    const PagedTables& t, void* out, void* plan_ws, int32_t* status, cudaStream_t stream,
+                    bool* decode_may_overlap) {
     const bool bf16 = d.q_dtype == B2A_BF16;
     const int capacity = paged_tc_capacity(d);
     const TcWorkspace w = tc_workspace(d);
@@ -1153,8 +1200,17 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     char* ws = static_cast<char*>(plan_ws);
     int* kv_base = gathered ? reinterpret_cast<int*>(ws + w.kv_base_at) : nullptr;
     int* owner = gathered ? reinterpret_cast<int*>(ws + w.owner_at) : nullptr;
-    if (launch_overlapped(paged_tc_plan_kernel, dim3(1), dim3(256), 0, stream, t, d.Hq / d.Hkv, capacity,
-                          static_cast<int*>(plan_ws), status, kv_base, owner, w.groups) != cudaSuccess)
+    const int sms = device_sm_count();
+    if (sms <= 0) return B2A_ERR_CUDA;
+    const long long bound = static_cast<long long>(capacity) * d.Hkv;
+    const int attention_ctas = static_cast<int>(bound < sms ? bound : sms);  // persistent CTAs over the sorted list
+    // The decode rows may run beside the prefill rows when the attention kernel is the persistent one (one CTA per SM
+    // at most, so what it leaves free is whole SMs) and the caller launches the decode kernel right behind it.
+    const bool share = gathered && decode_may_overlap != nullptr;
+    if (decode_may_overlap != nullptr) *decode_may_overlap = share;
+    if (launch_overlapped(paged_tc_plan_kernel, dim3(1), dim3(256), 0, stream, t, d.Hq / d.Hkv, d.Hkv, capacity,
+                          static_cast<int*>(plan_ws), status, kv_base, owner, w.groups, attention_ctas,
+                          share ? 1 : 0) != cudaSuccess)
         return B2A_ERR_CUDA;
     // the step's query matrix [tokens, Hq*128] as a [1, Hq, tokens, 128] view
     const int64_t qs[4] = {static_cast<int64_t>(d.num_tokens) * d.Hq * kHeadDim, kHeadDim,
@@ -1190,10 +1246,7 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     dim3 grid(capacity, d.Hkv, 1);
     TcPeers peers{};
     if (gathered) {
-        const int sms = device_sm_count();
-        if (sms <= 0) return B2A_ERR_CUDA;
-        const long long bound = static_cast<long long>(capacity) * d.Hkv;
-        grid = dim3(static_cast<unsigned>(bound < sms ? bound : sms));  // persistent CTAs over the sorted list
+        grid = dim3(static_cast<unsigned>(attention_ctas));
         static bool configured[2][64] = {};
         auto kern = bf16 ? attn_tc_kernel<true, 2> : attn_tc_kernel<false, 2>;
         const int rc = configure_once(kern, configured[bf16]);

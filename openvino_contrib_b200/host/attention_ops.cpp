@@ -17,6 +17,18 @@ int dtype_of(const ov::element::Type& t) {
     }
 }
 
+// integer entry of the node's run-time information, or `fallback`
+int64_t rt_info_int(const ov::Node& node, const char* key, int64_t fallback) {
+    const auto& rt = node.get_rt_info();
+    const auto it = rt.find(key);
+    if (it == rt.end()) return fallback;
+#ifdef B2A_WITH_OPENVINO
+    return it->second.as<int64_t>();
+#else
+    return it->second;
+#endif
+}
+
 void throwIfError(int rc, const std::string& where) {
     if (rc != B2A_OK) ov::throw_ov_exception(where + ": " + b2a_status_string(rc));
 }
@@ -43,8 +55,10 @@ SdpaOp::SdpaOp(const CreationContext& context, const NodeOp& node, IndexCollecti
                IndexCollection&& outputIds)
     : OperationBase(context, node, std::move(inputIds), std::move(outputIds)) {
     const size_t n_in = node.get_input_size();
-    if (n_in < 3 || n_in > 4)
-        ov::throw_ov_exception("ScaledDotProductAttention: 3 or 4 inputs supported (a scale operand must be folded)");
+    if (n_in < 3 || n_in > 5) ov::throw_ov_exception("ScaledDotProductAttention: 3 to 5 inputs expected");
+    if (n_in == 5 && !node.const_scale.has_value())
+        ov::throw_ov_exception("ScaledDotProductAttention: the scale operand must be a Constant (a run-time scale "
+                               "would need a synchronisation inside Execute)");
     const int dt = dtype_of(node.get_input_element_type(0));
     if (dt < 0 || dt == B2A_U8) ov::throw_ov_exception("ScaledDotProductAttention: unsupported precision");
     for (size_t i = 1; i < 3; ++i)
@@ -60,8 +74,14 @@ SdpaOp::SdpaOp(const CreationContext& context, const NodeOp& node, IndexCollecti
     desc_.B = bq; desc_.Hq = hq; desc_.Hkv = hk; desc_.Sq = sq; desc_.Skv = sk; desc_.D = e; desc_.Dv = ev;
     desc_.causal = node.get_causal() ? 1 : 0;
     desc_.scale = 0.f;  // 1/sqrt(E)
+    if (n_in == 5) {
+        desc_.scale = *node.const_scale;
+        if (!(desc_.scale > 0.f)) ov::throw_ov_exception("ScaledDotProductAttention: scale must be positive");
+    }
     desc_.mask_kind = B2A_MASK_NONE;
-    if (n_in == 4 && !node.get_causal()) {
+    // (an attention_mask operand of extent 0 means "no mask", as the op's specification has it)
+    const bool mask_given = n_in >= 4 && !(node.get_input_shape(3).size() == 1 && node.get_input_shape(3)[0] == 0);
+    if (mask_given && !node.get_causal()) {
         has_mask_ = true;
         const auto& mt = node.get_input_element_type(3);
         if (mt == ov::element::boolean || mt == ov::element::u8) {
@@ -94,7 +114,7 @@ WorkbufferRequest SdpaOp::GetWorkBufferRequest() const {
 }
 
 void SdpaOp::Execute(const InferenceRequestContext& context, Inputs in, Outputs out, const Workbuffers& wb) const {
-    if (in.size() < 3 || out.size() != 1) ov::throw_ov_exception("ScaledDotProductAttention: operand count");
+    if (in.size() < (has_mask_ ? 4u : 3u) || out.size() != 1) ov::throw_ov_exception("ScaledDotProductAttention: operand count");
     const void* mask = has_mask_ ? in[3].get() : nullptr;
     void* ws = (workspace_bytes_ > 0 && !wb.mutable_buffers.empty()) ? wb.mutable_buffers[0].get() : nullptr;
     throwIfError(b2a_sdpa_forward(&desc_, in[0].get(), in[1].get(), in[2].get(), mask, out[0].get(), ws,
@@ -132,38 +152,63 @@ PagedAttentionOp::PagedAttentionOp(const CreationContext& context, const NodeOp&
     if (desc_.Hkv <= 0 || desc_.Hq % desc_.Hkv != 0) ov::throw_ov_exception("PagedAttentionExtension: Hq % Hkv != 0");
     desc_.scale = node.const_scale.value_or(0.f);  // 0 selects 1/sqrt(D)
     desc_.sliding_window = node.const_sliding_window.value_or(0);
+    if (!(desc_.scale >= 0.f) || desc_.sliding_window < 0)
+        ov::throw_ov_exception("PagedAttentionExtension: scale / sliding_window out of range");
     desc_.num_tokens = static_cast<int>(qs[0]);  // 0 = dynamic: read per step
     desc_.num_seqs = static_cast<int>(node.get_input_shape(5).empty() ? 0 : node.get_input_shape(5)[0]);
-    max_seqs_ = desc_.num_seqs > 0 ? desc_.num_seqs : 256;
-    max_context_len_ = std::max(1, desc_.num_blocks_total * desc_.block_size);
-    has_dynamic_buffer_ = false;
+    const int64_t pool_tokens = std::max<int64_t>(1, static_cast<int64_t>(desc_.num_blocks_total) * desc_.block_size);
+    const int64_t ms = rt_info_int(node, "b2a.max_seqs", desc_.num_seqs > 0 ? desc_.num_seqs : 256);
+    const int64_t mc = rt_info_int(node, "b2a.max_context_len", pool_tokens);
+    const int64_t mp = rt_info_int(node, "b2a.max_prefill_kv_tokens", 0);
+    const int64_t mt = rt_info_int(node, "b2a.max_step_tokens", mc + ms);
+    if (ms <= 0 || ms > 65535 || mc <= 0 || mc > (1 << 30) || mp < 0 || mp > (1 << 30) || mt < ms || mt > (1 << 30))
+        ov::throw_ov_exception("PagedAttentionExtension: bad capacity in the node's run-time information");
+    max_seqs_ = static_cast<int>(ms);
+    max_context_len_ = static_cast<int>(mc);
+    max_step_tokens_ = static_cast<int>(mt);
+    max_prefill_kv_tokens_ = static_cast<int>((mp + 127) / 128 * 128);
     workspace_bytes_ = WorkspaceBound();
 }
 
-void PagedAttentionOp::SetCapacity(int max_seqs, int max_context_len, int max_prefill_kv_tokens) {
-    if (max_seqs <= 0 || max_context_len <= 0 || max_prefill_kv_tokens < 0)
-        ov::throw_ov_exception("PagedAttentionExtension: bad capacity");
-    max_seqs_ = max_seqs;
-    max_context_len_ = max_context_len;
-    max_prefill_kv_tokens_ = max_prefill_kv_tokens;
-    workspace_bytes_ = WorkspaceBound();
-}
-
-void PagedAttentionOp::SetStepHints(int32_t prefill_row_blocks, int32_t prefill_kv_tokens) {
-    hint_row_blocks_ = prefill_row_blocks > 0 ? prefill_row_blocks : 0;
-    hint_kv_tokens_ = prefill_kv_tokens > 0 && prefill_kv_tokens <= max_prefill_kv_tokens_ ? prefill_kv_tokens : 0;
+b2a_paged_desc PagedAttentionOp::StepDesc(int num_tokens, int num_seqs, const AttentionStepHints& hints) const {
+    if (num_seqs > max_seqs_) ov::throw_ov_exception("PagedAttentionExtension: more sequences than the capacity");
+    if (num_tokens > max_step_tokens())
+        ov::throw_ov_exception("PagedAttentionExtension: more tokens in one step than the capacity");
+    if (num_tokens < num_seqs) ov::throw_ov_exception("PagedAttentionExtension: a scheduled sequence without a token");
+    b2a_paged_desc d = desc_;
+    d.num_tokens = num_tokens;
+    d.num_seqs = num_seqs;
+    d.max_context_len = max_context_len_;
+    // every scheduled sequence has at least one token, so no sequence has more than this many
+    d.max_q_len = num_tokens - num_seqs + 1;
+    d.prefill_row_blocks = 0;
+    d.prefill_kv_tokens = 0;
+    if (d.max_q_len >= 2) {
+        // The work list is reserved for the bound tokens/128 + sequences; a hint can only tighten it.  The scratch
+        // of de-quantised contexts is reserved for max_prefill_kv_tokens; a step that says it needs more (or says
+        // nothing when nothing is reserved) de-quantises inside the prefill kernel instead.
+        const int32_t rb_bound = num_tokens / 128 + num_seqs;
+        if (hints.prefill_row_blocks > 0 && hints.prefill_row_blocks <= rb_bound) d.prefill_row_blocks = hints.prefill_row_blocks;
+        if (hints.prefill_kv_tokens > 0)
+            d.prefill_kv_tokens = hints.prefill_kv_tokens <= max_prefill_kv_tokens_ ? hints.prefill_kv_tokens : 0;
+        else
+            d.prefill_kv_tokens = max_prefill_kv_tokens_;  // unknown: the whole reserve (the device lays it out)
+    }
+    return d;
 }
 
 size_t PagedAttentionOp::WorkspaceBound() const {
-    // The split plan depends on the live sequence count, so take the largest request over 1..max_seqs.
+    // Largest request over every step the capacity admits.  The decode partials depend on the live sequence count
+    // (the split plan does), so take the maximum over 1..max_seqs; the prefill work list and scratch are largest
+    // for the largest token count, no hints (hints only tighten) and the whole scratch reserve.
     size_t worst = 16;
     for (int n = 1; n <= max_seqs_; ++n) {
         b2a_paged_desc d = desc_;
         d.num_seqs = n;
-        // a mixed step: the decode partials for n sequences plus the prefill work list for the token capacity
-        d.num_tokens = max_context_len_ + max_seqs_;
+        d.num_tokens = max_step_tokens();
         d.max_context_len = max_context_len_;
         d.max_q_len = 2;
+        d.prefill_row_blocks = 0;
         d.prefill_kv_tokens = max_prefill_kv_tokens_;
         size_t bytes = 0;
         throwIfError(b2a_paged_workspace_bytes(&d, 0, &bytes), "b2a_paged_workspace_bytes");
@@ -183,19 +228,13 @@ WorkbufferRequest PagedAttentionOp::GetWorkBufferRequest() const {
 void PagedAttentionOp::Execute(const InferenceRequestContext& context, Inputs in, Outputs out,
                                const Workbuffers& wb) const {
     if (in.size() < 11 || out.size() < 1) ov::throw_ov_exception("PagedAttentionExtension: operand count");
-    b2a_paged_desc d = desc_;
     // live extents: dynamic shapes recorded for this request win over the static ones
+    int num_tokens = desc_.num_tokens, num_seqs = desc_.num_seqs;
     const auto& dyn = context.getDynamicBufferContext();
-    if (auto s = dyn.getShape(input_ids_.at(0).GetId())) d.num_tokens = static_cast<int>(s->at(0));
-    if (auto s = dyn.getShape(input_ids_.at(5).GetId())) d.num_seqs = static_cast<int>(s->at(0));
-    if (d.num_tokens <= 0 || d.num_seqs <= 0) return;  // an empty step
-    if (d.num_seqs > max_seqs_) ov::throw_ov_exception("PagedAttentionExtension: more sequences than the capacity");
-    if (d.num_tokens > max_context_len_ + max_seqs_)
-        ov::throw_ov_exception("PagedAttentionExtension: more tokens in one step than the capacity");
-    d.max_context_len = max_context_len_;
-    d.max_q_len = d.num_tokens == d.num_seqs ? 1 : d.num_tokens - d.num_seqs + 1;
-    d.prefill_row_blocks = hint_row_blocks_;
-    d.prefill_kv_tokens = hint_kv_tokens_;
+    if (auto s = dyn.getShape(input_ids_.at(0).GetId())) num_tokens = static_cast<int>(s->at(0));
+    if (auto s = dyn.getShape(input_ids_.at(5).GetId())) num_seqs = static_cast<int>(s->at(0));
+    if (num_tokens <= 0 || num_seqs <= 0) return;  // an empty step
+    const b2a_paged_desc d = StepDesc(num_tokens, num_seqs, context.getAttentionStepHints());
     if (wb.mutable_buffers.size() < 2) ov::throw_ov_exception("PagedAttentionExtension: work buffers missing");
     auto stream = context.getThreadContext().stream().get();
     auto* status = static_cast<int32_t*>(wb.mutable_buffers[1].get());

@@ -13,9 +13,10 @@
 namespace ov {
 namespace nvidia_gpu {
 
-// ov::op::v13::ScaledDotProductAttention: inputs query, key, value[, attention_mask]; attribute causal.
-// A fifth (scale) operand is not accepted: it is a device scalar at run time and reading it would need a
-// synchronisation inside Execute; constant-fold it into the query or leave it to the default 1/sqrt(E).
+// ov::op::v13::ScaledDotProductAttention: inputs query, key, value[, attention_mask[, scale]]; attribute causal.
+// The scale operand is accepted when its producer is a Constant (its value is read at construction, the way the
+// reference's operations read constant operands); a scale computed at run time is refused: it is a device scalar
+// and reading it would need a synchronisation inside Execute.
 class SdpaOp : public OperationBase {
 public:
     using NodeOp = ov::op::v13::ScaledDotProductAttention;
@@ -33,12 +34,20 @@ private:
 };
 
 // PagedAttentionExtension.  The constructor depends only on what is static for a compiled model: head counts,
-// head size, block size, element types and the capacity maxima (sequences per step, context length).  The live
-// token / sequence counts of a step come from the request's DynamicBufferContext when the operand shapes are
-// dynamic, so one instance serves every step of a continuous-batching loop and never has to be re-created per
-// shape the way DynamicOperation does (modules/nvidia_plugin/src/cuda_dynamic_operation.cpp:420-528).
+// head size, block size, element types and the capacity maxima.  The live token / sequence counts of a step come
+// from the request's DynamicBufferContext when the operand shapes are dynamic, so one instance serves every step of
+// a continuous-batching loop and never has to be re-created per shape the way DynamicOperation does
+// (modules/nvidia_plugin/src/cuda_dynamic_operation.cpp:420-528).
+// Nothing about the object changes after construction (operation objects are shared by concurrent requests,
+// modules/nvidia_plugin/src/cuda_operation_base.hpp:41-44):
+//   - capacity (grids and work buffers are sized for it) comes from the node's run-time information, keys
+//     "b2a.max_seqs", "b2a.max_context_len", "b2a.max_step_tokens", "b2a.max_prefill_kv_tokens"; defaults: the
+//     static operand shapes, the pool size, one full context plus a token per sequence, and no scratch for
+//     de-quantised prefill contexts;
+//   - what the scheduler knows about one step (AttentionStepHints) comes with the request context.  Without hints a
+//     step with multi-token sequences is sized by the capacity, so a captured graph replays whatever the step holds.
 // Operands 3 and 4 (the caches) are updated in place: they must be bound to device-resident pool memory
-// (the KvBlockManager's pool), not uploaded per inference like an ordinary Parameter
+// (KvPoolState), not uploaded per inference like an ordinary Parameter
 // (modules/nvidia_plugin/src/ops/parameter.cpp:24-33).
 class PagedAttentionOp : public OperationBase {
 public:
@@ -49,20 +58,18 @@ public:
                  const Workbuffers& workbuffers) const override;
     CudaGraphCompatibility GetCudaGraphCompatibilityImpl() const override { return CudaGraphCompatibility::FULL; }
     WorkbufferRequest GetWorkBufferRequest() const override;
-    // Capacity the grids and the workspace are sized for; defaults to the static operand shapes.
-    // max_prefill_kv_tokens > 0 also reserves the f16 scratch that lets a step de-quantise the contexts of its
-    // multi-token sequences once (up to that many context tokens, each sequence rounded up to 128).
-    void SetCapacity(int max_seqs, int max_context_len, int max_prefill_kv_tokens = 0);
-    // What the scheduler knows about the next step (KvBlockManager::StepTables carries both); zeros = unknown.
-    // Hints beyond the reserved capacity are ignored.
-    void SetStepHints(int32_t prefill_row_blocks, int32_t prefill_kv_tokens);
     const b2a_paged_desc& desc() const { return desc_; }
+    int max_seqs() const { return max_seqs_; }
+    int max_context_len() const { return max_context_len_; }
+    int max_step_tokens() const { return max_step_tokens_; }
+    // The descriptor Execute would launch for a step of these extents and hints (the checks Execute makes, without
+    // the launch): what the capacity tests compare the work-buffer request against.
+    b2a_paged_desc StepDesc(int num_tokens, int num_seqs, const AttentionStepHints& hints) const;
 
 private:
     size_t WorkspaceBound() const;
     b2a_paged_desc desc_{};  // num_seqs / num_tokens hold the static extents (0 = dynamic)
-    int max_seqs_ = 0, max_context_len_ = 0, max_prefill_kv_tokens_ = 0;
-    int32_t hint_row_blocks_ = 0, hint_kv_tokens_ = 0;
+    int max_seqs_ = 0, max_context_len_ = 0, max_step_tokens_ = 0, max_prefill_kv_tokens_ = 0;
     size_t workspace_bytes_ = 0;
 };
 

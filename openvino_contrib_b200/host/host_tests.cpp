@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "attention_ops.hpp"
+#include "host_pipeline.hpp"
 #include "kv_block_manager.hpp"
 
 using namespace ov::nvidia_gpu;
@@ -81,6 +82,88 @@ void test_block_manager() {
     int64_t unknown[1] = {9};
     CHECK(m.schedule_step(unknown, ql, 1, t) == B2A_ERR_NOT_FOUND);
     CHECK(m.free_sequence(1) && m.free_blocks() == 7 && !m.free_sequence(1));
+}
+
+std::shared_ptr<ov::op::PagedAttentionExtension> paged_node(int Hq, int Hkv, int D, int bs, int nblocks) {
+    auto node = std::make_shared<ov::op::PagedAttentionExtension>();
+    const auto z = [](int x) { return static_cast<size_t>(x); };
+    node->add_input(ov::element::bf16, {0, z(Hq * D)});
+    node->add_input(ov::element::bf16, {0, z(Hkv * D)});
+    node->add_input(ov::element::bf16, {0, z(Hkv * D)});
+    node->add_input(ov::element::u8, {z(nblocks), z(Hkv), z(bs), z(D + 4)});
+    node->add_input(ov::element::u8, {z(nblocks), z(Hkv), z(bs), z(D + 4)});
+    for (int i = 0; i < 4; ++i) node->add_input(ov::element::i32, {0});
+    node->add_input(ov::element::f32, {});
+    node->add_input(ov::element::i32, {});
+    node->add_output(ov::element::bf16, {0, z(Hq * D)});
+    return node;
+}
+
+// The work-buffer request must cover every step the capacity admits.  Walks the edges: every sequence count with
+// the longest contexts, the largest token count, hints present, absent, too large - and compares the request with
+// what the library asks for the descriptor Execute would launch.  No device needed.
+void test_paged_op_capacity_edges() {
+    CreationContext cc{CUDA::Device{0}, false, /*set_current=*/false};
+    const int Hq = 32, Hkv = 8, D = 128, bs = 16;
+    for (int reserve : {0, 4096}) {
+        auto node = paged_node(Hq, Hkv, D, bs, 4096);
+        node->get_rt_info()["b2a.max_seqs"] = 48;
+        node->get_rt_info()["b2a.max_context_len"] = 8192;
+        node->get_rt_info()["b2a.max_prefill_kv_tokens"] = reserve;
+        auto base = OperationRegistry::getInstance().createOperation(cc, node, ids({0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10}), ids({11}));
+        auto op = std::dynamic_pointer_cast<const PagedAttentionOp>(base);
+        CHECK(op != nullptr);
+        const size_t have = op->GetWorkBufferRequest().mutable_sizes.at(0);
+        size_t largest = 0;
+        for (int n = 1; n <= op->max_seqs(); ++n)
+            for (int tokens : {n, n + 1, n + 127, n + 1000, op->max_step_tokens()})
+                for (AttentionStepHints h : {AttentionStepHints{}, AttentionStepHints{1, 128}, AttentionStepHints{9, 4096},
+                                             AttentionStepHints{1 << 20, 1 << 20}}) {
+                    const b2a_paged_desc d = op->StepDesc(tokens, n, h);
+                    CHECK(d.max_q_len == tokens - n + 1);
+                    CHECK(d.prefill_kv_tokens <= reserve);                  // never beyond the reserve
+                    CHECK(d.prefill_row_blocks <= tokens / 128 + n);        // a hint can only tighten
+                    size_t need = 0;
+                    CHECK(b2a_paged_workspace_bytes(&d, 0, &need) == B2A_OK);
+                    CHECK(need <= have);
+                    largest = std::max(largest, need);
+                }
+        std::printf("  reserve %d: request %zu bytes, largest step %zu bytes\n", reserve, have, largest);
+        CHECK(largest * 2 > have);  // and the request is not wildly more than the worst step
+        // beyond the capacity: refused, as an exception (how the plugin reports an unusable request)
+        for (auto bad : {std::pair<int, int>{op->max_step_tokens() + 1, 4}, std::pair<int, int>{60, 49}, std::pair<int, int>{3, 4}}) {
+            bool threw = false;
+            try {
+                op->StepDesc(bad.first, bad.second, {});
+            } catch (const std::exception&) {
+                threw = true;
+            }
+            CHECK(threw);
+        }
+    }
+}
+
+void test_sdpa_scale_operand() {
+    CreationContext cc{CUDA::Device{0}, false, /*set_current=*/false};
+    auto make = [](bool constant_scale) {
+        auto node = std::make_shared<ov::op::v13::ScaledDotProductAttention>(false);
+        for (int i = 0; i < 3; ++i) node->add_input(ov::element::f16, {1, 4, 64, 128});
+        node->add_input(ov::element::f16, {0});  // "no mask"
+        node->add_input(ov::element::f16, {});   // scale
+        node->add_output(ov::element::f16, {1, 4, 64, 128});
+        if (constant_scale) node->const_scale = 0.25f;
+        return node;
+    };
+    auto op = std::dynamic_pointer_cast<SdpaOp>(
+        OperationRegistry::getInstance().createOperation(cc, make(true), ids({0, 1, 2, 3, 4}), ids({5})));
+    CHECK(op != nullptr && op->desc().scale == 0.25f && op->desc().mask_kind == B2A_MASK_NONE);
+    bool threw = false;
+    try {
+        OperationRegistry::getInstance().createOperation(cc, make(false), ids({0, 1, 2, 3, 4}), ids({5}));
+    } catch (const std::exception&) {
+        threw = true;  // a scale that is only known at run time
+    }
+    CHECK(threw);
 }
 
 // ---- GPU tests ------------------------------------------------------------------------------------------
@@ -261,10 +344,13 @@ void test_paged_op_decode_with_block_manager() {
     node->add_input(ov::element::f32, {});
     node->add_input(ov::element::i32, {});
     node->add_output(ov::element::f16, {0, static_cast<size_t>(Hq * D)});
+    // capacity: part of the compiled model, carried by the node (room to de-quantise prefill contexts once)
+    node->get_rt_info()["b2a.max_seqs"] = 4;
+    node->get_rt_info()["b2a.max_context_len"] = nblocks * bs / 2;
+    node->get_rt_info()["b2a.max_prefill_kv_tokens"] = 512;
     auto base = OperationRegistry::getInstance().createOperation(cc, node, ids({0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10}), ids({11}));
-    auto op = std::dynamic_pointer_cast<PagedAttentionOp>(base);
+    auto op = std::dynamic_pointer_cast<const PagedAttentionOp>(base);  // const: nothing about it changes from here on
     CHECK(op != nullptr);
-    op->SetCapacity(4, nblocks * bs / 2, /*max_prefill_kv_tokens=*/512);  // room to de-quantise prefill contexts once
     const auto req = op->GetWorkBufferRequest();
     CHECK(req.mutable_sizes.size() == 2);
     DevBuf<uint8_t> ws(req.mutable_sizes[0]), st(req.mutable_sizes[1]);
@@ -295,7 +381,9 @@ void test_paged_op_decode_with_block_manager() {
         CHECK(mgr.schedule_step(seq_ids, step == 0 ? prefill : one, nseq, t) == B2A_OK);
         const int ntok = t.num_tokens;
         if (step == 0) CHECK(t.prefill_row_blocks == 3 && t.prefill_kv_tokens == 3 * 128);
-        op->SetStepHints(t.prefill_row_blocks, t.prefill_kv_tokens);  // what the scheduler knows about this step
+        // what the scheduler knows about this step travels with the request; the last step passes nothing and is
+        // sized by the capacity
+        ctx.setAttentionStepHints(step < 2 ? AttentionStepHints{t.prefill_row_blocks, t.prefill_kv_tokens} : AttentionStepHints{});
         std::vector<uint16_t> q(static_cast<size_t>(max_tok) * Hq * D, 0), k(static_cast<size_t>(max_tok) * Hkv * D, 0),
             v(static_cast<size_t>(max_tok) * Hkv * D, 0);
         for (size_t i = 0; i < static_cast<size_t>(ntok) * Hq * D; ++i) q[i] = f2h(nd(rng));
@@ -385,12 +473,47 @@ void test_paged_op_decode_with_block_manager() {
     cudaGraphExecDestroy(exec);
 }
 
+// Host tensors in, host tensor out, through HostSdpaRunner (upload / SdpaOp::Execute / download per piece on three
+// streams), against the CPU loop; two runs in a row (the second finds the device tensors in use by the first).
+void test_host_pipeline() {
+    const int B = 2, Hq = 4, Hkv = 2, S = 48, D = 64;
+    HostSdpaRunner runner(B2A_F32, B, Hq, Hkv, S, S, D, /*causal=*/true, /*device=*/0, /*kv_heads_per_piece=*/1);
+    CHECK(runner.pieces() == B * Hkv);
+    const size_t nq = static_cast<size_t>(B) * Hq * S * D, nkv = static_cast<size_t>(B) * Hkv * S * D;
+    float *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
+    CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&q), nq * 4));
+    CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&k), nkv * 4));
+    CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&v), nkv * 4));
+    CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&o), nq * 4));
+    std::mt19937 rng(11);
+    std::normal_distribution<float> nd;
+    cudaStream_t s{};
+    CUDA_OK(cudaStreamCreate(&s));
+    for (int run = 0; run < 3; ++run) {  // plain calls, then the captured step (same host tensors, new contents)
+        for (size_t i = 0; i < nq; ++i) q[i] = nd(rng);
+        for (size_t i = 0; i < nkv; ++i) { k[i] = nd(rng); v[i] = nd(rng); }
+        runner.Run(q, k, v, o, s);
+        CUDA_OK(cudaStreamSynchronize(s));
+        std::vector<float> qv(q, q + nq), kv(k, k + nkv), vv(v, v + nkv), ref(nq);
+        cpu_sdpa(qv, kv, vv, ref, B, Hq, Hkv, S, S, D, true);
+        float worst = 0.f;
+        for (size_t i = 0; i < nq; ++i) worst = std::max(worst, std::fabs(o[i] - ref[i]));
+        std::printf("  host pipeline run %d: %d pieces, graph %d, max|diff|=%g\n", run, runner.pieces(), runner.replaying(), worst);
+        CHECK(worst < 2e-5f);
+        CHECK(runner.replaying() == (run >= 1));
+    }
+    cudaStreamDestroy(s);
+    cudaFreeHost(q); cudaFreeHost(k); cudaFreeHost(v); cudaFreeHost(o);
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
     const bool cpu_only = argc > 1 && std::strcmp(argv[1], "--cpu") == 0;
     RUN(test_registry);
     RUN(test_block_manager);
+    RUN(test_paged_op_capacity_edges);
+    RUN(test_sdpa_scale_operand);
     if (!cpu_only) {
         int n = 0;
         if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -401,6 +524,7 @@ int main(int argc, char** argv) {
         RUN(test_sdpa_op_graph_capture);
         RUN(test_sdpa_op_rejects);
         RUN(test_paged_op_decode_with_block_manager);
+        RUN(test_host_pipeline);
     }
     std::printf("%d test(s), %d failed\n", g_run, g_failed);
     return g_failed ? 1 : 0;

@@ -5,6 +5,7 @@
 //   OperationRegistry, OPERATION_REGISTER              modules/nvidia_plugin/src/cuda_operation_registry.hpp:48-143
 //   CreationContext                                    modules/nvidia_plugin/src/cuda_creation_context.hpp:16-27
 //   InferenceRequestContext::getThreadContext          modules/nvidia_plugin/src/cuda_inference_request_context.hpp:22-102
+//     (+ one accessor the plugin's class has to gain: getAttentionStepHints, see AttentionStepHints below)
 //   ThreadContext::stream                              modules/nvidia_plugin/src/cuda_thread_context.hpp:14-31
 //   WorkbufferRequest / Workbuffers / WorkbufferIds    modules/nvidia_plugin/src/memory_manager/cuda_workbuffers.hpp:18-54
 //   CUDA::DevicePointer                                modules/nvidia_plugin/src/cuda/device_pointers.hpp:21-43
@@ -116,8 +117,14 @@ public:
         out_types_.push_back(t);
         out_shapes_.push_back(s);
     }
+    // Run-time information attached to the node by whoever built the model (ov::Node::get_rt_info; the real map
+    // holds ov::Any values - the operators only read integers from it, through rt_info_int in attention_ops.cpp).
+    using RTMap = std::map<std::string, int64_t>;
+    RTMap& get_rt_info() { return rt_info_; }
+    const RTMap& get_rt_info() const { return rt_info_; }
 
 private:
+    RTMap rt_info_;
     std::string name_;
     std::vector<Shape> in_shapes_, out_shapes_;
     std::vector<element::Type> in_types_, out_types_;
@@ -134,6 +141,9 @@ public:
         return info;
     }
     bool get_causal() const { return causal_; }
+    // Value of the scale operand (input 4) when its producer is a Constant, which is how exported models carry a
+    // non-default scale; an operator reads it once, at construction.
+    std::optional<float> const_scale;
 
 private:
     bool causal_;
@@ -242,7 +252,9 @@ struct WorkbufferIds {
 
 class CreationContext {
 public:
-    explicit CreationContext(CUDA::Device d, bool opBenchOption) : device_(d.setCurrent()), bench_(opBenchOption) {}
+    // (set_current = false: the shim's own addition, for tests that build operations on a host without a GPU)
+    explicit CreationContext(CUDA::Device d, bool opBenchOption, bool set_current = true)
+        : device_(set_current ? d.setCurrent() : d), bench_(opBenchOption) {}
     CUDA::Device device() const { return device_; }
     bool opBenchOption() const noexcept { return bench_; }
 
@@ -277,16 +289,28 @@ private:
     std::map<BufferID, Shape> shapes_;
 };
 
+// What the scheduler that built a continuous-batching step knows about it and the device does not have to find out
+// (b2a_paged_desc.prefill_row_blocks / prefill_kv_tokens; zeros = unknown).  It belongs to ONE inference request,
+// like the dynamic shapes: operation objects are shared by concurrent requests and Execute is const, so per-step
+// facts travel in the request context, never in the operation.
+struct AttentionStepHints {
+    int32_t prefill_row_blocks = 0;
+    int32_t prefill_kv_tokens = 0;
+};
+
 class InferenceRequestContext {
 public:
     explicit InferenceRequestContext(const ThreadContext& tc) : tc_(tc) {}
     const ThreadContext& getThreadContext() const noexcept { return tc_; }
     DynamicBufferContext& getDynamicBufferContext() { return dyn_; }
     const DynamicBufferContext& getDynamicBufferContext() const { return dyn_; }
+    void setAttentionStepHints(const AttentionStepHints& h) { hints_ = h; }
+    const AttentionStepHints& getAttentionStepHints() const noexcept { return hints_; }
 
 private:
     const ThreadContext& tc_;
     DynamicBufferContext dyn_;
+    AttentionStepHints hints_;
 };
 
 enum class CudaGraphCompatibility { NONE, FULL, SPECIAL };

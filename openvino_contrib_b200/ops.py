@@ -125,47 +125,57 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[
 
 
 class HostSdpaPipeline:
-    """SDPA on HOST tensors (pinned memory), pipelined over the batch dimension.
+    """SDPA on HOST tensors (pinned memory) through the C++ ``HostSdpaRunner``.
 
-    What a plugin does for a model whose inputs and outputs live in host memory (``ParameterOp`` uploads, ``ResultOp``
-    downloads, modules/nvidia_plugin/src/ops/parameter.cpp:24-33 and result.cpp) - except that here the upload of
-    batch entry b+1, the kernel on entry b and the download of entry b-1 run on three streams at the same time, so
-    a step costs about the larger of the two copy directions instead of their sum plus the kernel.
-    Device buffers are allocated once, for the shapes given at construction.
+    What a plugin does for a model whose inputs and outputs live in host memory (``ParameterOp`` uploads,
+    ``ResultOp`` downloads, modules/nvidia_plugin/src/ops/parameter.cpp:24-33 and result.cpp:28-43) - except that
+    the problem is cut into pieces of a few KV heads of one batch entry and the upload of piece i+1, ``SdpaOp::Execute`` on
+    piece i and the download of piece i-1 run on three streams at the same time, so a step costs about the longer
+    of the two copy directions instead of their sum plus the kernel.  The C++ operator is created once, through the
+    operation registry; device tensors are allocated once, for the shapes given at construction.
     """
 
-    def __init__(self, b: int, hq: int, hkv: int, sq: int, skv: int, d: int, dtype: torch.dtype, device="cuda"):
+    def __init__(self, b: int, hq: int, hkv: int, sq: int, skv: int, d: int, dtype: torch.dtype, causal: bool = False,
+                 kv_heads_per_piece: int = 0):
+        self._lib = _lib.load()
+        self._h = C.c_void_p()
         self.shape_q, self.shape_kv, self.dtype = (b, hq, sq, d), (b, hkv, skv, d), dtype
-        mk = lambda shape: torch.empty(shape, dtype=dtype, device=device)
-        self.q, self.k, self.v, self.o = mk(self.shape_q), mk(self.shape_kv), mk(self.shape_kv), mk(self.shape_q)
-        self.up, self.down = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
-        self.ev_in = [torch.cuda.Event() for _ in range(b)]
-        self.ev_done = [torch.cuda.Event() for _ in range(b)]
+        check(self._lib.b2a_host_sdpa_create(_dtype_code(dtype), b, hq, hkv, sq, skv, d, int(bool(causal)),
+                                             int(kv_heads_per_piece), C.byref(self._h)), "b2a_host_sdpa_create")
+        self.pieces = self._lib.b2a_host_sdpa_pieces(self._h)
 
-    def __call__(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, out_host: torch.Tensor,
-                 causal: bool = False, scale: Optional[float] = None) -> torch.Tensor:
-        """Enqueues the whole step; ``out_host`` is complete when the current stream has been synchronised."""
-        for t in (q_host, k_host, v_host, out_host):
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.b2a_host_sdpa_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def __call__(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+                 out_host: torch.Tensor) -> torch.Tensor:
+        """Enqueues the whole step behind the current stream's work; ``out_host`` is complete when the current stream
+        has been synchronised."""
+        for t, shape in ((q_host, self.shape_q), (k_host, self.shape_kv), (v_host, self.shape_kv), (out_host, self.shape_q)):
             if t.is_cuda or not t.is_pinned():
                 raise ValueError("HostSdpaPipeline takes pinned host tensors")
-        main = torch.cuda.current_stream()
-        self.up.wait_stream(main)    # earlier users of the device buffers are done
-        self.down.wait_stream(main)
-        nb = self.shape_q[0]
-        for b in range(nb):
-            with torch.cuda.stream(self.up):
-                self.q[b].copy_(q_host[b], non_blocking=True)
-                self.k[b].copy_(k_host[b], non_blocking=True)
-                self.v[b].copy_(v_host[b], non_blocking=True)
-                self.ev_in[b].record(self.up)
-            main.wait_event(self.ev_in[b])
-            sdpa(self.q[b:b + 1], self.k[b:b + 1], self.v[b:b + 1], causal=causal, scale=scale, out=self.o[b:b + 1])
-            self.ev_done[b].record(main)
-            with torch.cuda.stream(self.down):
-                self.down.wait_event(self.ev_done[b])
-                out_host[b].copy_(self.o[b], non_blocking=True)
-        main.wait_stream(self.down)
+            if tuple(t.shape) != shape or t.dtype != self.dtype or not t.is_contiguous():
+                raise ValueError(f"HostSdpaPipeline was built for dense {self.dtype} tensors of shape {shape}")
+        check(self._lib.b2a_host_sdpa_run(self._h, q_host.data_ptr(), k_host.data_ptr(), v_host.data_ptr(),
+                                          out_host.data_ptr(), _stream_ptr(None)), "b2a_host_sdpa_run")
         return out_host
+
+
+def _host_scalar(x, what: str):
+    """A constant operand: a Python number or a host tensor.  A device tensor is refused - reading it would make
+    ``Execute`` wait for the device, which an operation that reports full CUDA-graph compatibility must not do."""
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        if x.is_cuda:
+            raise B2AError(7, f"{what} must be a constant (host value), not a device tensor")
+        return x.item()
+    return x
 
 
 class SdpaOp:
@@ -191,10 +201,7 @@ class SdpaOp:
         if not 3 <= len(inputs) <= 5 or len(outputs) != 1:
             raise ValueError("ScaledDotProductAttention takes 3 to 5 inputs and 1 output")
         mask = inputs[3] if len(inputs) > 3 else None
-        scale = None
-        if len(inputs) > 4 and inputs[4] is not None:
-            s = inputs[4]
-            scale = float(s.item()) if isinstance(s, torch.Tensor) else float(s)
+        scale = _host_scalar(inputs[4], "ScaledDotProductAttention: scale") if len(inputs) > 4 else None
         sdpa(inputs[0], inputs[1], inputs[2], mask, scale, self.causal, out=outputs[0], stream=stream)
 
 
@@ -313,57 +320,91 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
 
 
 class PagedAttentionOp:
-    """Operator-shaped wrapper for ``PagedAttentionExtension``.
+    """Operator-shaped wrapper for ``PagedAttentionExtension`` (the Python twin of the C++ ``PagedAttentionOp``).
 
     ``Execute`` takes the operands in the op's order: query, key, value, key_cache, value_cache, past_lens,
     subsequence_begins, block_indices, block_indices_begins, scale, sliding_window[, alibi_slopes,
     max_context_len].  It first appends key/value to the caches, then attends.  The constructor fixes what is
-    static for a compiled model (head counts, head size, block size, capacity maxima), so one instance serves
-    every step of a continuous-batching loop whatever its token and sequence counts.
+    static for a compiled model - head counts, head size, block size, the capacity maxima, and the scale and
+    sliding window (Constants in an exported model) - so one instance serves every step of a continuous-batching
+    loop whatever its token and sequence counts, and nothing about it changes afterwards: what a scheduler knows
+    about one step is passed to that ``Execute`` call.  ``Execute`` only enqueues: it allocates nothing (the work
+    buffer must be the one ``GetWorkBufferRequest`` asked for) and never waits for the device.
     """
 
     type_name = "PagedAttentionExtension"
 
     def __init__(self, hq: int, hkv: int, d: int, block_size: int = 16, kv_dtype: torch.dtype = torch.uint8,
-                 max_seqs: int = 256, max_context_len: int = 32768):
+                 max_seqs: int = 256, max_context_len: int = 32768, max_prefill_kv_tokens: int = 0,
+                 scale: Optional[float] = None, sliding_window: int = 0, q_dtype: torch.dtype = torch.float16,
+                 max_step_tokens: Optional[int] = None):
         self.hq, self.hkv, self.d, self.block_size, self.kv_dtype = hq, hkv, d, block_size, kv_dtype
-        self.max_seqs, self.max_context_len = max_seqs, max_context_len
-        self._hint_row_blocks = self._hint_kv_tokens = 0
-
-    def SetStepHints(self, prefill_row_blocks: int = 0, prefill_kv_tokens: int = 0) -> None:
-        """What the scheduler knows about the next step (``KvBlockManager`` reports both); zeros = unknown."""
-        self._hint_row_blocks, self._hint_kv_tokens = max(0, int(prefill_row_blocks)), max(0, int(prefill_kv_tokens))
+        self.max_seqs, self.max_context_len = int(max_seqs), int(max_context_len)
+        # tokens of one step: by default one full context plus a token for every other sequence
+        self.max_step_tokens = int(max_step_tokens) if max_step_tokens else self.max_context_len + self.max_seqs
+        self.max_prefill_kv_tokens = (int(max_prefill_kv_tokens) + 127) // 128 * 128
+        self.scale, self.sliding_window, self.q_dtype = scale, int(sliding_window), q_dtype
+        self._workspace_bytes = self._workspace_bound()
 
     def GetCudaGraphCompatibility(self) -> str:
         return "FULL"
 
-    def GetWorkBufferRequest(self, q_dtype=torch.float16):
-        cache = PagedKvCache(torch.empty(0), torch.empty(0), self.hkv, self.d, self.d, self.block_size, self.kv_dtype)
-        cache.k = torch.empty((0, self.hkv, 1), dtype=torch.uint8)
-        n = paged_workspace_bytes(q_dtype, cache, self.hq, self.max_seqs, self.max_seqs, self.max_context_len, 1)
-        return {"immutable_sizes": [], "mutable_sizes": [n] if n else []}
+    def _geometry(self) -> "PagedKvCache":
+        return PagedKvCache(torch.empty((0, self.hkv, 1), dtype=torch.uint8), torch.empty(0), self.hkv, self.d, self.d,
+                            self.block_size, self.kv_dtype)
+
+    def _workspace_bound(self) -> int:
+        """Largest request over every step the capacity admits (the split plan depends on the sequence count)."""
+        cache, tokens = self._geometry(), self.max_step_tokens
+        return max(16, max(paged_workspace_bytes(self.q_dtype, cache, self.hq, n, tokens, self.max_context_len, 2, 0,
+                                                 self.max_prefill_kv_tokens) for n in range(1, self.max_seqs + 1)))
+
+    def GetWorkBufferRequest(self):
+        return {"immutable_sizes": [], "mutable_sizes": [self._workspace_bytes]}
+
+    def step_hints(self, num_tokens: int, num_seqs: int, prefill_row_blocks: int = 0, prefill_kv_tokens: int = 0):
+        """The (prefill_row_blocks, prefill_kv_tokens) a step is launched with: a row-block hint can only tighten
+        the reserved bound, a context hint beyond the scratch reserve switches to de-quantising inside the prefill
+        kernel, and no context hint means the whole reserve."""
+        if num_tokens == num_seqs:
+            return 0, 0
+        rb = prefill_row_blocks if 0 < prefill_row_blocks <= num_tokens // 128 + num_seqs else 0
+        if prefill_kv_tokens > 0:
+            kvt = prefill_kv_tokens if prefill_kv_tokens <= self.max_prefill_kv_tokens else 0
+        else:
+            kvt = self.max_prefill_kv_tokens
+        return rb, kvt
 
     def Execute(self, inputs: Sequence, outputs: Sequence[torch.Tensor], workbuffers: Optional[dict] = None,
-                stream=None, status: Optional[torch.Tensor] = None) -> None:
+                stream=None, status: Optional[torch.Tensor] = None, prefill_row_blocks: int = 0,
+                prefill_kv_tokens: int = 0) -> None:
         if len(inputs) < 11 or len(outputs) < 1:
             raise ValueError("PagedAttentionExtension takes at least 11 inputs and 1 output")
         (query, key, value, k_cache, v_cache, past_lens, subsequence_begins, block_indices,
          block_indices_begins, scale, sliding_window) = inputs[:11]
         if len(inputs) > 11 and inputs[11] is not None and getattr(inputs[11], "numel", lambda: 0)() > 0:
             raise B2AError(7, "PagedAttentionOp: alibi slopes")
-        max_ctx = int(inputs[12]) if len(inputs) > 12 and inputs[12] is not None else self.max_context_len
-        cache = PagedKvCache(k_cache, v_cache, self.hkv, self.d, self.d, self.block_size, self.kv_dtype)
+        # operands 9 and 10 are Constants of the model: they must agree with what the operator was built with
+        sc, sw = _host_scalar(scale, "PagedAttentionExtension: scale"), _host_scalar(sliding_window, "sliding_window")
+        if sc is not None and self.scale is not None and abs(float(sc) - self.scale) > 1e-6 * abs(self.scale):
+            raise ValueError("PagedAttentionOp: the scale operand differs from the constant the operator was built with")
+        if sw and int(sw) != self.sliding_window:
+            raise ValueError("PagedAttentionOp: the sliding_window operand differs from the operator's constant")
         num_tokens, num_seqs = query.shape[0], past_lens.shape[0]
-        max_q_len = 1 if num_tokens == num_seqs else max(1, num_tokens - (num_seqs - 1))
+        if num_seqs > self.max_seqs or num_tokens > self.max_step_tokens or num_tokens < num_seqs:
+            raise B2AError(8, "PagedAttentionOp: the step exceeds the capacity the operator was built for")
+        cache = PagedKvCache(k_cache, v_cache, self.hkv, self.d, self.d, self.block_size, self.kv_dtype)
+        max_q_len = num_tokens - num_seqs + 1  # every scheduled sequence has at least one token
+        ws = workbuffers["mutable"][0] if workbuffers and workbuffers.get("mutable") else None
+        if ws is None or ws.numel() * ws.element_size() < self._workspace_bytes:
+            raise B2AError(5, "PagedAttentionOp: pass the work buffer GetWorkBufferRequest() asked for")
+        rb, kvt = self.step_hints(num_tokens, num_seqs, prefill_row_blocks, prefill_kv_tokens)
         paged_kv_store(key, value, cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
                        stream=stream, status=status)
-        ws = workbuffers["mutable"][0] if workbuffers and workbuffers.get("mutable") else None
-        sc = None if scale is None else (float(scale.item()) if isinstance(scale, torch.Tensor) else float(scale))
-        sw = int(sliding_window.item()) if isinstance(sliding_window, torch.Tensor) else int(sliding_window or 0)
         paged_attention(query, cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
-                        self.hq, max_ctx, max_q_len, sc, sw, out=outputs[0], workspace=ws, stream=stream,
-                        status=status, prefill_row_blocks=self._hint_row_blocks,
-                        prefill_kv_tokens=self._hint_kv_tokens)
+                        self.hq, self.max_context_len, max_q_len, self.scale if sc is None else float(sc),
+                        self.sliding_window, out=outputs[0], workspace=ws, stream=stream,
+                        status=status, prefill_row_blocks=rb, prefill_kv_tokens=kvt)
 
 
 # ------------------------------------------------------------------------------------------------------------

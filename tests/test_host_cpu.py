@@ -133,3 +133,29 @@ def test_no_cpu_fallback():
     x = torch.zeros(1, 1, 4, 8)
     with pytest.raises(ValueError):
         sdpa(x, x, x)
+
+
+def test_python_operator_work_buffer_covers_every_step_of_its_capacity(lib):
+    """The Python twin of the C++ capacity test: the operator's work-buffer request is at least what the library
+    asks for any step the capacity admits, with and without a scratch reserve, whatever the hints."""
+    import torch
+    from openvino_contrib_b200 import B2AError, PagedAttentionOp
+    from openvino_contrib_b200.ops import paged_workspace_bytes
+    for reserve in (0, 2048):
+        op = PagedAttentionOp(32, 8, 128, 16, torch.uint8, max_seqs=24, max_context_len=4096,
+                              max_prefill_kv_tokens=reserve, q_dtype=torch.bfloat16)
+        have = op.GetWorkBufferRequest()["mutable_sizes"][0]
+        cache, worst = op._geometry(), 0
+        for n in range(1, op.max_seqs + 1):
+            for tokens in (n, n + 1, n + 500, op.max_step_tokens):
+                for hints in ((0, 0), (3, 384), (1 << 20, 1 << 20)):
+                    rb, kvt = op.step_hints(tokens, n, *hints)
+                    assert kvt <= reserve and rb <= tokens // 128 + n
+                    need = paged_workspace_bytes(torch.bfloat16, cache, 32, n, tokens, op.max_context_len,
+                                                 tokens - n + 1, rb, kvt)
+                    assert need <= have, (reserve, n, tokens, hints)
+                    worst = max(worst, need)
+        assert 2 * worst > have
+    # constants arriving as device tensors would make Execute wait for the device: refused
+    from openvino_contrib_b200.ops import _host_scalar
+    assert _host_scalar(0.5, "x") == 0.5 and _host_scalar(torch.tensor(3), "x") == 3 and _host_scalar(None, "x") is None

@@ -213,12 +213,13 @@ def test_mixed_step_through_the_operator(b2a, dtype):
     q = _round(w.query, dtype)
     ref = opaged.paged_attention_ref(q.float().numpy(), ref_k, ref_v, w.past, w.sb, w.bi, w.bb, hq, hkv, d, bs)
 
-    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=8, max_context_len=1024)
+    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=8, max_context_len=1024, q_dtype=dtype)
+    wb = {"mutable": [torch.empty(n, dtype=torch.uint8, device="cuda") for n in op.GetWorkBufferRequest()["mutable_sizes"]]}
     cache = w.device_cache()
     out = torch.empty(int(w.sb[-1]), hq * d, dtype=dtype, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     op.Execute([q.cuda(), nk.cuda(), nv.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, int(ctx.max())],
-               [out], status=status)
+               [out], workbuffers=wb, status=status)
     assert int(status.item()) == 0
     assert np.array_equal(cache.k.cpu().numpy(), ref_k) and np.array_equal(cache.v.cpu().numpy(), ref_v)
     assert_close(out, ref, dtype)
@@ -417,20 +418,30 @@ def test_config4_mixed_step(b2a):
     opaged.kv_store_ref(new_v, ref_v, w.past, w.sb, w.bi, w.bb, hkv, d, bs)
     q = _round(w.query, torch.bfloat16)
     ref = opaged.paged_attention_ref(q.float().numpy(), ref_k, ref_v, w.past, w.sb, w.bi, w.bb, hq, hkv, d, bs)
-    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=128, max_context_len=4096)
+    # no scratch reserve: the prefill contexts are de-quantised inside the prefill kernel
+    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=128, max_context_len=4096, q_dtype=torch.bfloat16,
+                              max_step_tokens=8 * 1024 + 120)
+    wb = {"mutable": [torch.empty(n, dtype=torch.uint8, device="cuda") for n in op.GetWorkBufferRequest()["mutable_sizes"]]}
     cache = w.device_cache()
     out = torch.empty(int(w.sb[-1]), hq * d, dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     op.Execute([q.cuda(), new_k.cuda(), new_v.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, 4096],
-               [out], status=status)
+               [out], workbuffers=wb, status=status)
     assert int(status.item()) == 0
     assert np.array_equal(cache.k.cpu().numpy(), ref_k) and np.array_equal(cache.v.cpu().numpy(), ref_v)
     assert_close(out, ref, torch.bfloat16)
-    # the same step with the scheduler's hints (contexts de-quantised once): storing the same rows again leaves
-    # the pools as they are, and the output is the same to the bit
-    op.SetStepHints(prefill_row_blocks=8 * 8, prefill_kv_tokens=8 * 1024)
-    out2 = torch.empty_like(out)
-    op.Execute([q.cuda(), new_k.cuda(), new_v.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, 4096],
-               [out2], status=status)
-    assert int(status.item()) == 0
-    assert np.array_equal(cache.k.cpu().numpy(), ref_k) and torch.equal(out2, out)
+    # An operator with a scratch reserve de-quantises the contexts once: with the scheduler's hints for this step,
+    # and with none (the reserve is then laid out on the device).  Storing the same rows again leaves the pools as
+    # they are, and the output is the same to the bit.  A work buffer that is too small is refused, not replaced.
+    op2 = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=128, max_context_len=4096,
+                               max_prefill_kv_tokens=12 * 1024, q_dtype=torch.bfloat16, max_step_tokens=8 * 1024 + 120)
+    with pytest.raises(b2a.B2AError):
+        op2.Execute([q.cuda(), new_k.cuda(), new_v.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, 4096],
+                    [out], workbuffers=wb, status=status)
+    wb2 = {"mutable": [torch.empty(n, dtype=torch.uint8, device="cuda") for n in op2.GetWorkBufferRequest()["mutable_sizes"]]}
+    for hints in (dict(prefill_row_blocks=8 * 8, prefill_kv_tokens=8 * 1024), dict()):
+        out2 = torch.empty_like(out)
+        op2.Execute([q.cuda(), new_k.cuda(), new_v.cuda(), cache.k, cache.v, *w.device_tables(), None, 0, None, 4096],
+                    [out2], workbuffers=wb2, status=status, **hints)
+        assert int(status.item()) == 0
+        assert np.array_equal(cache.k.cpu().numpy(), ref_k) and torch.equal(out2, out)

@@ -197,16 +197,18 @@ def test_config2_full_size_planes_against_oracle(b2a):
 
 
 def test_host_pipeline_matches_device_call(b2a):
-    # host tensors in, host tensor out, batch entries pipelined on three streams: same bits as the plain call
+    # host tensors in, host tensor out, one piece per (batch entry, KV head) pipelined on three streams through the
+    # C++ operator: same bits as the plain call
     B, hq, hkv, S, D = 3, 8, 2, 384, 128
     gen = torch.Generator().manual_seed(9)
     q = (torch.randn(B, hq, S, D, generator=gen) * 0.5).to(torch.bfloat16).pin_memory()
     k = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16).pin_memory()
     v = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16).pin_memory()
     out = torch.empty(B, hq, S, D, dtype=torch.bfloat16).pin_memory()
-    pipe = b2a.HostSdpaPipeline(B, hq, hkv, S, S, D, torch.bfloat16)
-    for _ in range(2):  # the second call reuses the device buffers behind the first
-        pipe(q, k, v, out, causal=True)
+    pipe = b2a.HostSdpaPipeline(B, hq, hkv, S, S, D, torch.bfloat16, causal=True, kv_heads_per_piece=1)
+    assert pipe.pieces == B * hkv
+    for _ in range(3):  # the second call captures the step into a graph, the third replays it
+        pipe(q, k, v, out)
         torch.cuda.synchronize()
         ref = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), causal=True)
         assert torch.equal(out.cuda(), ref)
