@@ -143,6 +143,20 @@ int b2a_paged_kv_store(const b2a_paged_desc* desc, const void* key, const void* 
                        const int32_t* block_indices, const int32_t* block_indices_begins, int32_t* status,
                        b2a_stream_t stream);
 
+/* b2a_paged_kv_store with the rotary position embedding of the KEY rows fused in: the first rotary_dim values of a key
+ * row at cache position p are rotated in pairs (i, i + rotary_dim/2) by the angle whose cosine and sine are
+ * cos_table[p][i] and sin_table[p][i] (device float32 tables [table_positions][rotary_dim/2]; the "rotate-half" form of
+ * the Llama family), each product and sum one float32 operation rounded to nearest, and the rotated float32 values are
+ * what is quantised.  Values are stored as they are.  No counterpart in the reference: there the rotation reaches the
+ * plugin decomposed into Multiply / Concat / Add nodes and costs a pass over K in memory (src/ops/multiply.cpp:16-43,
+ * src/kernels/concat.cu:16-32); a model hands the un-rotated key projection to this call instead.  A position beyond
+ * the table is reported (B2A_DEV_BAD_LEN) and its row left unwritten. */
+int b2a_paged_kv_store_rope(const b2a_paged_desc* desc, const void* key, const void* value, void* k_cache,
+                            void* v_cache, const int32_t* past_lens, const int32_t* subsequence_begins,
+                            const int32_t* block_indices, const int32_t* block_indices_begins, const float* cos_table,
+                            const float* sin_table, int32_t rotary_dim, int32_t table_positions, int32_t* status,
+                            b2a_stream_t stream);
+
 /* Attention of every query token over its sequence's cache (call after b2a_paged_kv_store of the same step).
  * Counterpart of ReadValue + decomposed SDPA (src/ops/read_value.cpp:31-72 and the SDPA chain above). */
 int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const void* k_cache, const void* v_cache,

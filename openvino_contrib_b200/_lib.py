@@ -44,6 +44,9 @@ SIGNATURES = {
     "b2a_paged_workspace_bytes": (C.c_int, [C.POINTER(PagedDesc), C.c_int, C.POINTER(C.c_size_t)]),
     "b2a_paged_kv_store": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2a_paged_kv_store_rope": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "b2a_paged_attention": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                       C.c_void_p, C.c_void_p]),

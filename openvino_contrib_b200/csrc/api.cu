@@ -202,6 +202,26 @@ int b2a_paged_kv_store(const b2a_paged_desc* desc, const void* key, const void* 
                                  status, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int b2a_paged_kv_store_rope(const b2a_paged_desc* desc, const void* key, const void* value, void* k_cache, void* v_cache,
+                            const int32_t* past_lens, const int32_t* subsequence_begins, const int32_t* block_indices,
+                            const int32_t* block_indices_begins, const float* cos_table, const float* sin_table,
+                            int32_t rotary_dim, int32_t table_positions, int32_t* status, b2a_stream_t stream) {
+    b2a_paged_desc d;
+    const int rc = resolve_paged_desc(desc, d);
+    if (rc != B2A_OK) return rc;
+    if (d.num_tokens == 0 || d.num_seqs == 0) return B2A_OK;
+    if (key == nullptr || value == nullptr || k_cache == nullptr || v_cache == nullptr || past_lens == nullptr ||
+        subsequence_begins == nullptr || block_indices == nullptr || block_indices_begins == nullptr ||
+        cos_table == nullptr || sin_table == nullptr)
+        return B2A_ERR_NULL;
+    if (rotary_dim <= 0 || rotary_dim % 2 != 0 || rotary_dim > d.D || table_positions <= 0) return B2A_ERR_DIM;
+    if (!aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(cos_table, 4) || !aligned(sin_table, 4)) return B2A_ERR_ALIGN;
+    const RopeTables rope{cos_table, sin_table, rotary_dim, table_positions};
+    return paged_kv_store_launch(d, key, value, k_cache, v_cache,
+                                 tables_of(d, past_lens, subsequence_begins, block_indices, block_indices_begins),
+                                 status, reinterpret_cast<cudaStream_t>(stream), &rope);
+}
+
 int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const void* k_cache, const void* v_cache,
                         const int32_t* past_lens, const int32_t* subsequence_begins, const int32_t* block_indices,
                         const int32_t* block_indices_begins, void* out, void* workspace, size_t workspace_bytes,

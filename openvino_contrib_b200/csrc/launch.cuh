@@ -15,8 +15,13 @@ int paged_generic_launch(const b2a_paged_desc& d, const void* query, const void*
                          const PagedTables& t, void* out, int32_t* status, cudaStream_t stream);
 
 // paged_kv_store.cu
+struct RopeTables {  // rotary embedding of the key rows: f32 tables [positions][rotary_dim / 2] in device memory
+    const float* cos;
+    const float* sin;
+    int rotary_dim, positions;
+};
 int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* value, void* k_cache, void* v_cache,
-                          const PagedTables& t, int32_t* status, cudaStream_t stream);
+                          const PagedTables& t, int32_t* status, cudaStream_t stream, const RopeTables* rope = nullptr);
 
 // Head-sharded decode across the GPUs of a node: where the decode kernel delivers a rank's output columns.
 // Every rank owns two full-width staging buffers, flag arrays and counters, all inside one allocation that its peers
@@ -41,6 +46,7 @@ struct PeerPush {
     // done; nobody stores into a rank's buffer for step s before that; the grid's last CTA publishes the step in
     // flags[r][rank] and waits for the other ranks.
     int ll;
+    int receive_in_kernel;             // ll: the decode kernel's CTAs also receive the rows (no second kernel)
     int32_t* group_counters;           // local: one ticket counter per (sequence, KV head), self-resetting
     int32_t* started[kMaxShardWorld];  // [rank]: that rank's array of "rank i has begun step s" (one int per source rank)
     long long wait_ns;                 // bound of every wait on another rank, in nanoseconds of wall-clock time

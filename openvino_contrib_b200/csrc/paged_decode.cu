@@ -584,6 +584,33 @@ __device__ __forceinline__ void send_zero_row_segment(const DecodeParams& p, int
     }
 }
 
+// Receiving side of the low-latency exchange for one output row: poll every 8-byte word of the row in this rank's
+// staging buffer until it carries the step's number (bounded in real time: B2A_DEV_TIMEOUT after push.wait_ns) and
+// write the value pairs to the caller's output.  Two words per load (rows are multiples of 256 bytes).
+__device__ __forceinline__ void receive_row(const PeerPush& push, uint32_t* out, int row, uint32_t epoch, int32_t* status) {
+    const int pairs_per_row = push.row_elems / 2;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(push.staging[push.rank][epoch & 1]) +
+                                                      static_cast<size_t>(row) * pairs_per_row);
+    uint2* dst = reinterpret_cast<uint2*>(out + static_cast<size_t>(row) * pairs_per_row);
+    const long long t0 = global_ns();
+    bool gave_up = false;
+    for (int i = threadIdx.x; i < pairs_per_row / 2; i += blockDim.x) {
+        uint32_t a, ea, b, eb;
+        for (;;) {
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(a), "=r"(ea), "=r"(b), "=r"(eb)
+                         : "l"(src + i)
+                         : "memory");
+            if ((ea == epoch && eb == epoch) || gave_up) break;
+            if (global_ns() - t0 > push.wait_ns) {
+                report(status, B2A_DEV_TIMEOUT);
+                gave_up = true;
+            }
+        }
+        dst[i] = make_uint2(a, b);
+    }
+}
+
 // kMode 0: the CTA leaves its partial in the workspace and paged_decode_merge_kernel follows (single GPU).
 // kMode 1, 2: the whole step of a head shard in this launch (PeerPush).  After its chunk a CTA takes a ticket of its
 // (sequence, KV head); the CTA that gets the last ticket merges the group's partials and delivers the rows to every
@@ -610,8 +637,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) paged_decode_kernel(
             st_release_sys(p.push.started[tid] + p.push.rank, epoch);  // this rank's readers of the previous step are done
         const ChunkState state = decode_chunk<T, NT, kLL, kWarps>(p, smem, nsplit, tok);
         if (tid == 0) s_role = 0;
+        __syncthreads();  // (the role starts cleared for everybody;) every thread's part of the partial is written ...
         if (state == kChunkWorked) {
-            __syncthreads();  // every thread's part of the partial is written ...
             if (tid == 0) {
                 __threadfence();  // ... and, through the barrier, ordered before this thread's ticket
                 int32_t* ctr = p.push.group_counters + seq * p.Hkv + hk;
@@ -640,6 +667,22 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) paged_decode_kernel(
         } else if (kLL && (state == kChunkInvalid || state == kChunkNotRow) && blockIdx.z == 0) {
             if (state == kChunkNotRow && tid == 0) report(p.status, B2A_DEV_BAD_LEN);
             send_zero_row_segment(p, seq, hk, epoch);
+            if (tid == 0) s_role = 1;  // (stands in for the merging CTA of a row that cannot be computed)
+            __syncthreads();
+        }
+        if constexpr (kLL) {
+            // One launch for the whole step: the CTA that delivered the first KV head's part of a row also receives
+            // the row - it waits for the other KV heads' CTAs of this grid and for the other ranks, which never wait
+            // for it, and there are at most as many such CTAs as SMs (the host checks), so every CTA they wait for
+            // finds a place to run.  The last receiver counts the step.
+            if (p.push.receive_in_kernel && hk == 0 && s_role == 1) {
+                receive_row(p.push, static_cast<uint32_t*>(p.out), seq, static_cast<uint32_t>(epoch), p.status);
+                __syncthreads();
+                if (tid == 0 && atomicAdd(p.push.done_counter, 1) == static_cast<int>(gridDim.y) - 1) {
+                    *p.push.done_counter = 0;
+                    *reinterpret_cast<volatile int32_t*>(p.push.step_counter) = epoch;
+                }
+            }
         }
         if constexpr (!kLL) {
             // in place: the grid's last CTA publishes the step on every rank and waits for theirs
@@ -700,35 +743,14 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
     orow[d] = from_f32<T>(l > 0.f ? o / l : 0.f);
 }
 
-// Receiver of the low-latency exchange: one CTA per row polls every 8-byte word of its staging row until it carries
-// this step's number (bounded in real time: B2A_DEV_TIMEOUT after push.wait_ns) and writes the two values to the
-// caller's output.  It is the last kernel of the step, so its last CTA counts the step: the decode kernel before it
-// and this kernel read the same counter value.
-__global__ void __launch_bounds__(256) peer_ll_copy_kernel(const PeerPush push, uint32_t* out, int pairs_per_row,
-                                                            int32_t* status) {
+// Receiver of the low-latency exchange as a kernel of its own, one CTA per row, for steps with more rows than the
+// decode kernel may hold waiting CTAs for.  It is the last kernel of the step, so its last CTA counts the step: the
+// decode kernel before it and this kernel read the same counter value.
+__global__ void __launch_bounds__(256) peer_ll_copy_kernel(const PeerPush push, uint32_t* out, int32_t* status) {
     grid_dependency_wait();  // our own decode kernel (its CTAs read the step counter that this kernel advances)
     grid_launch_dependents();
     const uint32_t epoch = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(push.step_counter) + 1);
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(push.staging[push.rank][epoch & 1]) +
-                                                      static_cast<size_t>(blockIdx.x) * pairs_per_row);
-    uint2* dst = reinterpret_cast<uint2*>(out + static_cast<size_t>(blockIdx.x) * pairs_per_row);
-    const long long t0 = global_ns();
-    bool gave_up = false;
-    for (int i = threadIdx.x; i < pairs_per_row / 2; i += blockDim.x) {  // two words per load (rows are multiples of 256 bytes)
-        uint32_t a, ea, b, eb;
-        for (;;) {
-            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(a), "=r"(ea), "=r"(b), "=r"(eb)
-                         : "l"(src + i)
-                         : "memory");
-            if ((ea == epoch && eb == epoch) || gave_up) break;
-            if (global_ns() - t0 > push.wait_ns) {
-                report(status, B2A_DEV_TIMEOUT);
-                gave_up = true;
-            }
-        }
-        dst[i] = make_uint2(a, b);
-    }
+    receive_row(push, out, blockIdx.x, epoch, status);
     __syncthreads();
     if (threadIdx.x == 0) {
         if (atomicAdd(push.done_counter, 1) == static_cast<int>(gridDim.x) - 1) {
@@ -771,10 +793,10 @@ int launch_t(const DecodeParams& p, int num_seqs, cudaStream_t stream) {
     if (p.push.world > 0) {
         if (!p.push.ll) return launch_kernel<T, NT, 2>(p, num_seqs, stream);
         const int rc = launch_kernel<T, NT, 1>(p, num_seqs, stream);
-        if (rc != B2A_OK) return rc;
+        if (rc != B2A_OK || p.push.receive_in_kernel) return rc;
         // decode steps carry one token per sequence: row index == sequence index == token index
         return launch_overlapped(peer_ll_copy_kernel, dim3(num_seqs), dim3(256), 0, stream, p.push,
-                                 static_cast<uint32_t*>(p.out), p.push.row_elems / 2, p.status) == cudaSuccess
+                                 static_cast<uint32_t*>(p.out), p.status) == cudaSuccess
                    ? B2A_OK
                    : B2A_ERR_CUDA;
     }
@@ -837,6 +859,8 @@ int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const v
                         cudaStream_t stream, const PeerPush* push, cudaEvent_t beside_predecessor) {
     DecodeParams p{};
     if (push != nullptr) p.push = *push;
+    // the rows are received by CTAs of the decode kernel itself while there are no more rows than SMs
+    if (push != nullptr && p.push.ll) p.push.receive_in_kernel = d.num_seqs <= device_sm_count() ? 1 : 0;
     p.beside_predecessor = beside_predecessor != nullptr && push == nullptr ? 1 : 0;
     p.predecessor_done = beside_predecessor;
     p.query = query;

@@ -8,6 +8,14 @@
 //     zp = f16(-min / s)
 //     q  = clamp(rint(x / s + zp), 0, 255)
 // so the bytes and the two f16 values are reproducible bit for bit on a CPU.
+//
+// Rotary position embedding can be applied to the key rows on the way (b2a_paged_kv_store_rope): the first
+// rotary_dim values of a key row, at cache position p, are rotated in pairs (i, i + rotary_dim/2) -
+//     x'[i]         = x[i] * cos[p][i] - x[i + r/2] * sin[p][i]
+//     x'[i + r/2]   = x[i + r/2] * cos[p][i] + x[i] * sin[p][i]            (r = rotary_dim, i < r/2)
+// each product and the sum single round-to-nearest binary32 operations (no fused multiply-add), and the rotated
+// float32 values are what is quantised (or rounded to the cache's 16-bit type).  A model then feeds the un-rotated
+// key projection to the store and saves the pass that rotates K in memory; queries are rotated by their producer.
 #include "launch.cuh"
 
 namespace b2a {
@@ -23,7 +31,19 @@ struct StoreParams {
     PagedTables t;
     int Hkv, D, Dv, kv_dtype;
     int32_t* status;
+    // rotary embedding of the key rows (rotary_dim == 0: none): f32 tables [positions][rotary_dim / 2]
+    const float* rope_cos;
+    const float* rope_sin;
+    int rotary_dim, rope_positions;
 };
+
+// x[d] of a key row at cache position `pos`, rotated; `own` is x[d], `partner` is x[d +- rotary_dim/2]
+__device__ __forceinline__ float rope_value(const StoreParams& p, int pos, int d, float own, float partner) {
+    const int half = p.rotary_dim >> 1;
+    const int i = d < half ? d : d - half;
+    const float c = p.rope_cos[static_cast<size_t>(pos) * half + i], s = p.rope_sin[static_cast<size_t>(pos) * half + i];
+    return d < half ? __fsub_rn(__fmul_rn(own, c), __fmul_rn(partner, s)) : __fadd_rn(__fmul_rn(own, c), __fmul_rn(partner, s));
+}
 
 // Sequence of token `tok`: the last s with subsequence_begins[s] <= tok, found by the whole warp - every round the 32
 // lanes probe 32 evenly spaced entries of the remaining range and a ballot picks the segment, so 65535 sequences take
@@ -72,13 +92,24 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
     const int slot = pos % bs;
     const T* src = reinterpret_cast<const T*>(which ? p.value : p.key) + (static_cast<size_t>(tok) * p.Hkv + hk) * D;
     uint8_t* cache = which ? p.v_cache : p.k_cache;
+    const bool rope = which == 0 && p.rotary_dim > 0;
+    if (rope && pos >= p.rope_positions) {  // no table row for this position
+        if (lane == 0) report(p.status, B2A_DEV_BAD_LEN);
+        return;
+    }
+    auto value_at = [&](int d) {
+        const float x = to_f32<T>(src[d]);
+        if (!rope || d >= p.rotary_dim) return x;
+        const int half = p.rotary_dim >> 1;
+        return rope_value(p, pos, d, x, to_f32<T>(src[d < half ? d + half : d - half]));
+    };
 
     if (p.kv_dtype != B2A_U8) {
         // plain [block_size, D] chunk of f16 / bf16
         uint16_t* dst = reinterpret_cast<uint16_t*>(cache) +
                         ((static_cast<size_t>(blk) * p.Hkv + hk) * bs + slot) * D;
         for (int d = lane; d < D; d += 32) {
-            const float x = to_f32<T>(src[d]);
+            const float x = value_at(d);
             dst[d] = p.kv_dtype == B2A_F16 ? __half_as_ushort(__float2half_rn(x))
                                            : __bfloat16_as_ushort(__float2bfloat16_rn(x));
         }
@@ -89,7 +120,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
     uint8_t* row = chunk + slot * D;
     // D == 128 with 16-bit inputs: each lane keeps its 4 consecutive values in registers (one 8-byte load, one
     // 4-byte store); other sizes take the strided loops below.  Same arithmetic either way.
-    const bool vec = (D == 128) && sizeof(T) == 2 && ((reinterpret_cast<uintptr_t>(src) & 7) == 0);
+    const bool vec = !rope && (D == 128) && sizeof(T) == 2 && ((reinterpret_cast<uintptr_t>(src) & 7) == 0);
     float xv[4];
     float mn = INFINITY, mx = -INFINITY;
     if (vec) {
@@ -103,7 +134,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
         }
     } else {
         for (int d = lane; d < D; d += 32) {
-            const float x = to_f32<T>(src[d]);
+            const float x = value_at(d);
             mn = fminf(mn, x);
             mx = fmaxf(mx, x);
         }
@@ -128,7 +159,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_kernel(const
         reinterpret_cast<uint32_t*>(row)[lane] = packed;
     } else {
         for (int d = lane; d < D; d += 32) {
-            const float x = to_f32<T>(src[d]);
+            const float x = value_at(d);
             const float t = rintf(__fadd_rn(__fdiv_rn(x, sf), zf));
             row[d] = static_cast<uint8_t>(fminf(fmaxf(t, 0.f), 255.f));
         }
@@ -156,7 +187,10 @@ __device__ __forceinline__ float bits_to_f32<__nv_bfloat16>(uint32_t h16) {
     return __uint_as_float(h16 << 16);
 }
 
-template <typename T>
+// kRope: the key rows are rotated over all 128 values (rotary_dim == 128): a value's partner, 64 further on or back,
+// sits at the same place in the registers of the lane four lanes away; rotated values are arbitrary float32
+// numbers, for which the reciprocal shortcut below is not proved, so those rows take the division itself.
+template <typename T, bool kRope>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kernel(const StoreParams p) {
     constexpr int D = 128;
     const int lane = threadIdx.x & 31, l8 = lane & 7, rg = lane >> 3;
@@ -179,6 +213,10 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kern
         return;
     }
     const int slot = pos % bs;
+    if (kRope && pos >= p.rope_positions) {  // no table row for this position
+        if (lane == 0) report(p.status, B2A_DEV_BAD_LEN);
+        return;
+    }
     const size_t chunk_bytes = u8_chunk_bytes(bs, D);
     const int rows = 2 * p.Hkv;  // row r: head r >> 1, key (0) or value (1)
     for (int r0 = 0; r0 < rows; r0 += 4) {
@@ -198,8 +236,20 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kern
         for (int i = 0; i < 8; ++i) {
             xv[2 * i] = bits_to_f32<T>(w[i] & 0xffffu);
             xv[2 * i + 1] = bits_to_f32<T>(w[i] >> 16);
-            mn = fminf(mn, fminf(xv[2 * i], xv[2 * i + 1]));
-            mx = fmaxf(mx, fmaxf(xv[2 * i], xv[2 * i + 1]));
+        }
+        const bool rotated = kRope && (r & 1) == 0;  // key rows
+        if constexpr (kRope) {
+            // lane l8 holds values 16*l8 .. +15: partners are in lane l8 ^ 4 (every lane takes part in the exchange)
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float partner = __shfl_xor_sync(0xffffffffu, xv[e], 4);
+                if (rotated) xv[e] = rope_value(p, pos, 16 * l8 + e, xv[e], partner);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            mn = fminf(mn, xv[e]);
+            mx = fmaxf(mx, xv[e]);
         }
 #pragma unroll
         for (int o = 1; o <= 4; o <<= 1) {
@@ -223,7 +273,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kern
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
             float q;
-            if (fabsf(xv[e]) < 1e-30f) {
+            if (rotated || fabsf(xv[e]) < 1e-30f) {
                 q = __fdiv_rn(xv[e], sf);
             } else {
                 const float q0 = __fmul_rn(xv[e], rs);
@@ -247,17 +297,29 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) paged_kv_store_rows128_kern
 }  // namespace
 
 int paged_kv_store_launch(const b2a_paged_desc& d, const void* key, const void* value, void* k_cache, void* v_cache,
-                          const PagedTables& t, int32_t* status, cudaStream_t stream) {
+                          const PagedTables& t, int32_t* status, cudaStream_t stream, const RopeTables* rope) {
     if (d.num_tokens == 0) return B2A_OK;
     StoreParams p{key, value, static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), t,
-                  d.Hkv, d.D, d.Dv, d.kv_dtype, status};
+                  d.Hkv, d.D, d.Dv, d.kv_dtype, status, nullptr, nullptr, 0, 0};
+    if (rope != nullptr && rope->rotary_dim > 0) {
+        p.rope_cos = rope->cos;
+        p.rope_sin = rope->sin;
+        p.rotary_dim = rope->rotary_dim;
+        p.rope_positions = rope->positions;
+    }
+    const bool rope_all = p.rotary_dim == 128;
     auto al8 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (d.kv_dtype == B2A_U8 && d.D == 128 && d.Dv == 128 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) &&
-        al8(key) && al8(value)) {
+        al8(key) && al8(value) && (p.rotary_dim == 0 || rope_all)) {
         const unsigned grid_t = static_cast<unsigned>((d.num_tokens + kWarpsPerCta - 1) / kWarpsPerCta);
-        const cudaError_t e = d.q_dtype == B2A_F16
-            ? launch_overlapped(paged_kv_store_rows128_kernel<__half>, dim3(grid_t), dim3(kWarpsPerCta * 32), 0, stream, p)
-            : launch_overlapped(paged_kv_store_rows128_kernel<__nv_bfloat16>, dim3(grid_t), dim3(kWarpsPerCta * 32), 0, stream, p);
+        const dim3 block(kWarpsPerCta * 32);
+        cudaError_t e;
+        if (d.q_dtype == B2A_F16)
+            e = rope_all ? launch_overlapped(paged_kv_store_rows128_kernel<__half, true>, dim3(grid_t), block, 0, stream, p)
+                         : launch_overlapped(paged_kv_store_rows128_kernel<__half, false>, dim3(grid_t), block, 0, stream, p);
+        else
+            e = rope_all ? launch_overlapped(paged_kv_store_rows128_kernel<__nv_bfloat16, true>, dim3(grid_t), block, 0, stream, p)
+                         : launch_overlapped(paged_kv_store_rows128_kernel<__nv_bfloat16, false>, dim3(grid_t), block, 0, stream, p);
         return e == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
     }
     const long long total = 2LL * d.num_tokens * d.Hkv;

@@ -83,7 +83,8 @@ struct TcParams {
 
 // Output side of a head-sharded launch (world == 0: single GPU, the tmO map is the output).
 struct TcPeers {
-    CUtensorMap out[kMaxShardWorld];  // [rank]: that rank's [B, Hq_total, Sq, 128] output buffer
+    uint8_t* out[kMaxShardWorld];     // [rank]: that rank's dense [B, Hq_total, Sq, 128] output buffer as mapped here
+    int hq_total, sq;                 // its extents (rows of 256 bytes, consecutive rows contiguous)
     int32_t* flags[kMaxShardWorld];
     int32_t* done_counter;
     int world, rank, head_offset;
@@ -101,10 +102,11 @@ constexpr int kPlanHeaderInts = 4;  // [0] items in the list (per KV head), [1] 
 // those CTAs are seated, takes the rest (and the others as they come free).  The share is worked out here from the
 // tables: item-steps of the work list against cached bytes of the one-token sequences, each divided by what one SM
 // gets through per microsecond (measured on a step of eight 1024-token prefills beside 120 decode sequences: about
-// 3.4 us per item-step of two 128 x 128 tiles over 128 keys at the efficiency of short items; about 63 bytes per
-// nanosecond of u8 cache per SM while the SMs that decode are a minority).
+// 3.4 us per item-step of two 128 x 128 tiles over 128 keys at the efficiency of short items; about 52 bytes per
+// nanosecond of u8 cache per SM while the SMs that decode are a minority - a sweep of the share on that step was
+// flat within 5 % between 0.59 and 0.70 and best at 0.59).
 constexpr float kUsPerItemStep = 3.4f;
-constexpr float kDecodeBytesPerNsPerSm = 63.f;
+constexpr float kDecodeBytesPerNsPerSm = 52.f;
 constexpr float kHbmBytesPerNs = 6500.f;
 // With `owner` given the kernel also lays out the gathered K/V scratch: every multi-token sequence gets a row range
 // of roundup(context, 128) rows (kv_base[seq]; allocation order is whatever the atomics make it), and owner[g] names
@@ -921,7 +923,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             }
                         }
                     }
-                } else {
+                } else if (peers.world == 0) {
                     // two passes of 64 columns through this warp's [32 rows x 128 bytes] staging slab
                     const uint32_t slab = sOut + static_cast<uint32_t>(warp) * 4096u;
                     uint8_t* prow = gbase + 6 * kTile + warp * 4096 + (r & 31) * 128;
@@ -949,15 +951,54 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            const int w = warp & 3;
-                            if (peers.world == 0) {
-                                tma_store_4d_hint(&tmO, slab, 64 * half, row0 + 32 * w, head, b, l2_evict_first_policy());
-                            } else {
-                                // the same slab into every rank's buffer, the next rank first so that the ranks do
-                                // not all write to the same peer at the same time; local copy last
+                            tma_store_4d_hint(&tmO, slab, 64 * half, row0 + 32 * (warp & 3), head, b, l2_evict_first_policy());
+                            tma_store_commit();
+                        }
+                    }
+                } else {
+                    // Sharded heads: the tile goes to every rank, and what limits the step from four ranks on is the
+                    // links, so the stores are made as large and as contiguous as they can be.  Rows of the output are
+                    // 256 bytes and consecutive rows of a head are adjacent, so 16 full rows form one contiguous 4 KB
+                    // piece of the destination: two passes of 16 rows through the warp's 4 KB slab (unswizzled), one
+                    // untiled bulk store per rank and pass.  (The 16 threads of a pass write the same banks; the epilogue is a small part of a
+                    // tile's time and off the critical path of an exchange-bound step.)
+                    const uint32_t slab = sOut + static_cast<uint32_t>(warp) * 4096u;
+                    uint8_t* prow = gbase + 6 * kTile + warp * 4096 + (r & 15) * 256;
+                    const int wrow0 = row0 + 32 * (warp & 3);  // first row of this warp
+                    const size_t head_rows = (static_cast<size_t>(b) * peers.hq_total + peers.head_offset + head) * peers.sq;
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass) {
+                        if (lane == 0) tma_store_wait_read();  // the slab's previous stores have read it
+                        __syncwarp();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {  // (every lane takes part in the load; half of them store)
+                            uint32_t o[32];
+                            tmem_ld32(tO + 32 * q, o);
+                            tmem_wait_ld();
+                            if ((lane >> 4) == pass) {
+#pragma unroll
+                                for (int ch = 0; ch < 4; ++ch) {
+                                    uint4 v;
+                                    v.x = pack2<kBf16>(__uint_as_float(o[8 * ch + 0]) * inv, __uint_as_float(o[8 * ch + 1]) * inv);
+                                    v.y = pack2<kBf16>(__uint_as_float(o[8 * ch + 2]) * inv, __uint_as_float(o[8 * ch + 3]) * inv);
+                                    v.z = pack2<kBf16>(__uint_as_float(o[8 * ch + 4]) * inv, __uint_as_float(o[8 * ch + 5]) * inv);
+                                    v.w = pack2<kBf16>(__uint_as_float(o[8 * ch + 6]) * inv, __uint_as_float(o[8 * ch + 7]) * inv);
+                                    *reinterpret_cast<uint4*>(prow + 64 * q + 16 * ch) = v;
+                                }
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int first = wrow0 + 16 * pass;
+                            const int rows = min(16, peers.sq - first);  // rows past the end of the tensor are dropped
+                            if (rows > 0) {
+                                const size_t at = (head_rows + first) * 256;
+                                // the next rank first so that the ranks do not all write to the same peer at the same
+                                // time; the local copy last
                                 for (int i = 1; i <= peers.world; ++i) {
                                     const int dst = (peers.rank + i) % peers.world;
-                                    tma_store_4d(&peers.out[dst], slab, 64 * half, row0 + 32 * w, peers.head_offset + head, b);
+                                    bulk_store(peers.out[dst] + at, slab, static_cast<uint32_t>(rows) * 256u);
                                 }
                             }
                             tma_store_commit();
@@ -1101,13 +1142,12 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
         if (!make_map(&mo, o, bf16, d.B, d.Hq, d.Sq, os, 32)) return B2A_ERR_CUDA;
     } else {
         mo = mq;  // not read
-        const int64_t fs[4] = {static_cast<int64_t>(peer_out->hq_total) * d.Sq * kHeadDim,
-                               static_cast<int64_t>(d.Sq) * kHeadDim, kHeadDim, 1};
         for (int r = 0; r < peer_out->world; ++r) {
-            if (!make_map(&peers.out[r], peer_out->out_base[r], bf16, d.B, peer_out->hq_total, d.Sq, fs, 32))
-                return B2A_ERR_CUDA;
+            peers.out[r] = static_cast<uint8_t*>(peer_out->out_base[r]);
             peers.flags[r] = peer_out->flags[r];
         }
+        peers.hq_total = peer_out->hq_total;
+        peers.sq = d.Sq;
         peers.done_counter = peer_out->done_counter;
         peers.world = peer_out->world;
         peers.rank = peer_out->rank;

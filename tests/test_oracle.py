@@ -134,3 +134,23 @@ def test_division_by_scale_identity(tmp_path):
     subprocess.run(["gcc", "-O2", "-mfma", "-o", exe, src, "-lm"], check=True)
     r = subprocess.run([exe, "16"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and " 0 mismatches" in r.stdout, r.stdout
+
+
+def test_rope_oracle_properties():
+    """The rotary-embedding restatement: position 0 is the identity, values beyond rotary_dim pass through, every
+    (i, i + r/2) pair keeps its norm, and a rotation by p then by q - the tables being angles p*f and q*f - equals the
+    rotation by p + q up to float32 rounding."""
+    from oracle import rope
+    r, d = 32, 48
+    cos, sin = rope.rope_tables(128, r)
+    assert cos.dtype == np.float32 and cos.shape == (128, r // 2)
+    x = np.random.default_rng(0).standard_normal((6, 3, d)).astype(np.float32)
+    pos = np.array([0, 1, 5, 17, 64, 127])
+    y = rope.rope_rows(x, pos, cos, sin, r)
+    assert np.array_equal(y[0], x[0]) and np.array_equal(y[..., r:], x[..., r:])
+    n0 = x[..., : r // 2] ** 2 + x[..., r // 2: r] ** 2
+    n1 = y[..., : r // 2] ** 2 + y[..., r // 2: r] ** 2
+    np.testing.assert_allclose(n1, n0, rtol=1e-5, atol=1e-6)
+    twice = rope.rope_rows(rope.rope_rows(x, [3] * 6, cos, sin, r), [9] * 6, cos, sin, r)
+    np.testing.assert_allclose(twice, rope.rope_rows(x, [12] * 6, cos, sin, r), rtol=1e-4, atol=1e-5)
+    assert rope.token_positions([4, 0], [0, 2, 5]).tolist() == [4, 5, 0, 1, 2]
