@@ -309,7 +309,7 @@ def bench_prefill(args, rank, world, local):
     h2d = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
     e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": out_h.numel() * 2, "ms_per_step": ems,
-           "api": f"C++ HostSdpaRunner: pinned upload, SdpaOp::Execute and download per (batch entry, KV head) piece "
+           "api": f"C++ HostSdpaRunner: pinned upload, SdpaOp::Execute and download per piece of a few KV heads of one batch entry "
                   f"({pipe.pieces} pieces) on three streams" if pipe is not None
            else "sdpa on device copies of the host tensors"}
     if group is not None:
