@@ -11,7 +11,10 @@
 //   2 paged, gathered: paged_gather_kernel has de-quantised the contexts of the step's multi-token sequences once
 //     into an f16 scratch (a row range per sequence), and K/V tiles are staged from there by TMA like dense ones.
 //     Taken when the caller passes the scheduler's bound on those contexts (b2a_paged_desc.prefill_kv_tokens).
-//   In the paged modes query token i of a sequence sees cache positions 0 .. past_len + i.
+//   In the paged modes query token i of a sequence sees cache positions 0 .. past_len + i, or only the last
+//   `sliding_window` of them: an item then starts at the first key tile that any of its rows still sees, and key
+//   tiles that begin below the window of a tile's last row are masked at their low edge like diagonal tiles at
+//   their high edge.
 //
 // Work is cut into items: TWO 128-row query tiles of one KV head, walked over the keys 128 at a time.  CTAs are
 // persistent (one per SM; mode 1 keeps one item per CTA): the items, heaviest first, are dealt in snake order.
@@ -19,8 +22,9 @@
 //               and sum, writes P_A = exp2(S*c - m) as 16-bit pairs over the first half of S_A's columns
 //               (tcgen05.st) and signals the MMA issuer after the first 64 keys and again after all 128; rescales
 //               O_A in TMEM when the maximum moved; finally normalises O_A and stores it (dense: through a
-//               [32 x 64] staging slab per warp and one TMA store per slab - to every rank's buffer when the heads
-//               are sharded; paged: row-wise stores).
+//               staging slab per warp - [32 x 64] and one TMA tensor store per slab, to every rank's buffer when the
+//               heads are sharded over two ranks; pieces of 16 full rows and one bulk store per rank from four ranks
+//               on; paged: row-wise stores).
 //   warps 4-7   the same for tile B.
 //   warp  8     TMA producer (one lane): the Q tiles of an item as soon as the previous item's last QK^T has
 //               completed, and (modes 0, 2) K_j and V_j into two-stage rings that run on across items.
@@ -70,6 +74,7 @@ enum Bar { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL 
 struct TcParams {
     int B, Hq, Hkv, G, Sq, Skv;
     int causal;
+    int window;  // paged modes: a query at position p sees keys p - window + 1 .. p (0: all of them)
     float scale_log2;
     int32_t* status;
     // paged mode
@@ -83,8 +88,10 @@ struct TcParams {
 
 // Output side of a head-sharded launch (world == 0: single GPU, the tmO map is the output).
 struct TcPeers {
-    uint8_t* out[kMaxShardWorld];     // [rank]: that rank's dense [B, Hq_total, Sq, 128] output buffer as mapped here
+    CUtensorMap out_map[kMaxShardWorld];  // [rank]: that rank's [B, Hq_total, Sq, 128] output buffer (two ranks)
+    uint8_t* out[kMaxShardWorld];     // ... and its address as mapped here (four ranks and more)
     int hq_total, sq;                 // its extents (rows of 256 bytes, consecutive rows contiguous)
+    int bulk_rows;                    // != 0: the epilogue sends pieces of 16 full rows by untiled bulk stores
     int32_t* flags[kMaxShardWorld];
     int32_t* done_counter;
     int world, rank, head_offset;
@@ -239,11 +246,6 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if constexpr (kBf16) {
@@ -374,8 +376,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // are dealt to the CTAs in snake order (round k forwards, round k+1 backwards), which evens out the causal
     // imbalance without any shared counter.  Every role calls get_item for itself, so the per-sequence values
     // below are private to the calling thread and follow its own progress through the items.
+    // nkvA, nkvB, nmax count key steps from the item's first key tile kv_tile0 (0 unless a sliding window lets the
+    // item skip the tiles that all its rows have left behind)
     struct Item {
-        int b, hk, row0A, row0B, headA, headB, nkvA, nkvB, nmax;
+        int b, hk, row0A, row0B, headA, headB, nkvA, nkvB, nmax, kv_tile0;
     };
     int seq = 0, tok_base = 0, nrows_total = 0, pos_base = 0, kv_limit = 0;
     bool causal = true;
@@ -428,7 +432,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // inconsistent tables: an empty item, reported once per item by the producer thread
                 if (threadIdx.x == 8 * 32) report(p.status, B2A_DEV_BAD_LEN);
                 it.hk = 0;
-                it.row0A = it.row0B = it.headA = it.headB = it.nkvA = it.nkvB = it.nmax = 0;
+                it.row0A = it.row0B = it.headA = it.headB = it.nkvA = it.nkvB = it.nmax = it.kv_tile0 = 0;
                 return true;
             }
         } else {
@@ -445,16 +449,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             it.b = y / p.Hkv;
             it.hk = y % p.Hkv;
         }
-        auto tile_of = [&](int t, int& row0, int& head, int& nkv) {
+        // a tile's rows, its head, the end of its keys (in tiles) and the first key tile any of its rows still sees
+        auto tile_of = [&](int t, int& row0, int& head, int& nkv, int& first) {
             const bool present = t < tiles;
             const int rb = present ? t / p.G : 0, g = present ? t % p.G : 0;
             row0 = rb * kBM;
             head = it.hk * p.G + g;
             const int kv_end = causal ? min(kv_limit, pos_base + row0 + kBM) : kv_limit;
             nkv = present ? (kv_end + kBN - 1) / kBN : 0;
+            if constexpr (kPaged) {
+                first = (p.window > 0 && present) ? max(0, pos_base + row0 - p.window + 1) / kBN : 0;
+                if (!present) first = 1 << 30;
+            } else {
+                first = 0;
+            }
         };
-        tile_of(2 * pair, it.row0A, it.headA, it.nkvA);
-        tile_of(2 * pair + 1, it.row0B, it.headB, it.nkvB);
+        int firstA, firstB;
+        tile_of(2 * pair, it.row0A, it.headA, it.nkvA, firstA);
+        tile_of(2 * pair + 1, it.row0B, it.headB, it.nkvB, firstB);
+        it.kv_tile0 = 0;
+        if constexpr (kPaged) {
+            // the two tiles walk the same key tiles: both start at the earlier of their first ones (a tile that starts
+            // before its window only meets keys its mask removes)
+            it.kv_tile0 = min(min(firstA, firstB), max(it.nkvA, it.nkvB));
+            it.nkvA = max(0, it.nkvA - it.kv_tile0);
+            it.nkvB = max(0, it.nkvB - it.kv_tile0);
+        }
         it.nmax = max(it.nkvA, it.nkvB);
         return true;
     };
@@ -529,10 +549,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // requested before anything is converted (one memory latency per tile, not one per block), and the
             // block ids of the next step are fetched while this step is converted.
             int phys[8], phys_next[8];
+            const int kv_tile0 = item.kv_tile0;
             auto load_ids = [&](int j, int (&ids)[8]) {
 #pragma unroll
                 for (int it = 0; it < 8; ++it) {
-                    const int lb = j * 8 + it;
+                    const int lb = (kv_tile0 + j) * 8 + it;
                     int id = -1;
                     if (lb < nblk && lb * 16 + tok_in_blk < kv_limit) {
                         id = btab[lb];
@@ -650,7 +671,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (ok) load_q(1);
                 if constexpr (!kDequant) {
                     // gathered mode: the sequence's keys start at row kv_row0 of the scratch, which is one [1, Hkv, rows, 128] tensor
-                    const int kv_row0 = kGathered ? p.kv_base[seq] : 0;
+                    const int kv_row0 = kGathered ? p.kv_base[seq] + it.kv_tile0 * kBN : 0;
                     for (int j = 0; ok && j < it.nmax; ++j, ++g) {
                         const int st = g & 1, n = g >> 1;
                         if (n > 0 && !mbar_wait(BAR(K_EMPTY + st), (n - 1) & 1, abort_flag)) { ok = false; break; }
@@ -793,8 +814,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 const int j_end = kv_limit / kBN;
                 const int dgl = row_pos0 - (kBN - 1);
                 const int j_diag = dgl < 0 ? 0 : dgl / kBN + 1;
-                jb = causal ? min(j_end, j_diag) : j_end;
+                jb = (causal ? min(j_end, j_diag) : j_end) - (kPaged ? item.kv_tile0 : 0);
             }
+            // with a sliding window, key tiles that begin below the window of the tile's LAST row need the mask too
+            const int tile0 = kPaged ? item.kv_tile0 : 0;
+            const int window = kPaged ? p.window : 0;
+            const int low_limit = window > 0 ? row_pos0 + kBM - window : -(1 << 30);  // mask while key0 < low_limit
             const float c = p.scale_log2;
             float m_used = -1.0e30f, l = 0.f;
             for (int j = 0; j < nkv; ++j) {
@@ -806,15 +831,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
                 for (int q = 0; q < 4; ++q) tmem_ld32(tS + 32 * q, s[q]);
                 tmem_wait_ld();
-                const int key0 = j * kBN;
-                if (j >= jb) {
+                const int key0 = (tile0 + j) * kBN;
+                if (j >= jb || (kPaged && key0 < low_limit)) {
                     const int row_pos = row_pos0 + r;  // last key position this row may see (causal)
+                    const int row_low = window > 0 ? row_pos - window + 1 : 0;  // and the first
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int key = key0 + q * 32 + i;
-                            const bool keep = key < kv_limit && (!causal || key <= row_pos);
+                            const bool keep = key < kv_limit && (!causal || key <= row_pos) && (!kPaged || key >= row_low);
                             if (!keep) s[q][i] = 0xff800000u;  // -inf
                         }
                 }
@@ -923,7 +949,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             }
                         }
                     }
-                } else if (peers.world == 0) {
+                } else if (!peers.bulk_rows) {
                     // two passes of 64 columns through this warp's [32 rows x 128 bytes] staging slab
                     const uint32_t slab = sOut + static_cast<uint32_t>(warp) * 4096u;
                     uint8_t* prow = gbase + 6 * kTile + warp * 4096 + (r & 31) * 128;
@@ -951,13 +977,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_4d_hint(&tmO, slab, 64 * half, row0 + 32 * (warp & 3), head, b, l2_evict_first_policy());
+                            if (peers.world == 0) {
+                                tma_store_4d_hint(&tmO, slab, 64 * half, row0 + 32 * (warp & 3), head, b, l2_evict_first_policy());
+                            } else {
+                                // the same slab into every rank's buffer, the next rank first so that the ranks do
+                                // not all write to the same peer at the same time; local copy last
+                                for (int i = 1; i <= peers.world; ++i) {
+                                    const int dst = (peers.rank + i) % peers.world;
+                                    tma_store_4d(&peers.out_map[dst], slab, 64 * half, row0 + 32 * (warp & 3), peers.head_offset + head, b);
+                                }
+                            }
                             tma_store_commit();
                         }
                     }
                 } else {
-                    // Sharded heads: the tile goes to every rank, and what limits the step from four ranks on is the
-                    // links, so the stores are made as large and as contiguous as they can be.  Rows of the output are
+                    // Heads sharded over four or more ranks: the tile goes to every rank and the links are what limits
+                    // the step, so the stores are made as large and as contiguous as they can be (with two ranks the
+                    // exchange hides behind the computation and the lighter epilogue above is faster: 0.263 against
+                    // 0.273 ms on the 4096-token prefill).  Rows of the output are
                     // 256 bytes and consecutive rows of a head are adjacent, so 16 full rows form one contiguous 4 KB
                     // piece of the destination: two passes of 16 rows through the warp's 4 KB slab (unswizzled), one
                     // untiled bulk store per rank and pass.  (The 16 threads of a pass write the same banks; the epilogue is a small part of a
@@ -1142,7 +1179,13 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
         if (!make_map(&mo, o, bf16, d.B, d.Hq, d.Sq, os, 32)) return B2A_ERR_CUDA;
     } else {
         mo = mq;  // not read
+        peers.bulk_rows = peer_out->world >= 4 ? 1 : 0;
+        const int64_t fs[4] = {static_cast<int64_t>(peer_out->hq_total) * d.Sq * kHeadDim,
+                               static_cast<int64_t>(d.Sq) * kHeadDim, kHeadDim, 1};
         for (int r = 0; r < peer_out->world; ++r) {
+            if (!peers.bulk_rows &&
+                !make_map(&peers.out_map[r], peer_out->out_base[r], bf16, d.B, peer_out->hq_total, d.Sq, fs, 32))
+                return B2A_ERR_CUDA;
             peers.out[r] = static_cast<uint8_t*>(peer_out->out_base[r]);
             peers.flags[r] = peer_out->flags[r];
         }
@@ -1187,7 +1230,7 @@ bool paged_tc_supported(const b2a_paged_desc& d, const void* query, const void* 
     const int g = d.Hkv > 0 ? d.Hq / d.Hkv : 0;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     return d.kv_dtype == B2A_U8 && (d.q_dtype == B2A_F16 || d.q_dtype == B2A_BF16) && d.D == kHeadDim &&
-           d.Dv == kHeadDim && d.block_size == 16 && d.sliding_window == 0 && d.max_q_len >= 2 && g >= 1 &&
+           d.Dv == kHeadDim && d.block_size == 16 && d.max_q_len >= 2 && g >= 1 &&
            d.Hkv <= 65535 && al(query) && al(out) && encode_fn() != nullptr;
 }
 
@@ -1275,6 +1318,7 @@ int paged_tc_launch(const b2a_paged_desc& d, const void* query, const void* k_ca
     TcParams p{};
     p.B = 1; p.Hq = d.Hq; p.Hkv = d.Hkv; p.G = d.Hq / d.Hkv; p.Sq = 0; p.Skv = 0;
     p.causal = 1;
+    p.window = d.sliding_window;
     p.scale_log2 = d.scale * kLog2e;
     p.status = status;
     p.k_cache = static_cast<const uint8_t*>(k_cache);

@@ -373,6 +373,32 @@ def test_mixed_step_graph_replay_with_new_lengths(b2a):
     assert_close(out, ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("window", [16, 100, 128, 300, 5000])
+@pytest.mark.parametrize("hq", [32, 24])
+def test_paged_prefill_sliding_window(b2a, window, hq):
+    # multi-token sequences with a sliding window run on the tensor-core kernel too (both prefill variants): a query at
+    # position p sees keys p - window + 1 .. p.  hq = 24 gives groups of three query heads, where the two tiles of a
+    # work item are different row blocks with different first key tiles.
+    past = np.array([0, 100, 700, 37, 0, 255], np.int32)
+    qlen = np.array([300, 129, 2, 1, 640, 1], np.int32)
+    hkv, d = 8, 128
+    w = PagedWorkload(past + qlen, qlen, hq, hkv, d, seed=51)
+    q = _round(w.query, torch.bfloat16)
+    ref = w.reference(q.float().numpy(), sliding_window=window)
+    ctx = past + qlen
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kw = dict(hq=hq, max_context_len=int(ctx.max()), max_q_len=int(qlen.max()), status=status, sliding_window=window)
+    out = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), **kw)
+    hint_rb = int(sum((int(x) + 127) // 128 for x in qlen if x >= 2))
+    hint_kv = int(sum((int(c) + 127) // 128 * 128 for c, x in zip(ctx, qlen) if x >= 2))
+    out2 = b2a.paged_attention(q.cuda(), w.device_cache(), *w.device_tables(), prefill_row_blocks=hint_rb,
+                               prefill_kv_tokens=hint_kv, **kw)
+    assert int(status.item()) == 0
+    assert_close(out, ref, torch.bfloat16, "contexts de-quantised in the kernel")
+    assert_close(out2, ref, torch.bfloat16, "contexts de-quantised once")
+    assert torch.equal(out, out2)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_paged_rows_far_from_zero(b2a, dtype):
     # Rows that sit far from zero have zero-points of thousands (mean 8, deviation 0.1: zp around -2500; the

@@ -93,21 +93,25 @@ def test_world1_low_latency_reports_bad_rows_and_still_delivers(b2a):
     group.close()
 
 
-def _two_ranks_in_one_process(lib, staging_bytes):
-    """Groups of rank 0 and rank 1 of a world of two, both on the current device, connected by pointer."""
+def _ranks_in_one_process(lib, staging_bytes, world=2):
+    """Groups of all ranks of a world, every one on the current device, connected by pointer."""
     gs = []
-    for r in range(2):
+    for r in range(world):
         h = C.c_void_p()
-        assert lib.b2a_shard_group_create(r, 2, staging_bytes, C.byref(h)) == 0
+        assert lib.b2a_shard_group_create(r, world, staging_bytes, C.byref(h)) == 0
         gs.append(h)
-    bases = (C.c_void_p * 2)()
-    for r in range(2):
+    bases = (C.c_void_p * world)()
+    for r in range(world):
         p = C.c_void_p()
         assert lib.b2a_shard_group_output(gs[r], C.byref(p)) == 0
         bases[r] = p.value
-    for r in range(2):
+    for r in range(world):
         assert lib.b2a_shard_group_connect_pointers(gs[r], bases) == 0
     return gs
+
+
+def _two_ranks_in_one_process(lib, staging_bytes):
+    return _ranks_in_one_process(lib, staging_bytes, 2)
 
 
 def _local_desc(_lib, w, n, maxc, hq_local, hkv_local):
@@ -161,30 +165,42 @@ def test_absent_rank_times_out_decode(b2a, in_place):
     lib.b2a_shard_group_destroy(g1)
 
 
-def test_absent_rank_times_out_prefill(b2a):
+@pytest.mark.parametrize("world", [2, 4])
+def test_absent_ranks_time_out_prefill_and_own_tiles_reach_every_rank(b2a, world):
+    # Only rank 0 of the world runs the step (all ranks' buffers live on this one GPU).  Its wait for the others must
+    # run out; its own heads must nevertheless sit, bit-identical to the plain kernel, in the buffer of EVERY rank -
+    # the epilogue's stores to the peers (tensor stores with two ranks, bulk stores of full rows from four on).
     from openvino_contrib_b200 import _lib
+    from openvino_contrib_b200.sharding import _device_view
     lib = _lib.load()
-    B, hq, hkv, S = 1, 4, 1, 256
+    B, hq, hkv, S = 2, 4, 1, 200   # S not a multiple of a row piece: the ragged last rows are clipped
     gen = torch.Generator().manual_seed(3)
     q = (torch.randn(B, hq, S, D, generator=gen) * 0.5).to(torch.bfloat16).cuda()
     k = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16).cuda()
     v = (torch.randn(B, hkv, S, D, generator=gen) * 0.5).to(torch.bfloat16).cuda()
-    g0, g1 = _two_ranks_in_one_process(lib, B * 2 * hq * S * D * 2)
-    assert lib.b2a_shard_group_set_wait_ms(g0, 20) == 0
+    groups = _ranks_in_one_process(lib, B * world * hq * S * D * 2, world)
+    assert lib.b2a_shard_group_set_wait_ms(groups[0], 20) == 0
     d = _lib.SdpaDesc()
     d.dtype = _lib.BF16
     d.B, d.Hq, d.Hkv, d.Sq, d.Skv, d.D, d.Dv = B, hq, hkv, S, S, D, D
     d.causal = 1
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = C.c_void_p()
-    rc = lib.b2a_sdpa_forward_sharded(g0, C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), C.byref(out),
+    rc = lib.b2a_sdpa_forward_sharded(groups[0], C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), C.byref(out),
                                       status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) & _lib.DEV_TIMEOUT
-    # this rank's heads are nevertheless in its own buffer, bit-identical to the plain kernel
-    from openvino_contrib_b200.sharding import _device_view
-    full = _device_view(out.value, (B, 2 * hq, S, D), torch.bfloat16, q.device)
-    assert torch.equal(full[:, :hq], b2a.sdpa(q, k, v, causal=True))
-    lib.b2a_shard_group_destroy(g0)
-    lib.b2a_shard_group_destroy(g1)
+    plain = b2a.sdpa(q, k, v, causal=True)
+    offset = out.value - _base_of(lib, groups[0])   # which half of the staging area this step used
+    for r in range(world):
+        full = _device_view(_base_of(lib, groups[r]) + offset, (B, world * hq, S, D), torch.bfloat16, q.device)
+        assert torch.equal(full[:, :hq], plain), f"rank {r}'s copy of rank 0's heads"
+    for g in groups:
+        lib.b2a_shard_group_destroy(g)
+
+
+def _base_of(lib, group) -> int:
+    p = C.c_void_p()
+    assert lib.b2a_shard_group_output(group, C.byref(p)) == 0
+    return p.value
