@@ -156,8 +156,8 @@ int b2a_sdpa_forward(const b2a_sdpa_desc* desc, const void* q, const void* k, co
     const size_t es = elem_size(r.d.dtype);
     if (!aligned(q, es) || !aligned(k, es) || !aligned(v, es) || !aligned(o, es)) return B2A_ERR_ALIGN;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (!masked && sdpa_tc_supported(r.d, r.qs, r.ks, r.vs, r.os, q, k, v, o))
-        return sdpa_tc_launch(r.d, r.qs, r.ks, r.vs, r.os, q, k, v, o, status, s);
+    if (sdpa_tc_supported(r.d, r.qs, r.ks, r.vs, r.os, q, k, v, o) && (!masked || sdpa_tc_mask_supported(r.d, mask)))
+        return sdpa_tc_launch(r.d, r.qs, r.ks, r.vs, r.os, q, k, v, o, status, s, nullptr, masked ? mask : nullptr);
     return sdpa_generic_launch(r.d, r.qs, r.ks, r.vs, r.os, q, k, v, mask, o, status, s);
 }
 

@@ -94,9 +94,12 @@ struct TcPeerOut {
     int32_t step;                      // value published when the step is complete (increases by one per step)
     long long wait_ns;                 // bound of the wait for the other ranks, nanoseconds of wall-clock time
 };
+// mask != nullptr (and d.causal == 0): the attention mask of the descriptor, when sdpa_tc_mask_supported says the
+// kernel can read it (16-byte pieces along the keys)
+bool sdpa_tc_mask_supported(const b2a_sdpa_desc& d, const void* mask);
 int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
                    const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
-                   cudaStream_t stream, const TcPeerOut* peers = nullptr);
+                   cudaStream_t stream, const TcPeerOut* peers = nullptr, const void* mask = nullptr);
 int sdpa_peer_wait_launch(const int32_t* local_flags, int world, int32_t step, long long wait_ns, int32_t* status,
                           cudaStream_t stream);
 

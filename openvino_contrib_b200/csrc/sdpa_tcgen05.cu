@@ -76,6 +76,10 @@ struct TcParams {
     int causal;
     int window;  // paged modes: a query at position p sees keys p - window + 1 .. p (0: all of them)
     float scale_log2;
+    // dense mode with an attention mask (kMask 1: u8, non-zero keeps; 2: additive, the tensors' 16-bit type):
+    // logical [B, Hq, Sq, Skv] with element strides mask_strides[0..2] (0 on broadcast dimensions), innermost 1
+    const uint8_t* mask;
+    int64_t mask_strides[3];
     int32_t* status;
     // paged mode
     const uint8_t* k_cache;
@@ -346,7 +350,7 @@ __global__ void __launch_bounds__(128) paged_gather_kernel(const PagedTables t, 
 
 // kMode: 0 dense tensors; 1 paged, K/V de-quantised by producer warps inside the kernel; 2 paged, K/V de-quantised
 // beforehand into per-sequence row ranges of an f16 scratch (paged_gather_kernel) and staged by TMA like dense ones
-template <bool kBf16, int kMode>
+template <bool kBf16, int kMode, int kMask = 0>
 __global__ void __launch_bounds__(kMode == 1 ? kThreadsPaged : kThreadsDense, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p,
@@ -820,7 +824,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const int tile0 = kPaged ? item.kv_tile0 : 0;
             const int window = kPaged ? p.window : 0;
             const int low_limit = window > 0 ? row_pos0 + kBM - window : -(1 << 30);  // mask while key0 < low_limit
-            const float c = p.scale_log2;
+            const float c = kMask == 2 ? 1.0f : p.scale_log2;  // (additive masks: the block below has scaled the scores)
             float m_used = -1.0e30f, l = 0.f;
             for (int j = 0; j < nkv; ++j) {
                 // every lane takes the same decision, so the warp-collective TMEM instructions stay converged
@@ -832,6 +836,51 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 for (int q = 0; q < 4; ++q) tmem_ld32(tS + 32 * q, s[q]);
                 tmem_wait_ld();
                 const int key0 = (tile0 + j) * kBN;
+                if constexpr (kMask != 0) {
+                    // this row's 128 mask values of the step, 32 keys at a time (rows past the end of the tensor read
+                    // the last row: their results are dropped; keys past the end are removed below)
+                    const int mrow = min(row_pos0 + r, nrows_total - 1);
+                    const uint8_t* mbase = p.mask + (static_cast<int64_t>(item.b) * p.mask_strides[0] +
+                                                     static_cast<int64_t>(X ? item.headB : item.headA) * p.mask_strides[1] +
+                                                     static_cast<int64_t>(mrow) * p.mask_strides[2] + key0) * (kMask == 1 ? 1 : 2);
+                    const bool whole = key0 + kBN <= kv_limit;  // else only whole 16-byte pieces inside the row are read
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if constexpr (kMask == 1) {
+                            uint4 m0 = make_uint4(0u, 0u, 0u, 0u), m1 = m0;
+                            if (whole || key0 + 32 * q + 16 <= kv_limit) m0 = *reinterpret_cast<const uint4*>(mbase + 32 * q);
+                            if (whole || key0 + 32 * q + 32 <= kv_limit) m1 = *reinterpret_cast<const uint4*>(mbase + 32 * q + 16);
+                            const uint32_t w[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (((w[i >> 2] >> (8 * (i & 3))) & 0xffu) == 0u) s[q][i] = 0xff800000u;  // -inf
+                        } else {
+                            // additive: the scores leave this block as S * scale * log2(e) + mask * log2(e)
+                            const float c = p.scale_log2;
+#pragma unroll
+                            for (int h = 0; h < 4; ++h) {
+                                uint4 m = make_uint4(0u, 0u, 0u, 0u);
+                                if (whole || key0 + 32 * q + 8 * h + 8 <= kv_limit) m = *reinterpret_cast<const uint4*>(mbase + 64 * q + 16 * h);
+                                const uint32_t w[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    float lo, hi;
+                                    if constexpr (kBf16) {
+                                        lo = __uint_as_float(w[i] << 16);
+                                        hi = __uint_as_float(w[i] & 0xffff0000u);
+                                    } else {
+                                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                                        lo = f.x;
+                                        hi = f.y;
+                                    }
+                                    const int e = 8 * h + 2 * i;
+                                    s[q][e] = __float_as_uint(fmaf(__uint_as_float(s[q][e]), c, lo * kLog2e));
+                                    s[q][e + 1] = __float_as_uint(fmaf(__uint_as_float(s[q][e + 1]), c, hi * kLog2e));
+                                }
+                            }
+                        }
+                    }
+                }
                 if (j >= jb || (kPaged && key0 < low_limit)) {
                     const int row_pos = row_pos0 + r;  // last key position this row may see (causal)
                     const int row_low = window > 0 ? row_pos - window + 1 : 0;  // and the first
@@ -1166,9 +1215,22 @@ bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int
     return encode_fn() != nullptr;
 }
 
+bool sdpa_tc_mask_supported(const b2a_sdpa_desc& d, const void* mask) {
+    // the mask is read in 16-byte pieces along the keys: unit stride there, every row start 16-byte aligned, and a
+    // key count that is a whole number of pieces
+    if (d.mask_kind != B2A_MASK_BOOL && d.mask_kind != B2A_MASK_ADD) return false;
+    const int es = d.mask_kind == B2A_MASK_BOOL ? 1 : 2;
+    const int per_piece = 16 / es;
+    if (d.mask_strides[3] != 1 || d.Skv % per_piece != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(mask) & 15) != 0) return false;
+    for (int i = 0; i < 3; ++i)
+        if (d.mask_strides[i] < 0 || (d.mask_strides[i] * es) % 16 != 0) return false;
+    return true;
+}
+
 int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4], const int64_t (&vs)[4],
                    const int64_t (&os)[4], const void* q, const void* k, const void* v, void* o, int32_t* status,
-                   cudaStream_t stream, const TcPeerOut* peer_out) {
+                   cudaStream_t stream, const TcPeerOut* peer_out, const void* mask) {
     const bool bf16 = d.dtype == B2A_BF16;
     CUtensorMap mq, mk, mv, mo;
     if (!make_map(&mq, q, bf16, d.B, d.Hq, d.Sq, qs, 128) || !make_map(&mk, k, bf16, d.B, d.Hkv, d.Skv, ks, 128) ||
@@ -1210,9 +1272,16 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
     const int sms = device_sm_count();
     if (sms <= 0) return B2A_ERR_CUDA;
     dim3 grid(static_cast<unsigned>(items < sms ? items : sms));  // persistent CTAs, one per SM
-    static bool configured[2][64] = {};
-    auto kern = bf16 ? attn_tc_kernel<true, 0> : attn_tc_kernel<false, 0>;
-    const int rc = configure_once(kern, configured[bf16]);
+    const int mask_kind = (mask != nullptr && !d.causal) ? d.mask_kind : B2A_MASK_NONE;
+    if (mask_kind != B2A_MASK_NONE) {
+        p.mask = static_cast<const uint8_t*>(mask);
+        for (int i = 0; i < 3; ++i) p.mask_strides[i] = d.mask_strides[i];
+    }
+    static bool configured[3][2][64] = {};
+    auto kern = mask_kind == B2A_MASK_BOOL  ? (bf16 ? attn_tc_kernel<true, 0, 1> : attn_tc_kernel<false, 0, 1>)
+                : mask_kind == B2A_MASK_ADD ? (bf16 ? attn_tc_kernel<true, 0, 2> : attn_tc_kernel<false, 0, 2>)
+                                            : (bf16 ? attn_tc_kernel<true, 0, 0> : attn_tc_kernel<false, 0, 0>);
+    const int rc = configure_once(kern, configured[mask_kind][bf16]);
     if (rc != B2A_OK) return rc;
     kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mo, p, peers);
     return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;

@@ -12,6 +12,7 @@
 
 #include "attention_ops.hpp"
 #include "host_pipeline.hpp"
+#include "op_profiling.hpp"
 #include "kv_block_manager.hpp"
 
 using namespace ov::nvidia_gpu;
@@ -473,6 +474,43 @@ void test_paged_op_decode_with_block_manager() {
     cudaGraphExecDestroy(exec);
 }
 
+// The per-operation timing hook: an event pair (and an NVTX range) around Execute, accumulated over calls the way
+// the reference's profiler accumulates them (src/utils/perf_timing.hpp:24-40).
+void test_profiled_step() {
+    CreationContext cc{CUDA::Device{0}, false};
+    ThreadContext tc{CUDA::Device{0}};
+    InferenceRequestContext ctx{tc};
+    auto node = std::make_shared<ov::op::v13::ScaledDotProductAttention>(true);
+    node->set_friendly_name("layer0/attention");
+    const ov::Shape shp{1, 8, 512, 128};
+    for (int i = 0; i < 3; ++i) node->add_input(ov::element::f16, shp);
+    node->add_output(ov::element::f16, shp);
+    auto op = OperationRegistry::getInstance().createOperation(cc, node, ids({0, 1, 2}), ids({3}));
+    const size_t n = 8 * 512 * 128;
+    DevBuf<uint16_t> dq(n), dk(n), dv(n), dout(n);
+    auto s = tc.stream().get();
+    CUDA_OK(cudaMemsetAsync(dq.p, 0, n * 2, s));
+    CUDA_OK(cudaMemsetAsync(dk.p, 0, n * 2, s));
+    CUDA_OK(cudaMemsetAsync(dv.p, 0, n * 2, s));
+    std::vector<CUDA::DevicePointer<const void*>> in{CUDA::DevicePointer<const void*>{dq.p},
+                                                     CUDA::DevicePointer<const void*>{dk.p},
+                                                     CUDA::DevicePointer<const void*>{dv.p}};
+    std::vector<CUDA::DevicePointer<void*>> out{CUDA::DevicePointer<void*>{dout.p}};
+    Workbuffers wb;
+    ProfiledStep step(*op);
+    CHECK(step.label() == "ScaledDotProductAttention: layer0/attention");
+    float total = 0.f;
+    for (int i = 0; i < 3; ++i) {
+        step.execute(ctx, {in.data(), in.size()}, {out.data(), out.size()}, wb);
+        tc.stream().synchronize();
+        const float now = step.measure();
+        CHECK(now > total);  // every call adds its own device time
+        total = now;
+    }
+    CHECK(step.calls() == 3 && step.measure() == total);  // nothing pending: the total stays
+    std::printf("  %s: %u calls, %.3f ms on the device\n", step.label().c_str(), step.calls(), total);
+}
+
 // Host tensors in, host tensor out, through HostSdpaRunner (upload / SdpaOp::Execute / download per piece on three
 // streams), against the CPU loop; two runs in a row (the second finds the device tensors in use by the first).
 void test_host_pipeline() {
@@ -525,6 +563,7 @@ int main(int argc, char** argv) {
         RUN(test_sdpa_op_rejects);
         RUN(test_paged_op_decode_with_block_manager);
         RUN(test_host_pipeline);
+        RUN(test_profiled_step);
     }
     std::printf("%d test(s), %d failed\n", g_run, g_failed);
     return g_failed ? 1 : 0;

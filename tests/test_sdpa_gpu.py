@@ -214,3 +214,31 @@ def test_host_pipeline_matches_device_call(b2a):
         assert torch.equal(out.cuda(), ref)
     with pytest.raises(ValueError):
         pipe(q.cuda(), k, v, out)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["bool", "add"])
+def test_masks_on_the_tensor_core_shape(b2a, dtype, kind):
+    # D = 128 half-precision with an explicit mask (the tensor-core kernel reads the mask rows in 16-byte pieces):
+    # per-batch, per-head and fully broadcast masks, a key count that ends inside a key tile, a query count that ends
+    # inside a row tile, one fully masked row (zeros, not NaN) and, for additive masks, -inf entries.
+    B, hq, hkv, sq, skv, D = 2, 8, 2, 200, 272, 128
+    g = torch.Generator().manual_seed(21)
+    q = (torch.randn(B, hq, sq, D, generator=g) * 0.5).to(dtype)
+    k = (torch.randn(B, hkv, skv, D, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(B, hkv, skv, D, generator=g) * 0.5).to(dtype)
+    for shape in ((B, 1, sq, skv), (1, hq, sq, skv), (sq, skv)):
+        keep = torch.rand(shape, generator=g) > 0.3
+        keep[..., 7, :] = False                       # a fully masked query row
+        keep[..., 0, 0] = True
+        if kind == "bool":
+            mask = keep
+        else:
+            mask = (torch.randn(shape, generator=g) * 2.0).to(dtype)
+            mask = torch.where(keep, mask, torch.tensor(float("-inf"), dtype=dtype))
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = b2a.sdpa(q.cuda(), k.cuda(), v.cuda(), attn_mask=mask.cuda(), status=status)
+        ref = osdpa.sdpa_ref(q, k, v, mask=mask if kind == "bool" else mask.float())
+        assert int(status.item()) == 0
+        assert not torch.isnan(out).any()
+        assert_close(out, ref, dtype, f"{kind} mask of shape {shape}")
