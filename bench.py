@@ -247,7 +247,8 @@ def bench_prefill(args, rank, world, local):
     exchange, group = "none", None
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     if world > 1:
-        exchange = "peer stores from the kernel's epilogue"
+        exchange = ("peer stores from the attention kernel: its epilogue stores every tile to both ranks (2 GPUs); from 4 GPUs "
+                    "on the tile is stored locally and two spare warps of the CTA forward it to the other ranks")
         try:
             from openvino_contrib_b200.sharding import ShardGroup
             group = ShardGroup(shard, staging_bytes=B * Hq * S * D * 2)
@@ -419,7 +420,8 @@ def bench_decode(name, steps, warmup, rank, world):
     exchange = "none"
     group = None
     if world > 1:
-        exchange = "peer stores from the decode kernel (8-byte value pairs with the step number), polled by a receiving kernel"
+        exchange = ("one kernel per step: the last CTA of a (sequence, KV head) merges the splits and sends the rows to every "
+                    "rank as 8-byte words {two values, step number}; CTAs of the same kernel receive the other ranks' rows")
         try:
             group = ShardGroup(shard, staging_bytes=2 * n * Hq * D * 2)
         except Exception as e:  # CUDA IPC not available in this container: fall back to the library collective
@@ -470,7 +472,7 @@ def bench_decode(name, steps, warmup, rank, world):
                    f"{per_rank / 1e6:.0f} MB of cache per GPU and step, read once, evict-first: nothing of it survives in the 126 MB L2"),
             "traffic": NCU_TRAFFIC.get(name) if world == 1 else None,
             "traffic_source": TRAFFIC_SOURCE if world == 1 and name in NCU_TRAFFIC else None,
-            "launches_per_step": 2, "output_exchange": exchange, "timing": how}
+            "launches_per_step": 1 if group is not None else 2, "output_exchange": exchange, "timing": how}
 
 
 def bench_mixed(steps, warmup, rank, world):

@@ -147,39 +147,58 @@ enum ChunkState {
 // The walk over this CTA's chunk of one (sequence, KV head).  On kChunkWorked its partial is in the workspace, `nsplit`
 // is the number of CTAs of this sequence that write one and `tok` the sequence's token row.  With kRowIsSeq the
 // token row must equal the sequence index (the sharded exchange addresses rows by sequence), else kChunkInvalid.
+//
+// With `wait_for_predecessor` the kernel was launched programmatically dependent on the kernel before it, and its CTAs
+// sit on the SMs while that kernel drains.  The walk uses that time for the first two of its three dependent loads:
+// the step's tables and this warp's block ids are read BEFORE the wait (the tables of a step exist before its first
+// kernel is launched; nothing on this path writes them), through L2 so that no line cached by an earlier step is
+// met.  Everything an earlier kernel of the step produces - the query rows, the cache rows of the new tokens, the
+// workspace, the status word, the exchange's counters - is touched only after the wait.
 template <typename T, int NT, bool kRowIsSeq, int kWarps>
-__device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out) {
+__device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out,
+                                                   const bool wait_for_predecessor) {
     const int hk = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tid4 = lane & 3;
 
     // A CTA's start is a chain of dependent global loads (tables -> block ids -> cache rows), and in a step that
     // fills the GPU only once nothing hides it.  So the chain is kept as short as it can be: the five table entries
-    // are requested together, the query rows right behind them, then the block ids, then the first cache stages;
-    // the query fragments are put together while those are in flight.
-    const int tok = p.t.subsequence_begins[seq];
-    const int tok_end = p.t.subsequence_begins[seq + 1];
-    const int past = p.t.past_lens[seq];
-    const int bib0 = p.t.block_indices_begins[seq];
-    const int bib1 = p.t.block_indices_begins[seq + 1];
-    if (tok_end - tok != 1) return kChunkNotRow;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
+    // are requested together, then the block ids, then the query rows and the first cache stages; the query
+    // fragments are put together while those are in flight.
+    const int tok = __ldcg(p.t.subsequence_begins + seq);
+    const int tok_end = __ldcg(p.t.subsequence_begins + seq + 1);
+    const int past = __ldcg(p.t.past_lens + seq);
+    const int bib0 = __ldcg(p.t.block_indices_begins + seq);
+    const int bib1 = __ldcg(p.t.block_indices_begins + seq + 1);
     const int ctx = past + 1;  // the query token sits at position `past` and sees 0..past
     const int nblk = (ctx + kBS - 1) / kBS;
-    if (past < 0 || nblk > bib1 - bib0 || tok < 0 || tok >= p.t.num_tokens || (kRowIsSeq && tok != seq)) {
-        if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return kChunkInvalid;
-    }
     const int first_pos = p.sliding_window > 0 ? max(0, ctx - p.sliding_window) : 0;
     const int blk_lo = first_block_of(ctx, p.sliding_window);
-    if (nblk - blk_lo > p.max_splits * p.blocks_per_cta) {  // context longer than the max_context_len the grid was sized for
+    const int my_lo = blk_lo + split * p.blocks_per_cta;
+    const int my_hi = min(nblk, my_lo + p.blocks_per_cta);
+    ChunkState state = kChunkWorked;
+    if (tok_end - tok != 1) state = kChunkNotRow;  // idle sequences, and multi-token sequences of a mixed step (the prefill kernel's)
+    else if (past < 0 || nblk > bib1 - bib0 || tok < 0 || tok >= p.t.num_tokens || (kRowIsSeq && tok != seq) ||
+             nblk - blk_lo > p.max_splits * p.blocks_per_cta)  // (last: context longer than the max_context_len the grid was sized for)
+        state = kChunkInvalid;
+    else if (my_lo >= my_hi) state = kChunkIdle;
+
+    // blocks of this warp: my_lo + warp + kWarps*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
+    const int n_w = state == kChunkWorked ? (my_hi - my_lo - warp + kWarps - 1) / kWarps : 0;
+    int my_phys = 0;
+    if (lane < n_w) my_phys = __ldcg(p.t.block_indices + bib0 + my_lo + warp + kWarps * lane);
+
+    if (wait_for_predecessor) grid_dependency_wait();
+    grid_launch_dependents();  // the next kernel's CTAs may take their seats while this grid drains
+
+    if (state == kChunkNotRow) return state;
+    if (state == kChunkInvalid) {
         if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return kChunkInvalid;
+        return state;
     }
     nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
     tok_out = tok;
-    const int my_lo = blk_lo + split * p.blocks_per_cta;
-    const int my_hi = min(nblk, my_lo + p.blocks_per_cta);
-    if (my_lo >= my_hi) return kChunkIdle;
+    if (state == kChunkIdle) return state;
 
     // ---- query rows of this thread's heads as loaded: head nt*8 + gid, elements tid4*32 .. +31 (64 bytes)
     const T* qrow = reinterpret_cast<const T*>(p.query) + (static_cast<size_t>(tok) * p.Hq + hk * p.G) * kD;
@@ -194,16 +213,9 @@ __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_
         }
     }
 
-    // blocks of this warp: my_lo + warp + kWarps*i, i < n_w  (n_w <= 32 because blocks_per_cta <= 128)
-    const int n_w = (my_hi - my_lo - warp + kWarps - 1) / kWarps;
-    const int32_t* btab = p.t.block_indices + bib0;
-    int my_phys = 0;
-    if (lane < n_w) {
-        my_phys = btab[my_lo + warp + kWarps * lane];
-        if (my_phys < 0 || my_phys >= p.t.num_blocks_total) {
-            report(p.status, B2A_DEV_BAD_BLOCK);
-            my_phys = -1;
-        }
+    if (lane < n_w && (my_phys < 0 || my_phys >= p.t.num_blocks_total)) {
+        report(p.status, B2A_DEV_BAD_BLOCK);
+        my_phys = -1;
     }
 
     const uint32_t smem_warp = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStage);
@@ -622,20 +634,27 @@ template <typename T, int NT, int kMode, int kWarps>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) paged_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     int nsplit = 0, tok = 0;
-    // the cache rows of this step's new tokens and the query come from earlier kernels (beside the prefill kernel of
-    // a mixed step there is nothing to wait for: that kernel waited for them already and is not waited for itself)
-    if (!p.beside_predecessor) grid_dependency_wait();
-    grid_launch_dependents();   // the next kernel's CTAs may take their seats while this grid drains
+    // the cache rows of this step's new tokens and the query come from earlier kernels: decode_chunk waits for them
+    // after its table walk (beside the prefill kernel of a mixed step there is nothing to wait for: that kernel waited
+    // for them already and is not waited for itself)
+    const bool wait_for_predecessor = !p.beside_predecessor;
     if constexpr (kMode == 0) {
-        decode_chunk<T, NT, false, kWarps>(p, smem, nsplit, tok);
+        decode_chunk<T, NT, false, kWarps>(p, smem, nsplit, tok, wait_for_predecessor);
     } else {
         constexpr bool kLL = kMode == 1;
         __shared__ int s_role;
         const int tid = threadIdx.x, hk = blockIdx.x, seq = blockIdx.y;
-        const int32_t epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
-        if (!kLL && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
-            st_release_sys(p.push.started[tid] + p.push.rank, epoch);  // this rank's readers of the previous step are done
-        const ChunkState state = decode_chunk<T, NT, kLL, kWarps>(p, smem, nsplit, tok);
+        int32_t epoch = 0;
+        if constexpr (!kLL) {
+            // in place: the other ranks hold their stores back until this rank says that the readers of its previous
+            // step are done, so that is said as early as it is true - before the walk, hence after a wait of its own
+            if (wait_for_predecessor) grid_dependency_wait();
+            epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.push.world)
+                st_release_sys(p.push.started[tid] + p.push.rank, epoch);
+        }
+        const ChunkState state = decode_chunk<T, NT, kLL, kWarps>(p, smem, nsplit, tok, kLL && wait_for_predecessor);
+        if constexpr (kLL) epoch = *reinterpret_cast<volatile int32_t*>(p.push.step_counter) + 1;  // (after the walk's wait)
         if (tid == 0) s_role = 0;
         __syncthreads();  // (the role starts cleared for everybody;) every thread's part of the partial is written ...
         if (state == kChunkWorked) {
@@ -712,17 +731,18 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) paged_decode_kernel(
 template <typename T>
 __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodeParams p) {
     const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
-    grid_dependency_wait();  // the partials
+    // the step's tables are read while the decode kernel drains (see decode_chunk), the partials after the wait
+    const int tok = __ldcg(p.t.subsequence_begins + seq);
+    const int qlen = __ldcg(p.t.subsequence_begins + seq + 1) - tok;
+    const int past = __ldcg(p.t.past_lens + seq);
+    const int nblk_have = __ldcg(p.t.block_indices_begins + seq + 1) - __ldcg(p.t.block_indices_begins + seq);
+    grid_dependency_wait();
     grid_launch_dependents();
-    const int tok = p.t.subsequence_begins[seq];
-    const int qlen = p.t.subsequence_begins[seq + 1] - tok;
-    const int past = p.t.past_lens[seq];
     const int ctx = past + 1;
     const int nblk = (ctx + kBS - 1) / kBS;
     const int blk_lo = first_block_of(ctx, p.sliding_window);
     // the same conditions under which the decode kernel wrote partials
-    const bool valid = qlen == 1 && past >= 0 && tok >= 0 && tok < p.t.num_tokens &&
-                       nblk <= p.t.block_indices_begins[seq + 1] - p.t.block_indices_begins[seq] &&
+    const bool valid = qlen == 1 && past >= 0 && tok >= 0 && tok < p.t.num_tokens && nblk <= nblk_have &&
                        nblk - blk_lo <= p.max_splits * p.blocks_per_cta;
     if (!valid) return;
     const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);

@@ -169,7 +169,8 @@ def test_absent_rank_times_out_decode(b2a, in_place):
 def test_absent_ranks_time_out_prefill_and_own_tiles_reach_every_rank(b2a, world):
     # Only rank 0 of the world runs the step (all ranks' buffers live on this one GPU).  Its wait for the others must
     # run out; its own heads must nevertheless sit, bit-identical to the plain kernel, in the buffer of EVERY rank -
-    # the epilogue's stores to the peers (tensor stores with two ranks, bulk stores of full rows from four on).
+    # the epilogue's tensor stores to the peers with two ranks; from four ranks on, the forwarding warps' copies of the
+    # locally stored tile.
     from openvino_contrib_b200 import _lib
     from openvino_contrib_b200.sharding import _device_view
     lib = _lib.load()
