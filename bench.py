@@ -434,10 +434,11 @@ def bench_decode(name, steps, warmup, rank, world):
         turn[0] += 1
         if group is not None:
             group.paged_attention(q, cache, past, sb, bi, bb, max_context_len=maxc, out_full=out_full, workspace=ws,
-                                  status=status)
+                                  status=status, cache_rows_settled=True)
             return out_full
+        # (cache_rows_settled: what the operator passes, whose attention call follows its own store of the new tokens)
         b2a.paged_attention(q, cache, past, sb, bi, bb, hq=hq_l, max_context_len=maxc, max_q_len=1, out=out,
-                            workspace=ws, status=status)
+                            workspace=ws, status=status, cache_rows_settled=True)
         if world > 1:
             return gather_heads_rows(out, shard, D, buffer=gathered)
         return out

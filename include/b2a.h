@@ -128,6 +128,12 @@ typedef struct b2a_paged_desc {
      * into an f16 scratch and the prefill kernel stages K/V tiles by TMA; without it (0) every prefill CTA
      * de-quantises its own tiles.  A bound that is too small makes the step report B2A_DEV_BAD_LEN. */
     int32_t prefill_kv_tokens;
+    /* Optional, decode rows only.  Non-zero: the caller promises that the kernel directly before this call on the stream
+     * writes no cache row other than the rows of this step's new tokens (true when that kernel is this step's
+     * b2a_paged_kv_store, or a kernel that does not touch the cache at all).  The decode kernel, which is launched
+     * while that kernel still drains, then starts copying cache blocks that hold no new token before it waits for
+     * it.  0 (the default): every cache read comes after the wait. */
+    int32_t cache_rows_settled;
 } b2a_paged_desc;
 
 /* Bytes of one (block, KV head) chunk of a cache of `kv_dtype` with head size d. */
@@ -158,7 +164,11 @@ int b2a_paged_kv_store_rope(const b2a_paged_desc* desc, const void* key, const v
                             b2a_stream_t stream);
 
 /* Attention of every query token over its sequence's cache (call after b2a_paged_kv_store of the same step).
- * Counterpart of ReadValue + decomposed SDPA (src/ops/read_value.cpp:31-72 and the SDPA chain above). */
+ * Counterpart of ReadValue + decomposed SDPA (src/ops/read_value.cpp:31-72 and the SDPA chain above).
+ * The four table arrays of a step must be complete before the step's kernels are launched: the kernels are launched
+ * programmatically dependent on the kernel before them on the stream and read the tables while that kernel drains,
+ * so that kernel must not be the one that writes them (tables uploaded from the host, or written by any earlier
+ * kernel, are fine; so is replaying a captured step after changing them). */
 int b2a_paged_attention(const b2a_paged_desc* desc, const void* query, const void* k_cache, const void* v_cache,
                         const int32_t* past_lens, const int32_t* subsequence_begins, const int32_t* block_indices,
                         const int32_t* block_indices_begins, void* out, void* workspace, size_t workspace_bytes,

@@ -30,6 +30,7 @@ class PagedDesc(C.Structure):
         ("num_blocks_total", C.c_int32), ("max_context_len", C.c_int32), ("max_q_len", C.c_int32),
         ("scale", C.c_float), ("sliding_window", C.c_int32), ("prefill_row_blocks", C.c_int32),
         ("prefill_kv_tokens", C.c_int32),
+        ("cache_rows_settled", C.c_int32),
     ]
 
 

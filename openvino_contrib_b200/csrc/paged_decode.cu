@@ -59,6 +59,7 @@ struct DecodeParams {
     float scale_log2;  // softmax scale * log2(e)
     int32_t* status;
     int beside_predecessor;      // see paged_decode_launch: no wait for the kernel before this one
+    int cache_rows_settled;      // b2a_paged_desc: the kernel before this one writes no cache row but the new tokens'
     cudaEvent_t predecessor_done;  // host side only: completes with that kernel
     PeerPush push;     // world == 0 unless the heads are sharded over several GPUs
 };
@@ -152,8 +153,9 @@ enum ChunkState {
 // sit on the SMs while that kernel drains.  The walk uses that time for the first two of its three dependent loads:
 // the step's tables and this warp's block ids are read BEFORE the wait (the tables of a step exist before its first
 // kernel is launched; nothing on this path writes them), through L2 so that no line cached by an earlier step is
-// met.  Everything an earlier kernel of the step produces - the query rows, the cache rows of the new tokens, the
-// workspace, the status word, the exchange's counters - is touched only after the wait.
+// met; so are the first cache blocks of a CTA that does not hold its sequence's last block.  Everything an earlier
+// kernel of the step produces - the query rows, the cache rows of the new tokens, the workspace, the status word, the
+// exchange's counters - is touched only after the wait.
 template <typename T, int NT, bool kRowIsSeq, int kWarps>
 __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_t* smem, int& nsplit, int& tok_out,
                                                    const bool wait_for_predecessor) {
@@ -187,36 +189,8 @@ __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_
     const int n_w = state == kChunkWorked ? (my_hi - my_lo - warp + kWarps - 1) / kWarps : 0;
     int my_phys = 0;
     if (lane < n_w) my_phys = __ldcg(p.t.block_indices + bib0 + my_lo + warp + kWarps * lane);
-
-    if (wait_for_predecessor) grid_dependency_wait();
-    grid_launch_dependents();  // the next kernel's CTAs may take their seats while this grid drains
-
-    if (state == kChunkNotRow) return state;
-    if (state == kChunkInvalid) {
-        if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
-        return state;
-    }
-    nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
-    tok_out = tok;
-    if (state == kChunkIdle) return state;
-
-    // ---- query rows of this thread's heads as loaded: head nt*8 + gid, elements tid4*32 .. +31 (64 bytes)
-    const T* qrow = reinterpret_cast<const T*>(p.query) + (static_cast<size_t>(tok) * p.Hq + hk * p.G) * kD;
-    uint4 qraw[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int n = nt * 8 + gid;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            qraw[nt][c] = make_uint4(0u, 0u, 0u, 0u);
-            if (n < p.G) qraw[nt][c] = reinterpret_cast<const uint4*>(qrow + n * kD + tid4 * 32)[c];
-        }
-    }
-
-    if (lane < n_w && (my_phys < 0 || my_phys >= p.t.num_blocks_total)) {
-        report(p.status, B2A_DEV_BAD_BLOCK);
-        my_phys = -1;
-    }
+    const bool bad_block = lane < n_w && (my_phys < 0 || my_phys >= p.t.num_blocks_total);
+    if (bad_block) my_phys = -1;
 
     const uint32_t smem_warp = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStage);
     const size_t head_stride = kChunk;                         // chunks of one block: [Hkv][2112]
@@ -243,11 +217,53 @@ __device__ __forceinline__ ChunkState decode_chunk(const DecodeParams& p, uint8_
         }
     };
 
-    // ---- pipeline prologue: the first stages are on their way before the query is touched
+    // With the caller's promise that the kernel before this one writes no cache row but the new tokens' (each in
+    // its sequence's last block), a CTA whose blocks end before that block reads nothing that kernel changes, so its
+    // first copy stages also go out before the wait.
+    const bool early = wait_for_predecessor && p.cache_rows_settled && state == kChunkWorked && my_hi < nblk;
+    if (early) {
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
-        if (s < n_w) issue(s);
-        cp_async_commit();
+        for (int s = 0; s < kStages - 1; ++s) {
+            if (s < n_w) issue(s);
+            cp_async_commit();
+        }
+    }
+
+    if (wait_for_predecessor) grid_dependency_wait();
+    grid_launch_dependents();  // the next kernel's CTAs may take their seats while this grid drains
+
+    if (state == kChunkNotRow) return state;
+    if (state == kChunkInvalid) {
+        if (tid == 0 && split == 0) report(p.status, B2A_DEV_BAD_LEN);
+        return state;
+    }
+    nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
+    tok_out = tok;
+    if (state == kChunkIdle) return state;
+
+    // ---- query rows of this thread's heads as loaded: head nt*8 + gid, elements tid4*32 .. +31 (64 bytes)
+    const T* qrow = reinterpret_cast<const T*>(p.query) + (static_cast<size_t>(tok) * p.Hq + hk * p.G) * kD;
+    uint4 qraw[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int n = nt * 8 + gid;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            qraw[nt][c] = make_uint4(0u, 0u, 0u, 0u);
+            if (n < p.G) qraw[nt][c] = reinterpret_cast<const uint4*>(qrow + n * kD + tid4 * 32)[c];
+        }
+    }
+
+    if (bad_block) report(p.status, B2A_DEV_BAD_BLOCK);
+
+    // ---- pipeline prologue (unless it went out before the wait): the first stages are on their way before the
+    // query fragments are put together
+    if (!early) {
+#pragma unroll
+        for (int s = 0; s < kStages - 1; ++s) {
+            if (s < n_w) issue(s);
+            cp_async_commit();
+        }
     }
 
     // ---- query fragments (B operand of QK^T) and per-head sums of Q
@@ -897,6 +913,7 @@ int paged_decode_launch(const b2a_paged_desc& d, const DecodePlan& plan, const v
     p.blocks_per_cta = plan.blocks_per_cta;
     p.max_splits = plan.max_splits;
     p.sliding_window = d.sliding_window;
+    p.cache_rows_settled = d.cache_rows_settled;
     p.scale_log2 = d.scale * kLog2e;
     p.status = status;
     const bool two = p.G > 8;

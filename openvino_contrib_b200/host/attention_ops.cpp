@@ -183,6 +183,8 @@ b2a_paged_desc PagedAttentionOp::StepDesc(int num_tokens, int num_seqs, const At
     d.max_q_len = num_tokens - num_seqs + 1;
     d.prefill_row_blocks = 0;
     d.prefill_kv_tokens = 0;
+    // Execute launches the step's store directly before its attention: no other cache row changes in between
+    d.cache_rows_settled = 1;
     if (d.max_q_len >= 2) {
         // The work list is reserved for the bound tokens/128 + sequences; a hint can only tighten it.  The scratch
         // of de-quantised contexts is reserved for max_prefill_kv_tokens; a step that says it needs more (or says

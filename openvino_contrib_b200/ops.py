@@ -240,7 +240,7 @@ class PagedKvCache:
 
 def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens: int, max_context_len: int,
                 max_q_len: int, scale: Optional[float], sliding_window: int, prefill_row_blocks: int = 0,
-                prefill_kv_tokens: int = 0) -> PagedDesc:
+                prefill_kv_tokens: int = 0, cache_rows_settled: bool = False) -> PagedDesc:
     d = PagedDesc()
     d.q_dtype = _dtype_code(q_dtype)
     d.kv_dtype = _dtype_code(cache.kv_dtype)
@@ -251,6 +251,7 @@ def _paged_desc(q_dtype, cache: PagedKvCache, hq: int, num_seqs: int, num_tokens
     d.sliding_window = int(sliding_window)
     d.prefill_row_blocks = int(prefill_row_blocks)
     d.prefill_kv_tokens = int(prefill_kv_tokens)
+    d.cache_rows_settled = 1 if cache_rows_settled else 0
     return d
 
 
@@ -292,11 +293,13 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
                     scale: Optional[float] = None, sliding_window: int = 0, out: Optional[torch.Tensor] = None,
                     workspace: Optional[torch.Tensor] = None, stream=None,
                     status: Optional[torch.Tensor] = None, prefill_row_blocks: int = 0,
-                    prefill_kv_tokens: int = 0) -> torch.Tensor:
+                    prefill_kv_tokens: int = 0, cache_rows_settled: bool = False) -> torch.Tensor:
     """Attention of query [tokens, Hq*D] over the cache; returns [tokens, Hq*Dv].
 
     ``prefill_row_blocks`` and ``prefill_kv_tokens`` are the optional scheduler hints of ``b2a_paged_desc``
-    (``KvBlockManager`` reports both); the second lets a mixed step de-quantise its prefill contexts once."""
+    (``KvBlockManager`` reports both); the second lets a mixed step de-quantise its prefill contexts once.
+    ``cache_rows_settled``: the caller's promise that the kernel directly before this call on the stream writes no
+    cache row other than this step's new tokens (see ``b2a_paged_desc``)."""
     _require_cuda(query, cache.k, cache.v, past_lens, subsequence_begins, block_indices, block_indices_begins, out)
     if not query.is_contiguous() or query.shape[1] != hq * cache.d:
         raise ValueError("query must be dense [tokens, Hq*D]")
@@ -304,7 +307,7 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
     if out is None:
         out = torch.empty((num_tokens, hq * cache.dv), dtype=query.dtype, device=query.device)
     d = _paged_desc(query.dtype, cache, hq, num_seqs, num_tokens, max_context_len, max_q_len, scale, sliding_window,
-                    prefill_row_blocks, prefill_kv_tokens)
+                    prefill_row_blocks, prefill_kv_tokens, cache_rows_settled)
     lib = _lib.load()
     ws = C.c_size_t(0)
     check(lib.b2a_paged_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_workspace_bytes")
@@ -404,7 +407,8 @@ class PagedAttentionOp:
         paged_attention(query, cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
                         self.hq, self.max_context_len, max_q_len, self.scale if sc is None else float(sc),
                         self.sliding_window, out=outputs[0], workspace=ws, stream=stream,
-                        status=status, prefill_row_blocks=rb, prefill_kv_tokens=kvt)
+                        status=status, prefill_row_blocks=rb, prefill_kv_tokens=kvt,
+                        cache_rows_settled=True)  # the kernel before it is this step's store
 
 
 # ------------------------------------------------------------------------------------------------------------

@@ -156,13 +156,14 @@ class ShardGroup:
     def paged_attention(self, query_local, cache_local, past_lens, subsequence_begins, block_indices,
                         block_indices_begins, max_context_len: int, out_full: Optional[torch.Tensor],
                         workspace: torch.Tensor, scale: Optional[float] = None,
-                        status: Optional[torch.Tensor] = None, stream=None):
+                        status: Optional[torch.Tensor] = None, stream=None, cache_rows_settled: bool = False):
         """One decode step on this rank's heads; the [tokens, Hq*D] result is complete on every rank afterwards.
 
         With ``out_full=None`` the step is a single kernel that produces the rows in the group's own buffer on every
         rank; the returned tensor is a view of that buffer (valid until the next step on this group).  With a
         caller's ``out_full`` the rows travel as 8-byte {two values, step number} words through staging buffers of
-        twice the output size and a second kernel copies them there.
+        twice the output size and the decode kernel's own CTAs (a second kernel when there are more rows than SMs)
+        copy them there.  ``cache_rows_settled``: see ``ops.paged_attention``.
         """
         from . import _lib
         from .ops import _paged_desc, _ptr, _stream_ptr
@@ -174,7 +175,7 @@ class ShardGroup:
             out_full = _device_view(ptr.value, (n, self.shard.hq * cache_local.dv), query_local.dtype,
                                     query_local.device)
         d = _paged_desc(query_local.dtype, cache_local, self.shard.hq_local, past_lens.shape[0], n, max_context_len,
-                        1, scale, 0)
+                        1, scale, 0, cache_rows_settled=cache_rows_settled)
         _lib.check(self._lib.b2a_paged_attention_sharded(
             self._h, C.byref(d), query_local.data_ptr(), cache_local.k.data_ptr(), cache_local.v.data_ptr(),
             past_lens.data_ptr(), subsequence_begins.data_ptr(), block_indices.data_ptr(),

@@ -225,6 +225,72 @@ def test_mixed_step_through_the_operator(b2a, dtype):
     assert_close(out, ref, dtype)
 
 
+def test_decode_steps_through_the_operator_see_their_new_tokens(b2a):
+    # Pure decode steps through the operator: its attention call promises that only the new tokens' rows changed
+    # (cache_rows_settled), so the decode kernel copies earlier blocks while the store kernel before it still runs.
+    # Three consecutive steps in one captured graph (store, attention, store, attention, ...: every attention kernel
+    # is launched while a store kernel drains); every step's new row - first row of a fresh block, last row of a
+    # block, somewhere inside - must be seen, and nothing else may differ from the oracle.
+    hq, hkv, d, bs = 32, 4, 128, 16
+    past0 = np.array([15, 16, 31, 700, 4095, 2050], np.int32)
+    steps = 3
+    n = len(past0)
+    w = PagedWorkload(past0 + steps, [1] * n, hq, hkv, d, seed=77)   # tables sized for the last step's contexts
+    rng = np.random.default_rng(78)
+    new_k = [_round(rng.standard_normal((n, hkv * d), dtype=np.float32), torch.float16) for _ in range(steps)]
+    new_v = [_round(rng.standard_normal((n, hkv * d), dtype=np.float32), torch.float16) for _ in range(steps)]
+    qs = [_round(rng.standard_normal((n, hq * d), dtype=np.float32), torch.float16) for _ in range(steps)]
+    sb = np.arange(n + 1, dtype=np.int32)
+    ref_k, ref_v = w.k_cache.copy(), w.v_cache.copy()
+    refs = []
+    for i in range(steps):
+        past = (past0 + i).astype(np.int32)
+        opaged.kv_store_ref(new_k[i], ref_k, past, sb, w.bi, w.bb, hkv, d, bs)
+        opaged.kv_store_ref(new_v[i], ref_v, past, sb, w.bi, w.bb, hkv, d, bs)
+        refs.append(opaged.paged_attention_ref(qs[i].float().numpy(), ref_k, ref_v, past, sb, w.bi, w.bb, hq, hkv, d, bs))
+
+    op = b2a.PagedAttentionOp(hq, hkv, d, bs, torch.uint8, max_seqs=8, max_context_len=8192, q_dtype=torch.float16)
+    wb = {"mutable": [torch.empty(m, dtype=torch.uint8, device="cuda") for m in op.GetWorkBufferRequest()["mutable_sizes"]]}
+    cache = w.device_cache()
+    _, sb_d, bi_d, bb_d = w.device_tables()
+    pasts = [torch.from_numpy((past0 + i).astype(np.int32)).cuda() for i in range(steps)]
+    dk, dv, dq = [t.cuda() for t in new_k], [t.cuda() for t in new_v], [t.cuda() for t in qs]
+    outs = [torch.empty(n, hq * d, dtype=torch.float16, device="cuda") for _ in range(steps)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def run():
+        for i in range(steps):
+            op.Execute([dq[i], dk[i], dv[i], cache.k, cache.v, pasts[i], sb_d, bi_d, bb_d, None, 0, None, 8192],
+                       [outs[i]], workbuffers=wb, status=status)
+
+    pool_k, pool_v = cache.k.clone(), cache.v.clone()
+    run()                                   # eager
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for i in range(steps):
+        assert_close(outs[i], refs[i], torch.float16)
+    assert np.array_equal(cache.k.cpu().numpy(), ref_k) and np.array_equal(cache.v.cpu().numpy(), ref_v)
+    eager = [o.clone() for o in outs]
+    cache.k.copy_(pool_k)                   # the same three steps again, captured and replayed
+    cache.v.copy_(pool_v)
+    for o in outs:
+        o.zero_()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            run()
+    torch.cuda.current_stream().wait_stream(side)
+    cache.k.copy_(pool_k)
+    cache.v.copy_(pool_v)
+    g.replay()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for i in range(steps):
+        assert torch.equal(outs[i], eager[i]), f"step {i}"
+
+
 # ---------------------------------------------------------------- benchmark-sized cases
 
 def test_config3_shape_against_oracle(b2a):
