@@ -764,12 +764,33 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const DecodePara
     const int nsplit = min(p.max_splits, (nblk - blk_lo + p.blocks_per_cta - 1) / p.blocks_per_cta);
     const size_t base = (static_cast<size_t>(seq) * p.Hq + h) * p.max_splits;
     const float2* ml = reinterpret_cast<const float2*>(p.ws_ml) + base;
+    // the first sixteen splits (all of them, for the chunk plans in use) are requested at once, (m, l) and values
+    // alike, so that the merge costs one trip to L2 instead of two; the arithmetic keeps its order
+    constexpr int kFirst = 16;
+    float2 mlv[kFirst];
+    float ov[kFirst];
+#pragma unroll
+    for (int i = 0; i < kFirst; ++i) {
+        const int sp = min(i, nsplit - 1);  // (the tail repeats the last split: dropped below)
+        mlv[i] = ml[sp];
+        ov[i] = p.ws_o[(base + sp) * kD + d];
+    }
     float mc = kNegBig;
+#pragma unroll
+    for (int i = 0; i < kFirst; ++i) mc = fmaxf(mc, mlv[i].x);
 #pragma unroll 8
-    for (int s = 0; s < nsplit; ++s) mc = fmaxf(mc, ml[s].x);
+    for (int s = kFirst; s < nsplit; ++s) mc = fmaxf(mc, ml[s].x);
     float o = 0.f, l = 0.f;
+#pragma unroll
+    for (int i = 0; i < kFirst; ++i) {
+        if (i < nsplit) {
+            const float f = ex2(mlv[i].x - mc);
+            o += ov[i] * f;
+            l += mlv[i].y * f;
+        }
+    }
 #pragma unroll 8
-    for (int s = 0; s < nsplit; ++s) {
+    for (int s = kFirst; s < nsplit; ++s) {
         const float2 v = ml[s];
         const float f = ex2(v.x - mc);
         o += p.ws_o[(base + s) * kD + d] * f;
