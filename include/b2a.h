@@ -199,6 +199,24 @@ int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, c
                                 const int32_t* block_indices, const int32_t* block_indices_begins, void* out,
                                 int32_t* status, b2a_stream_t stream);
 
+/* Score output of PagedAttentionExtension (its second output, which cache-eviction policies accumulate; the
+ * reference's policy consumes such sums, modules/genai_optimizations/genai_opt/token_eviction.py:154-183): for every
+ * sequence of the step, the attention probabilities of its LAST query token over the sequence's cached keys, summed
+ * over the query heads.  Call after b2a_paged_kv_store of the step (the new tokens' keys are part of the context).
+ *   scores        float32, flat: sequence s occupies [score_begins[s], score_begins[s+1]) with one value per context
+ *                 position 0 .. past + new tokens - 1 (positions a sliding window leaves out: 0); a sequence without a
+ *                 new token has no entries.  Every sequence's values sum to Hq.
+ *   score_begins  int32 [num_seqs + 1], written by the call.
+ *   scores_capacity  floats `scores` holds; a step that needs more reports B2A_DEV_BAD_LEN and writes nothing beyond.
+ * u8 caches with D = 128, 16-token blocks, f16 / bf16 queries, at most eight query heads per KV head and 128 query
+ * heads; anything else is B2A_ERR_UNSUPPORTED.  Only K is read, twice.  Enqueue-only, graph-capturable. */
+int b2a_paged_scores_workspace_bytes(const b2a_paged_desc* desc, int sm_count, size_t* out_bytes);
+int b2a_paged_last_token_scores(const b2a_paged_desc* desc, const void* query, const void* k_cache,
+                                const int32_t* past_lens, const int32_t* subsequence_begins,
+                                const int32_t* block_indices, const int32_t* block_indices_begins, float* scores,
+                                int64_t scores_capacity, int32_t* score_begins, void* workspace, size_t workspace_bytes,
+                                int32_t* status, b2a_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Head-sharded attention over the GPUs of one node (one rank per GPU).
  *

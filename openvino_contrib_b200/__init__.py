@@ -4,7 +4,7 @@ mirror of the plugin's operator interface in ``openvino_contrib_b200/host`` (C++
 from . import _lib
 from ._lib import B2AError
 from .ops import (HostSdpaPipeline, KvBlockManager, PagedAttentionOp, PagedKvCache, SdpaOp, paged_attention,
-                  paged_kv_store, sdpa)
+                  paged_kv_store, paged_last_token_scores, sdpa)
 
-__all__ = ["_lib", "B2AError", "sdpa", "HostSdpaPipeline", "paged_kv_store", "paged_attention", "SdpaOp", "PagedAttentionOp", "PagedKvCache",
+__all__ = ["_lib", "B2AError", "sdpa", "HostSdpaPipeline", "paged_kv_store", "paged_attention", "paged_last_token_scores", "SdpaOp", "PagedAttentionOp", "PagedKvCache",
            "KvBlockManager"]

@@ -53,6 +53,10 @@ SIGNATURES = {
                                       C.c_void_p, C.c_void_p]),
     "b2a_paged_attention_noalloc": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2a_paged_scores_workspace_bytes": (C.c_int, [C.POINTER(PagedDesc), C.c_int, C.POINTER(C.c_size_t)]),
+    "b2a_paged_last_token_scores": (C.c_int, [C.POINTER(PagedDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
+                                              C.c_size_t, C.c_void_p, C.c_void_p]),
     "b2a_shard_group_create": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]),
     "b2a_shard_group_handle": (C.c_int, [C.c_void_p, C.c_char_p]),
     "b2a_shard_group_connect": (C.c_int, [C.c_void_p, C.c_char_p]),

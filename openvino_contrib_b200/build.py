@@ -25,7 +25,7 @@ NVCC_FLAGS = [
 ]
 
 CU_SOURCES = ["csrc/api.cu", "csrc/attn_generic.cu", "csrc/paged_kv_store.cu", "csrc/paged_decode.cu",
-              "csrc/sdpa_tcgen05.cu", "csrc/shard_group.cu", "csrc/paged_kv_state.cu"]
+              "csrc/sdpa_tcgen05.cu", "csrc/shard_group.cu", "csrc/paged_kv_state.cu", "csrc/paged_scores.cu"]
 # host side in the library: the block manager, the operator classes (registered with the operation registry when the
 # library is loaded) and the host-tensor pipeline built on them
 CXX_SOURCES = ["host/kv_block_manager.cpp", "host/attention_ops.cpp", "host/host_pipeline.cpp",

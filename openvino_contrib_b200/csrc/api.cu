@@ -289,4 +289,42 @@ int b2a_paged_attention_noalloc(const b2a_paged_desc* desc, const void* query, c
         reinterpret_cast<cudaStream_t>(stream));
 }
 
+int b2a_paged_scores_workspace_bytes(const b2a_paged_desc* desc, int sm_count, size_t* out_bytes) {
+    if (out_bytes == nullptr) return B2A_ERR_NULL;
+    b2a_paged_desc d;
+    const int rc = resolve_paged_desc(desc, d);
+    if (rc != B2A_OK) return rc;
+    if (d.max_context_len <= 0) return B2A_ERR_DIM;
+    if (!paged_scores_supported(d)) return B2A_ERR_UNSUPPORTED;
+    if (sm_count <= 0) sm_count = device_sm_count();
+    if (sm_count <= 0) sm_count = 148;
+    *out_bytes = paged_scores_plan(d, sm_count).workspace_bytes;
+    return B2A_OK;
+}
+
+int b2a_paged_last_token_scores(const b2a_paged_desc* desc, const void* query, const void* k_cache,
+                                const int32_t* past_lens, const int32_t* subsequence_begins,
+                                const int32_t* block_indices, const int32_t* block_indices_begins, float* scores,
+                                int64_t scores_capacity, int32_t* score_begins, void* workspace, size_t workspace_bytes,
+                                int32_t* status, b2a_stream_t stream) {
+    b2a_paged_desc d;
+    const int rc = resolve_paged_desc(desc, d);
+    if (rc != B2A_OK) return rc;
+    if (d.num_seqs == 0) return B2A_OK;
+    if (query == nullptr || k_cache == nullptr || scores == nullptr || score_begins == nullptr || past_lens == nullptr ||
+        subsequence_begins == nullptr || block_indices == nullptr || block_indices_begins == nullptr)
+        return B2A_ERR_NULL;
+    if (d.max_context_len <= 0 || scores_capacity < 0) return B2A_ERR_DIM;
+    if (!paged_scores_supported(d)) return B2A_ERR_UNSUPPORTED;
+    if (!aligned(k_cache, 16) || !aligned(query, 16)) return B2A_ERR_ALIGN;
+    const int sms = device_sm_count();
+    if (sms <= 0) return B2A_ERR_CUDA;
+    const ScorePlan plan = paged_scores_plan(d, sms);
+    if (workspace == nullptr || workspace_bytes < plan.workspace_bytes) return B2A_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return B2A_ERR_ALIGN;
+    return paged_scores_launch(d, plan, query, k_cache,
+                               tables_of(d, past_lens, subsequence_begins, block_indices, block_indices_begins), scores,
+                               scores_capacity, score_begins, workspace, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

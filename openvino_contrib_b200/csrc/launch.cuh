@@ -75,6 +75,17 @@ int paged_decode_launch_builtin_scratch(const b2a_paged_desc& d, const DecodePla
                                         const void* k_cache, const void* v_cache, const PagedTables& t, void* out,
                                         int32_t* status, cudaStream_t stream);
 
+// paged_scores.cu — per-key attention probabilities of every sequence's last query token, summed over the heads
+struct ScorePlan {
+    int blocks_per_cta, max_splits;
+    size_t workspace_bytes;
+};
+bool paged_scores_supported(const b2a_paged_desc& d);
+ScorePlan paged_scores_plan(const b2a_paged_desc& d, int sm_count);
+int paged_scores_launch(const b2a_paged_desc& d, const ScorePlan& plan, const void* query, const void* k_cache,
+                        const PagedTables& t, float* scores, long long capacity, int32_t* score_begins, void* workspace,
+                        int32_t* status, cudaStream_t stream);
+
 // sdpa_tcgen05.cu — TMA + tcgen05 flash prefill (f16 / bf16, D = Dv = 128)
 bool sdpa_tc_supported(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t (&ks)[4],
                        const int64_t (&vs)[4], const int64_t (&os)[4], const void* q, const void* k, const void* v,

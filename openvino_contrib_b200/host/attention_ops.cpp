@@ -168,6 +168,23 @@ PagedAttentionOp::PagedAttentionOp(const CreationContext& context, const NodeOp&
     max_step_tokens_ = static_cast<int>(mt);
     max_prefill_kv_tokens_ = static_cast<int>((mp + 127) / 128 * 128);
     workspace_bytes_ = WorkspaceBound();
+    if (node.get_output_size() >= 2) {
+        const int64_t cap = rt_info_int(node, "b2a.max_score_entries", ms * mc);
+        if (cap <= 0) ov::throw_ov_exception("PagedAttentionExtension: bad b2a.max_score_entries");
+        b2a_paged_desc d = desc_;
+        d.max_context_len = max_context_len_;
+        d.max_q_len = 1;
+        size_t worst = 0;
+        for (int n = 1; n <= max_seqs_; ++n) {  // (fewer sequences are cut into more chunks: not monotone)
+            d.num_seqs = d.num_tokens = n;
+            size_t bytes = 0;
+            // (a configuration the score kernels do not take fails here, which query_model reads as "not supported")
+            throwIfError(b2a_paged_scores_workspace_bytes(&d, 0, &bytes), "b2a_paged_scores_workspace_bytes");
+            worst = std::max(worst, bytes);
+        }
+        score_capacity_ = cap;
+        score_ws_bytes_ = (worst + 15) & ~static_cast<size_t>(15);
+    }
 }
 
 b2a_paged_desc PagedAttentionOp::StepDesc(int num_tokens, int num_seqs, const AttentionStepHints& hints) const {
@@ -224,6 +241,8 @@ WorkbufferRequest PagedAttentionOp::GetWorkBufferRequest() const {
     WorkbufferRequest r;
     r.mutable_sizes.push_back(workspace_bytes_);
     r.mutable_sizes.push_back(16);
+    // [2] (nodes with a score output) scratch of the score kernels, then the sequences' offsets in the output
+    if (has_scores()) r.mutable_sizes.push_back(score_ws_bytes_ + sizeof(int32_t) * (static_cast<size_t>(max_seqs_) + 1));
     return r;
 }
 
@@ -253,6 +272,21 @@ void PagedAttentionOp::Execute(const InferenceRequestContext& context, Inputs in
     throwIfError(b2a_paged_attention(&d, in[0].get(), in[3].get(), in[4].get(), past_lens, subseq, bidx, bbeg,
                                      out[0].get(), wb.mutable_buffers[0].get(), workspace_bytes_, status, s),
                  "b2a_paged_attention");
+    if (has_scores() && out.size() >= 2 && out[1].get() != nullptr) {
+        if (wb.mutable_buffers.size() < 3) ov::throw_ov_exception("PagedAttentionExtension: score work buffer missing");
+        // the score kernels split the longest admitted context the same way for every step, so the scratch reserved
+        // at construction fits: the step's descriptor with the capacity's sequence count for the layout
+        b2a_paged_desc sd = d;
+        char* ws = static_cast<char*>(wb.mutable_buffers[2].get());
+        size_t need = 0;
+        throwIfError(b2a_paged_scores_workspace_bytes(&sd, 0, &need), "b2a_paged_scores_workspace_bytes");
+        if (need > score_ws_bytes_) ov::throw_ov_exception("PagedAttentionExtension: score scratch too small");
+        throwIfError(b2a_paged_last_token_scores(&sd, in[0].get(), in[3].get(), past_lens, subseq, bidx, bbeg,
+                                                 static_cast<float*>(out[1].get()), score_capacity_,
+                                                 reinterpret_cast<int32_t*>(ws + score_ws_bytes_), ws, score_ws_bytes_,
+                                                 status, s),
+                     "b2a_paged_last_token_scores");
+    }
 }
 
 }  // namespace nvidia_gpu

@@ -62,6 +62,13 @@ public:
     int max_seqs() const { return max_seqs_; }
     int max_context_len() const { return max_context_len_; }
     int max_step_tokens() const { return max_step_tokens_; }
+    // The node's second output (scores of every sequence's last query token, flat float32) is produced when the node
+    // has one: the bound buffer must hold score_capacity() floats (run-time information "b2a.max_score_entries",
+    // default max_seqs * max_context_len); the third work buffer then holds the score kernels' scratch followed by
+    // the int32 [max_seqs + 1] offsets of the sequences in the output.
+    bool has_scores() const { return score_capacity_ > 0; }
+    int64_t score_capacity() const { return score_capacity_; }
+    size_t score_begins_offset() const { return score_ws_bytes_; }
     // The descriptor Execute would launch for a step of these extents and hints (the checks Execute makes, without
     // the launch): what the capacity tests compare the work-buffer request against.
     b2a_paged_desc StepDesc(int num_tokens, int num_seqs, const AttentionStepHints& hints) const;
@@ -71,6 +78,8 @@ private:
     b2a_paged_desc desc_{};  // num_seqs / num_tokens hold the static extents (0 = dynamic)
     int max_seqs_ = 0, max_context_len_ = 0, max_step_tokens_ = 0, max_prefill_kv_tokens_ = 0;
     size_t workspace_bytes_ = 0;
+    int64_t score_capacity_ = 0;   // 0: the node has no second output
+    size_t score_ws_bytes_ = 0;
 };
 
 }  // namespace nvidia_gpu

@@ -476,6 +476,103 @@ void test_paged_op_decode_with_block_manager() {
 
 // The per-operation timing hook: an event pair (and an NVTX range) around Execute, accumulated over calls the way
 // the reference's profiler accumulates them (src/utils/perf_timing.hpp:24-40).
+// The node's second output: scores of every sequence's last query token (b2a_paged_last_token_scores through the
+// operator).  One mixed step (20-token prefill, 5-token prefill, then the same sequences with one token each); the
+// scores must be non-negative, sum to Hq per sequence, and sit at the cumulative contexts.
+void test_paged_op_score_output() {
+    const int Hq = 8, Hkv = 2, D = 128, bs = 16, nseq = 2, nblocks = 32;
+    const int chunk = bs * (D + 4);
+    CreationContext cc{CUDA::Device{0}, false};
+    ThreadContext tc{CUDA::Device{0}};
+    InferenceRequestContext ctx{tc};
+    auto s = tc.stream().get();
+    auto node = std::make_shared<ov::op::PagedAttentionExtension>();
+    node->add_input(ov::element::f16, {0, static_cast<size_t>(Hq * D)});
+    node->add_input(ov::element::f16, {0, static_cast<size_t>(Hkv * D)});
+    node->add_input(ov::element::f16, {0, static_cast<size_t>(Hkv * D)});
+    node->add_input(ov::element::u8, {nblocks, Hkv, bs, D + 4});
+    node->add_input(ov::element::u8, {nblocks, Hkv, bs, D + 4});
+    for (int i = 0; i < 4; ++i) node->add_input(ov::element::i32, {0});
+    node->add_input(ov::element::f32, {});
+    node->add_input(ov::element::i32, {});
+    node->add_output(ov::element::f16, {0, static_cast<size_t>(Hq * D)});
+    node->add_output(ov::element::f32, {0});
+    node->get_rt_info()["b2a.max_seqs"] = 4;
+    node->get_rt_info()["b2a.max_context_len"] = 128;
+    auto base = OperationRegistry::getInstance().createOperation(cc, node, ids({0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10}), ids({11, 12}));
+    auto op = std::dynamic_pointer_cast<const PagedAttentionOp>(base);
+    CHECK(op != nullptr && op->has_scores() && op->score_capacity() == 4 * 128);
+    const auto req = op->GetWorkBufferRequest();
+    CHECK(req.mutable_sizes.size() == 3);
+    DevBuf<uint8_t> ws(req.mutable_sizes[0]), st(req.mutable_sizes[1]), sws(req.mutable_sizes[2]);
+    Workbuffers wb;
+    wb.mutable_buffers = {CUDA::DevicePointer<void*>{ws.p}, CUDA::DevicePointer<void*>{st.p}, CUDA::DevicePointer<void*>{sws.p}};
+    DevBuf<uint8_t> kc(static_cast<size_t>(nblocks) * Hkv * chunk), vc(static_cast<size_t>(nblocks) * Hkv * chunk);
+    CUDA_OK(cudaMemsetAsync(kc.p, 0, kc.n, s));
+    CUDA_OK(cudaMemsetAsync(vc.p, 0, vc.n, s));
+    b2a::KvBlockManager mgr(nblocks, bs, 7);
+    const int64_t seq_ids[nseq] = {1, 2};
+    for (auto id : seq_ids) mgr.add_sequence(id);
+    std::mt19937 rng(11);
+    std::normal_distribution<float> nd;
+    const int max_tok = 32;
+    DevBuf<uint16_t> dq(static_cast<size_t>(max_tok) * Hq * D), dk(static_cast<size_t>(max_tok) * Hkv * D),
+        dv(static_cast<size_t>(max_tok) * Hkv * D), dout(static_cast<size_t>(max_tok) * Hq * D);
+    DevBuf<float> dscores(static_cast<size_t>(op->score_capacity()));
+    DevBuf<int32_t> d_past(nseq), d_sb(nseq + 1), d_bi(nblocks), d_bb(nseq + 1);
+    const int32_t first[nseq] = {20, 5}, one[nseq] = {1, 1};
+    for (int step = 0; step < 2; ++step) {
+        b2a::StepTables t;
+        CHECK(mgr.schedule_step(seq_ids, step == 0 ? first : one, nseq, t) == B2A_OK);
+        const int ntok = t.num_tokens;
+        std::vector<uint16_t> q(static_cast<size_t>(max_tok) * Hq * D, 0), k(static_cast<size_t>(max_tok) * Hkv * D, 0),
+            v(static_cast<size_t>(max_tok) * Hkv * D, 0);
+        for (size_t i = 0; i < static_cast<size_t>(ntok) * Hq * D; ++i) q[i] = f2h(nd(rng));
+        for (size_t i = 0; i < static_cast<size_t>(ntok) * Hkv * D; ++i) {
+            k[i] = f2h(nd(rng));
+            v[i] = f2h(nd(rng));
+        }
+        dq.up(q, s); dk.up(k, s); dv.up(v, s);
+        std::vector<int32_t> bi(static_cast<size_t>(nblocks), 0);
+        std::copy(t.block_indices.begin(), t.block_indices.end(), bi.begin());
+        d_past.up(t.past_lens, s); d_sb.up(t.subsequence_begins, s); d_bi.up(bi, s); d_bb.up(t.block_indices_begins, s);
+        ctx.getDynamicBufferContext().setShape(0, {static_cast<size_t>(ntok), static_cast<size_t>(Hq * D)});
+        ctx.getDynamicBufferContext().setShape(5, {static_cast<size_t>(nseq)});
+        std::vector<CUDA::DevicePointer<const void*>> in;
+        for (const void* p : {static_cast<const void*>(dq.p), static_cast<const void*>(dk.p), static_cast<const void*>(dv.p),
+                              static_cast<const void*>(kc.p), static_cast<const void*>(vc.p),
+                              static_cast<const void*>(d_past.p), static_cast<const void*>(d_sb.p),
+                              static_cast<const void*>(d_bi.p), static_cast<const void*>(d_bb.p),
+                              static_cast<const void*>(st.p), static_cast<const void*>(st.p)})
+            in.emplace_back(p);
+        std::vector<CUDA::DevicePointer<void*>> out{CUDA::DevicePointer<void*>{dout.p}, CUDA::DevicePointer<void*>{dscores.p}};
+        op->Execute(ctx, {in.data(), in.size()}, {out.data(), out.size()}, wb);
+        std::vector<float> sc;
+        std::vector<uint8_t> status, tail;
+        dscores.down(sc, s); st.down(status, s); sws.down(tail, s);
+        tc.stream().synchronize();
+        CUDA_OK(cudaGetLastError());
+        int32_t st_word;
+        std::memcpy(&st_word, status.data(), 4);
+        CHECK(st_word == 0);
+        int32_t begins[nseq + 1];
+        std::memcpy(begins, tail.data() + op->score_begins_offset(), sizeof begins);
+        int expect = 0;
+        for (int sq = 0; sq < nseq; ++sq) {
+            CHECK(begins[sq] == expect);
+            const int ctxlen = t.past_lens[static_cast<size_t>(sq)] + (step == 0 ? first[sq] : 1);
+            float sum = 0.f;
+            for (int i = 0; i < ctxlen; ++i) {
+                CHECK(sc[static_cast<size_t>(expect + i)] >= 0.f);
+                sum += sc[static_cast<size_t>(expect + i)];
+            }
+            CHECK(std::fabs(sum - Hq) < 0.05f);
+            expect += ctxlen;
+        }
+        CHECK(begins[nseq] == expect);
+    }
+}
+
 void test_profiled_step() {
     CreationContext cc{CUDA::Device{0}, false};
     ThreadContext tc{CUDA::Device{0}};
@@ -562,6 +659,7 @@ int main(int argc, char** argv) {
         RUN(test_sdpa_op_graph_capture);
         RUN(test_sdpa_op_rejects);
         RUN(test_paged_op_decode_with_block_manager);
+        RUN(test_paged_op_score_output);
         RUN(test_host_pipeline);
         RUN(test_profiled_step);
     }

@@ -322,6 +322,41 @@ def paged_attention(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequ
     return out
 
 
+def paged_last_token_scores(query: torch.Tensor, cache: PagedKvCache, past_lens, subsequence_begins, block_indices,
+                            block_indices_begins, hq: int, max_context_len: int, scale: Optional[float] = None,
+                            sliding_window: int = 0, scores: Optional[torch.Tensor] = None,
+                            workspace: Optional[torch.Tensor] = None, stream=None,
+                            status: Optional[torch.Tensor] = None):
+    """Score output of the paged attention: per sequence, the attention probabilities of its last query token over
+    its cached keys, summed over the query heads.  Returns ``(scores, score_begins)``: flat float32 scores and the
+    int32 [num_seqs + 1] offsets of the sequences in it (``b2a_paged_last_token_scores``).  ``scores`` defaults to a
+    buffer of ``num_seqs * max_context_len`` floats."""
+    _require_cuda(query, cache.k, past_lens, subsequence_begins, block_indices, block_indices_begins, scores)
+    if not query.is_contiguous() or query.shape[1] != hq * cache.d:
+        raise ValueError("query must be dense [tokens, Hq*D]")
+    num_tokens, num_seqs = query.shape[0], past_lens.shape[0]
+    if scores is None:
+        scores = torch.empty(num_seqs * max_context_len, dtype=torch.float32, device=query.device)
+    if scores.dtype != torch.float32 or not scores.is_contiguous():
+        raise TypeError("scores must be a contiguous float32 tensor")
+    begins = torch.empty(num_seqs + 1, dtype=torch.int32, device=query.device)
+    d = _paged_desc(query.dtype, cache, hq, num_seqs, num_tokens, max_context_len, max(1, num_tokens - num_seqs + 1),
+                    scale, sliding_window)
+    lib = _lib.load()
+    ws = C.c_size_t(0)
+    check(lib.b2a_paged_scores_workspace_bytes(C.byref(d), 0, C.byref(ws)), "b2a_paged_scores_workspace_bytes")
+    if workspace is None or workspace.numel() * workspace.element_size() < ws.value:
+        workspace = torch.empty(max(16, ws.value), dtype=torch.uint8, device=query.device)
+    check(lib.b2a_paged_last_token_scores(C.byref(d), query.data_ptr(), cache.k.data_ptr(), _i32(past_lens).data_ptr(),
+                                          _i32(subsequence_begins).data_ptr(), _i32(block_indices).data_ptr(),
+                                          _i32(block_indices_begins).data_ptr(), scores.data_ptr(), scores.numel(),
+                                          begins.data_ptr(), workspace.data_ptr(),
+                                          workspace.numel() * workspace.element_size(), _ptr(status),
+                                          _stream_ptr(stream)),
+          "b2a_paged_last_token_scores")
+    return scores, begins
+
+
 class PagedAttentionOp:
     """Operator-shaped wrapper for ``PagedAttentionExtension`` (the Python twin of the C++ ``PagedAttentionOp``).
 
@@ -380,7 +415,10 @@ class PagedAttentionOp:
 
     def Execute(self, inputs: Sequence, outputs: Sequence[torch.Tensor], workbuffers: Optional[dict] = None,
                 stream=None, status: Optional[torch.Tensor] = None, prefill_row_blocks: int = 0,
-                prefill_kv_tokens: int = 0) -> None:
+                prefill_kv_tokens: int = 0):
+        """Store this step's K/V rows, then attention into ``outputs[0]``.  A second output tensor (float32, flat)
+        receives the node's score output - per sequence, the last query token's attention probabilities summed over
+        the heads - and the int32 offsets of the sequences in it are returned (else None)."""
         if len(inputs) < 11 or len(outputs) < 1:
             raise ValueError("PagedAttentionExtension takes at least 11 inputs and 1 output")
         (query, key, value, k_cache, v_cache, past_lens, subsequence_begins, block_indices,
@@ -409,6 +447,13 @@ class PagedAttentionOp:
                         self.sliding_window, out=outputs[0], workspace=ws, stream=stream,
                         status=status, prefill_row_blocks=rb, prefill_kv_tokens=kvt,
                         cache_rows_settled=True)  # the kernel before it is this step's store
+        if len(outputs) > 1 and outputs[1] is not None:
+            _, begins = paged_last_token_scores(query, cache, past_lens, subsequence_begins, block_indices,
+                                                block_indices_begins, self.hq, self.max_context_len,
+                                                self.scale if sc is None else float(sc), self.sliding_window,
+                                                scores=outputs[1], stream=stream, status=status)
+            return begins
+        return None
 
 
 # ------------------------------------------------------------------------------------------------------------

@@ -100,6 +100,38 @@ def paged_attention_ref(query, k_cache, v_cache, past_lens, subsequence_begins, 
     return out.reshape(-1, hq * d)
 
 
+def last_token_scores_ref(query, k_cache, past_lens, subsequence_begins, block_indices, block_indices_begins,
+                          hq, hkv, d, block_size, scale=None, sliding_window=0):
+    """Score output: per sequence, the softmax row of its LAST query token over the sequence's keys, summed over the
+    query heads (what an eviction policy accumulates, modules/genai_optimizations/genai_opt/token_eviction.py:154-183:
+    attention weights summed over query rows and heads per key).  Returns (scores f32 flat, begins i32 [seqs+1]);
+    a sequence without a query token has no entries; keys a sliding window leaves out score 0.
+    PARITY UNPINNED: the reference has no paged attention; the arithmetic is the pinned softmax of this file."""
+    q = _as_f32(query).reshape(-1, hq, d)
+    g = hq // hkv
+    if scale is None:
+        scale = 1.0 / np.sqrt(np.float32(d))
+    parts, begins = [], [0]
+    for s in range(len(past_lens)):
+        b, e = int(subsequence_begins[s]), int(subsequence_begins[s + 1])
+        if e - b < 1:
+            begins.append(begins[-1])
+            continue
+        ctx = int(past_lens[s]) + (e - b)
+        kk = gather_sequence(k_cache, s, ctx, block_indices, block_indices_begins, d, block_size)  # [Hkv, ctx, D]
+        qs = q[e - 1].reshape(hkv, g, d)
+        sc = np.matmul(qs, np.swapaxes(kk, -1, -2)) * np.float32(scale)  # [Hkv, g, ctx]
+        if sliding_window and sliding_window > 0:
+            keep = (ctx - 1 - np.arange(ctx)) < sliding_window
+            sc = np.where(keep[None, None], sc, np.float32(-np.inf))
+        p = np.exp(sc - sc.max(axis=-1, keepdims=True))
+        p = p / p.sum(axis=-1, keepdims=True)
+        parts.append(p.sum(axis=(0, 1)).astype(np.float32))
+        begins.append(begins[-1] + ctx)
+    flat = np.concatenate(parts) if parts else np.zeros(0, np.float32)
+    return flat, np.asarray(begins, np.int32)
+
+
 # ---------------------------------------------------------------------------------------
 # Seeded workload builders shared by tests and bench (shapes follow the benchmark configs).
 # ---------------------------------------------------------------------------------------

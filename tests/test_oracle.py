@@ -154,3 +154,27 @@ def test_rope_oracle_properties():
     twice = rope.rope_rows(rope.rope_rows(x, [3] * 6, cos, sin, r), [9] * 6, cos, sin, r)
     np.testing.assert_allclose(twice, rope.rope_rows(x, [12] * 6, cos, sin, r), rtol=1e-4, atol=1e-5)
     assert rope.token_positions([4, 0], [0, 2, 5]).tolist() == [4, 5, 0, 1, 2]
+
+
+def test_score_oracle_is_the_softmax_of_the_attention_oracle():
+    """last_token_scores_ref restates the probabilities inside paged_attention_ref: with V = one-hot of the key
+    position (one sequence, D >= context), the attention output of the last row IS its probability vector."""
+    from oracle import paged as opaged
+    hq, hkv, d, bs = 4, 2, 32, 16
+    ctx = np.array([20], np.int64)
+    rng = np.random.default_rng(0)
+    bi, bb, nb = opaged.build_block_tables(ctx, bs, 1)
+    rows_k = [rng.standard_normal((20, hkv, d), dtype=np.float32)]
+    onehot = np.zeros((20, hkv, d), np.float32)
+    for t in range(20):
+        onehot[t, :, t] = 1.0
+    k_cache = opaged.fill_cache_from_rows(rows_k, ctx, bi, bb, nb, hkv, d, bs)
+    v_cache = opaged.fill_cache_from_rows([onehot], ctx, bi, bb, nb, hkv, d, bs)
+    q = rng.standard_normal((1, hq * d), dtype=np.float32)
+    past, sb = np.array([19], np.int32), np.array([0, 1], np.int32)
+    out = opaged.paged_attention_ref(q, k_cache, v_cache, past, sb, bi, bb, hq, hkv, d, bs).reshape(hq, d)
+    scores, begins = opaged.last_token_scores_ref(q, k_cache, past, sb, bi, bb, hq, hkv, d, bs)
+    assert begins.tolist() == [0, 20]
+    # (one-hot values go through the u8 quantiser: exact 0 and 1 up to its rounding of the scale)
+    np.testing.assert_allclose(scores, out[:, :20].sum(axis=0), atol=5e-3)
+    assert abs(scores.sum() - hq) < 1e-4
