@@ -66,10 +66,10 @@ def _absent_worker(rank, world, port, out_dir):
         t0 = time.time()
         try:
             gather_heads_rows(mine, shard, 16)
-            verdict = "completed"          # must not happen: the other rank never joined
+            outcome = "completed"          # must not happen: the other rank never joined
         except Exception as e:             # gloo reports the timeout as a RuntimeError / DistBackendError
-            verdict = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
-        open(os.path.join(out_dir, "verdict"), "w").write(verdict)
+            outcome = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
+        open(os.path.join(out_dir, "outcome"), "w").write(outcome)
     else:
         time.sleep(6.0)                    # stays alive, between steps, and simply never calls the collective
     # no destroy_process_group: its own barrier would wait for the rank that left the protocol
@@ -82,9 +82,9 @@ def test_absent_rank_ends_the_gather_with_an_error(tmp_path):
     for p in ctx.processes:
         if p.is_alive():
             p.terminate()
-    verdict = (tmp_path / "verdict").read_text()
-    assert verdict.startswith("error after"), verdict
-    assert float(verdict.split()[2][:-2]) < 30.0
+    outcome = (tmp_path / "outcome").read_text()
+    assert outcome.startswith("error after"), outcome
+    assert float(outcome.split()[2][:-2]) < 30.0
 
 
 def test_shard_rejects_uneven_split():
