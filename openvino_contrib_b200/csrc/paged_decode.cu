@@ -675,13 +675,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) paged_decode_kernel(
         __syncthreads();  // (the role starts cleared for everybody;) every thread's part of the partial is written ...
         if (state == kChunkWorked) {
             if (tid == 0) {
-                __threadfence();  // ... and, through the barrier, ordered before this thread's ticket
+                // ... and, through the barrier, ordered before this thread's ticket: one acquire-release add (the
+                // release publishes this CTA's partial, the acquire of the last ticket sees everybody else's)
                 int32_t* ctr = p.push.group_counters + seq * p.Hkv + hk;
-                const bool last = atomicAdd(ctr, 1) == nsplit - 1;
-                if (last) {
-                    *ctr = 0;
-                    __threadfence();  // the other CTAs' partials after the ticket
-                }
+                int32_t before;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(ctr) : "memory");
+                const bool last = before == nsplit - 1;
+                if (last) *ctr = 0;
                 s_role = last ? 1 : 0;
             }
             __syncthreads();
