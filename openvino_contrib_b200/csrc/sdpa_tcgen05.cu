@@ -691,37 +691,27 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 const int pieces = min(kBM, peers.sq - row0) * 16;  // 16-byte pieces of the tile's rows (256 bytes each)
                 const size_t at = ((static_cast<size_t>(item.b) * peers.hq_total + peers.head_offset + head) * peers.sq + row0) * 256;
                 const uint4* src = reinterpret_cast<const uint4*>(peers.out[peers.rank] + at);
-                // Two register buffers: the loads of the next 2 KB are in flight while this one is stored.  (Holding
-                // every warp to its share of the link rate was tried: stores issued faster than the links take them
-                // queue up in the SM's path to memory in front of the K/V loads, and pacing them did end the
-                // computation 15 us earlier with four ranks - but the step got longer, because what bounds it is the
-                // last tile of every CTA, which all CTAs finish at the same time: 148 x 2 tiles x 3 ranks = 28 MB that
-                // can only leave when the computation is over.)
-                auto load4 = [&](uint4 (&v)[4], int i) {
+                // 2 KB at a time: four loads, then the stores to every other rank.  A warp that keeps the links busier
+                // does not help: stores issued faster than the links take them queue up in the SM's path to memory in
+                // front of the K/V loads.  Measured with four ranks: this loop 0.209 ms a step; the next loads in
+                // flight during the stores (two register buffers) 0.222 ms; every warp held to its share of the link
+                // rate 0.221 ms (the computation then ends 15 us earlier, but the last tile of every CTA, which all
+                // CTAs finish at about the same time - 148 x 2 tiles x 3 ranks = 28 MB - leaves later).
+                for (int i0 = lane; i0 < pieces; i0 += 32 * 4) {
+                    uint4 v[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
-                        if (i + 32 * u < pieces)
+                        if (i0 + 32 * u < pieces)
                             asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
                                          : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                                         : "l"(src + i + 32 * u)
+                                         : "l"(src + i0 + 32 * u)
                                          : "memory");
-                };
-                auto store4 = [&](const uint4 (&v)[4], int i) {
+                    for (int pr = 1; pr < peers.world; ++pr) {
+                        uint4* dst = reinterpret_cast<uint4*>(peers.out[(peers.rank + pr) % peers.world] + at);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (i + 32 * u < pieces) {
-                            for (int pr = 1; pr < peers.world; ++pr)  // the next rank first: the ranks do not all write to one peer at a time
-                                reinterpret_cast<uint4*>(peers.out[(peers.rank + pr) % peers.world] + at)[i + 32 * u] = v[u];
-                        }
+                        for (int u = 0; u < 4; ++u)
+                            if (i0 + 32 * u < pieces) dst[i0 + 32 * u] = v[u];
                     }
-                };
-                uint4 va[4], vb[4];
-                load4(va, lane);
-                for (int i = lane; i < pieces; i += 2 * 128) {
-                    load4(vb, i + 128);
-                    store4(va, i);
-                    load4(va, i + 256);
-                    store4(vb, i + 128);
                 }
             }
             __threadfence_system();  // this lane's stores to the other ranks, ordered before the CTA's arrival below
