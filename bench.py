@@ -247,8 +247,8 @@ def bench_prefill(args, rank, world, local):
     exchange, group = "none", None
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     if world > 1:
-        exchange = ("peer stores from the attention kernel: its epilogue stores every tile to both ranks (2 GPUs); from 4 GPUs "
-                    "on the tile is stored locally and two spare warps of the CTA forward it to the other ranks")
+        exchange = ("peer stores from the attention kernel: its epilogue stores every tile into every rank's buffer "
+                    "(from 4 GPUs on the CTAs take their items lightest first, so the stores start at once)")
         try:
             from openvino_contrib_b200.sharding import ShardGroup
             group = ShardGroup(shard, staging_bytes=B * Hq * S * D * 2)

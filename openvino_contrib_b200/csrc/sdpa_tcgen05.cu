@@ -93,8 +93,6 @@ struct TcParams {
 // Output side of a head-sharded launch (world == 0: single GPU, the tmO map is the output).
 struct TcPeers {
     CUtensorMap out_map[kMaxShardWorld];  // [rank]: that rank's [B, Hq_total, Sq, 128] output buffer
-    uint8_t* out[kMaxShardWorld];     // ... and its address as mapped here (read and written by the forwarding warps)
-    int hq_total, sq;                 // its extents (rows of 256 bytes, consecutive rows contiguous)
     int32_t* flags[kMaxShardWorld];
     int32_t* done_counter;
     int world, rank, head_offset;
@@ -349,7 +347,7 @@ __global__ void __launch_bounds__(128) paged_gather_kernel(const PagedTables t, 
 
 // kMode: 0 dense tensors; 1 paged, K/V de-quantised by producer warps inside the kernel; 2 paged, K/V de-quantised
 // beforehand into per-sequence row ranges of an f16 scratch (paged_gather_kernel) and staged by TMA like dense ones
-template <bool kBf16, int kMode, int kMask = 0, bool kPush = false>
+template <bool kBf16, int kMode, int kMask = 0>
 __global__ void __launch_bounds__(kMode == 1 ? kThreadsPaged : kThreadsDense, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcParams p,
@@ -363,8 +361,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t bars = base + 6 * kTile + kStageOut;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 6 * kTile + kStageOut + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 6 * kTile + kStageOut + kNumBars * 8 + 8);
-    // (kPush) reports of the softmax warps that a tile of group A / B lies complete in this rank's buffer: four per tile
-    int* stored_tiles = reinterpret_cast<int*>(gbase + 6 * kTile + kStageOut + kNumBars * 8 + 12);
     auto BAR = [&](int i) { return bars + 8u * static_cast<uint32_t>(i); };
     constexpr bool kPaged = kMode != 0, kDequant = kMode == 1, kGathered = kMode == 2;
     constexpr bool kKvBf16 = kPaged ? false : kBf16;  // element format of the K/V tiles and of P
@@ -442,9 +438,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
         } else {
             const int ctas = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
-            // With many ranks the step is bound by the exchange of the output tiles, which can only start when the
-            // first items end: then a CTA walks the SAME items (the deal below is what balances the CTAs) from its
-            // lightest to its heaviest.
+            // With four or more ranks the step is bound by the exchange of the output tiles, which can only start
+            // when the first items end: then a CTA walks the SAME items (the deal below is what balances the CTAs)
+            // from its lightest to its heaviest, and the epilogue's stores to the other ranks are on the wire from
+            // the first microseconds on.  Measured with four ranks: 0.200 ms a step, against 0.231 ms heaviest
+            // first.  (Storing a tile once locally and letting the CTA's two spare warps forward it to the other
+            // ranks - so that no softmax warp ever waits for the links - was built and measured as well: 0.207-0.211
+            // ms at best, the forwarding stores queue up in the SM's path to memory in front of the K/V loads.)
             if (peers.light_first) {
                 const int rounds = total_items / ctas, rem = total_items - rounds * ctas;
                 const int mine = rounds + ((((rounds & 1) ? ctas - 1 - me : me) < rem) ? 1 : 0);
@@ -503,7 +503,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_init(BAR(i), count);
         }
         *abort_flag = 0;
-        stored_tiles[0] = stored_tiles[1] = 0;
         fence_barrier_init();
     }
     if (warp == 9) {
@@ -654,67 +653,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     }
                 }
             }
-        }
-        if constexpr (kPush) {
-            // Heads sharded over four or more ranks: the links, not the tensor cores, bound the step, and a softmax
-            // warp that stored its tile to every rank itself would sit in its epilogue whenever the links are busy
-            // (measured with four ranks: computing and sending then alternate, 0.231 ms a step against 0.122 ms of
-            // computing and 0.146 ms of sending).  So the softmax warps store a tile once, into this rank's buffer,
-            // and these two otherwise idle warps forward it from there (it is still in L2) to the other ranks with
-            // plain 16-byte stores, 512 contiguous bytes per instruction: the backlog of tiles waiting for the links
-            // lives in the output buffer itself and the computation never waits for it.  Warp 10 forwards the tiles
-            // of softmax group A, warp 11 those of group B.
-            const int X = warp - 10;
-            Item item;
-            int n = 0;
-            bool ok = true;
-            for (int kk = 0; ok && get_item(kk, item); ++kk) {
-                if ((X ? item.nkvB : item.nkvA) == 0) continue;
-                // a count, not a barrier phase: with light items first the softmax warps run many tiles ahead of the links
-                ++n;
-                {
-                    const uint32_t addr = smem_u32(stored_tiles + X);
-                    int seen = 0, spins = 0;
-                    for (;;) {
-                        asm volatile("ld.acquire.cta.shared.s32 %0, [%1];" : "=r"(seen) : "r"(addr) : "memory");
-                        if (seen >= 4 * n) break;
-                        if (*abort_flag || ++spins > (1 << 23)) {  // (a second or so: a tile takes microseconds)
-                            *abort_flag = 1;
-                            break;
-                        }
-                        __nanosleep(128);
-                    }
-                    ok = __all_sync(0xffffffffu, seen >= 4 * n);
-                }
-                if (!ok) break;
-                const int row0 = X ? item.row0B : item.row0A, head = X ? item.headB : item.headA;
-                const int pieces = min(kBM, peers.sq - row0) * 16;  // 16-byte pieces of the tile's rows (256 bytes each)
-                const size_t at = ((static_cast<size_t>(item.b) * peers.hq_total + peers.head_offset + head) * peers.sq + row0) * 256;
-                const uint4* src = reinterpret_cast<const uint4*>(peers.out[peers.rank] + at);
-                // 2 KB at a time: four loads, then the stores to every other rank.  A warp that keeps the links busier
-                // does not help: stores issued faster than the links take them queue up in the SM's path to memory in
-                // front of the K/V loads.  Measured with four ranks: this loop 0.209 ms a step; the next loads in
-                // flight during the stores (two register buffers) 0.222 ms; every warp held to its share of the link
-                // rate 0.221 ms (the computation then ends 15 us earlier, but the last tile of every CTA, which all
-                // CTAs finish at about the same time - 148 x 2 tiles x 3 ranks = 28 MB - leaves later).
-                for (int i0 = lane; i0 < pieces; i0 += 32 * 4) {
-                    uint4 v[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (i0 + 32 * u < pieces)
-                            asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                                         : "l"(src + i0 + 32 * u)
-                                         : "memory");
-                    for (int pr = 1; pr < peers.world; ++pr) {
-                        uint4* dst = reinterpret_cast<uint4*>(peers.out[(peers.rank + pr) % peers.world] + at);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (i0 + 32 * u < pieces) dst[i0 + 32 * u] = v[u];
-                    }
-                }
-            }
-            __threadfence_system();  // this lane's stores to the other ranks, ordered before the CTA's arrival below
         }
     } else if (warp == 8) {
         // =============================== TMA producer ===============================
@@ -876,17 +814,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t tO = tmem + lane_base + static_cast<uint32_t>(256 + X * 128);
         int sxb = 0;  // steps of this tile in the CTA's earlier items: every per-step barrier is at phase (sxb + j)
         bool ok = true;
-        // (kPush) this warp's stores of its last tile have been issued but not yet reported to the forwarding warp:
-        // the report waits for their completion, which costs nothing once a key step of the next item has passed
-        bool unreported = false;
-        auto report_tile = [&]() {
-            if (lane == 0) {
-                tma_store_wait_all();
-                asm volatile("fence.proxy.async;" ::: "memory");  // the tile was written through the async proxy; it is read with ordinary loads
-                asm volatile("red.release.cta.shared.add.s32 [%0], 1;" ::"r"(smem_u32(stored_tiles + X)) : "memory");
-            }
-            unreported = false;
-        };
         Item item;
         for (int k = 0; ok && get_item(k, item); ++k) {
             const int nkv = X ? item.nkvB : item.nkvA;
@@ -1040,11 +967,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     tc_fence_before();
                     mbar_arrive(BAR(P_HALF + X));
                 }
-                if constexpr (kPush) {
-                    // before the arrival below: no warp of the group gets past this step until all four have reported,
-                    // so four reports per tile arrive in tile order
-                    if (unreported) report_tile();
-                }
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(BAR(P_READY + X));
@@ -1114,9 +1036,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         if (lane == 0) {
                             if (peers.world == 0) {
                                 tma_store_4d_hint(&tmO, slab, 64 * half, row0 + 32 * (warp & 3), head, b, l2_evict_first_policy());
-                            } else if constexpr (kPush) {
-                                // into this rank's buffer only: warps 10 and 11 forward the tile from there
-                                tma_store_4d(&peers.out_map[peers.rank], slab, 64 * half, row0 + 32 * (warp & 3), peers.head_offset + head, b);
                             } else {
                                 // the same slab into every rank's buffer, the next rank first so that the ranks do
                                 // not all write to the same peer at the same time; local copy last
@@ -1128,12 +1047,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             tma_store_commit();
                         }
                     }
-                    if constexpr (kPush) unreported = true;
                 }
             }
-        }
-        if constexpr (kPush) {
-            if (unreported) report_tile();
         }
         // stores still in flight: their completion (not only the read of shared memory) before the CTA ends
         if (lane == 0) tma_store_wait_all();
@@ -1288,11 +1203,8 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
         for (int r = 0; r < peer_out->world; ++r) {
             if (!make_map(&peers.out_map[r], peer_out->out_base[r], bf16, d.B, peer_out->hq_total, d.Sq, fs, 32))
                 return B2A_ERR_CUDA;
-            peers.out[r] = static_cast<uint8_t*>(peer_out->out_base[r]);
             peers.flags[r] = peer_out->flags[r];
         }
-        peers.hq_total = peer_out->hq_total;
-        peers.sq = d.Sq;
         peers.done_counter = peer_out->done_counter;
         peers.world = peer_out->world;
         peers.rank = peer_out->rank;
@@ -1317,16 +1229,7 @@ int sdpa_tc_launch(const b2a_sdpa_desc& d, const int64_t (&qs)[4], const int64_t
         p.mask = static_cast<const uint8_t*>(mask);
         for (int i = 0; i < 3; ++i) p.mask_strides[i] = d.mask_strides[i];
     }
-    // four or more ranks: tiles are stored locally and forwarded by the kernel's two spare warps
-    const bool push = peer_out != nullptr && peer_out->world >= 4 && mask_kind == B2A_MASK_NONE;
-    static bool configured[4][2][64] = {};
-    if (push) {
-        auto kern = bf16 ? attn_tc_kernel<true, 0, 0, true> : attn_tc_kernel<false, 0, 0, true>;
-        const int rc = configure_once(kern, configured[3][bf16]);
-        if (rc != B2A_OK) return rc;
-        kern<<<grid, kThreadsDense, kSmemBytes, stream>>>(mq, mk, mv, mo, p, peers);
-        return cudaGetLastError() == cudaSuccess ? B2A_OK : B2A_ERR_CUDA;
-    }
+    static bool configured[3][2][64] = {};
     auto kern = mask_kind == B2A_MASK_BOOL  ? (bf16 ? attn_tc_kernel<true, 0, 1> : attn_tc_kernel<false, 0, 1>)
                 : mask_kind == B2A_MASK_ADD ? (bf16 ? attn_tc_kernel<true, 0, 2> : attn_tc_kernel<false, 0, 2>)
                                             : (bf16 ? attn_tc_kernel<true, 0, 0> : attn_tc_kernel<false, 0, 0>);

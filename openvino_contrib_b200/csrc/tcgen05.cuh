@@ -88,11 +88,6 @@ __device__ __forceinline__ void tma_store_4d_hint(const CUtensorMap* map, uint32
                  ::"l"(map), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
                  : "memory");
 }
-// Untiled bulk store shared -> global: `bytes` contiguous bytes (a multiple of 16; both addresses 16-byte aligned).
-__device__ __forceinline__ void bulk_store(void* gmem_dst, uint32_t smem_src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_src), "r"(bytes)
-                 : "memory");
-}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // only until the stores have READ their shared-memory source (it may be overwritten; the writes may still be in flight)

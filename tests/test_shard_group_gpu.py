@@ -169,8 +169,7 @@ def test_absent_rank_times_out_decode(b2a, in_place):
 def test_absent_ranks_time_out_prefill_and_own_tiles_reach_every_rank(b2a, world):
     # Only rank 0 of the world runs the step (all ranks' buffers live on this one GPU).  Its wait for the others must
     # run out; its own heads must nevertheless sit, bit-identical to the plain kernel, in the buffer of EVERY rank -
-    # the epilogue's tensor stores to the peers with two ranks; from four ranks on, the forwarding warps' copies of the
-    # locally stored tile.
+    # the epilogue's tensor stores to the peers (with four ranks the CTAs also walk their items lightest first).
     from openvino_contrib_b200 import _lib
     from openvino_contrib_b200.sharding import _device_view
     lib = _lib.load()
