@@ -128,15 +128,15 @@ __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t,
     constexpr int kBuckets = 256;
     __shared__ int s_hist[kBuckets], s_count, s_groups, s_steps;
     __shared__ unsigned long long s_decode_blocks;
-    grid_dependency_wait();  // earlier kernels may still read the previous step's list and scratch layout
-    grid_launch_dependents();
+    // Everything that only reads the step's tables - the histogram of the weights, the counts, the bucket offsets -
+    // is done while the kernel in front (the step's store) drains; what this kernel WRITES (list, scratch layout)
+    // may still be read by earlier kernels, so the writes come after the wait.  (The tables of a step exist before
+    // its kernels are launched.)
     for (int i = threadIdx.x; i < kBuckets; i += blockDim.x) s_hist[i] = 0;
     if (threadIdx.x == 0) {
         s_count = s_groups = s_steps = 0;
         s_decode_blocks = 0ull;
     }
-    if (owner != nullptr)
-        for (int g = threadIdx.x; g < owner_groups; g += blockDim.x) owner[g] = -1;
     __syncthreads();
     auto weight = [&](int past, int qlen, int pair) {
         const int tiles = ((qlen + 127) / 128) * G;
@@ -159,13 +159,6 @@ __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t,
             steps += w;
         }
         atomicAdd(&s_steps, steps);
-        if (owner != nullptr) {
-            const int groups = t.past_lens[s] < 0 ? 0 : (past + qlen + 127) / 128;
-            const int g0 = atomicAdd(&s_groups, groups);
-            kv_base[s] = g0 * 128;
-            for (int i = 0; i < groups; ++i)
-                if (g0 + i < owner_groups) owner[g0 + i] = s;
-        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {  // bucket w starts after all heavier buckets
@@ -174,6 +167,22 @@ __global__ void __launch_bounds__(256) paged_tc_plan_kernel(const PagedTables t,
             const int n = s_hist[w];
             s_hist[w] = at;
             at += n;
+        }
+    }
+    grid_dependency_wait();
+    grid_launch_dependents();
+    if (owner != nullptr) {
+        for (int g = threadIdx.x; g < owner_groups; g += blockDim.x) owner[g] = -1;
+        __syncthreads();
+        for (int s = threadIdx.x; s < t.num_seqs; s += blockDim.x) {
+            const int qlen = t.subsequence_begins[s + 1] - t.subsequence_begins[s];
+            if (qlen < 2) continue;
+            const int past = max(0, t.past_lens[s]);
+            const int groups = t.past_lens[s] < 0 ? 0 : (past + qlen + 127) / 128;
+            const int g0 = atomicAdd(&s_groups, groups);
+            kv_base[s] = g0 * 128;
+            for (int i = 0; i < groups; ++i)
+                if (g0 + i < owner_groups) owner[g0 + i] = s;
         }
     }
     __syncthreads();
