@@ -83,6 +83,33 @@ def test_decode_chunk_plan(lib):
     assert splits(16, 2, 16, 32768) == 19    # two-head shard: 112-block chunks, one wave of 4 CTAs per SM
 
 
+def test_score_entry_points_validate_on_the_host(lib):
+    """b2a_paged_scores_workspace_bytes / b2a_paged_last_token_scores refuse on the host what the score kernels do not
+    take (no GPU needed: every check comes before the first launch)."""
+    ws = C.c_size_t(0)
+    p = _lib.PagedDesc()
+    p.q_dtype, p.kv_dtype = _lib.F16, _lib.U8
+    p.Hq, p.Hkv, p.D, p.Dv, p.block_size = 32, 8, 128, 128, 16
+    p.num_seqs, p.num_tokens, p.num_blocks_total, p.max_context_len, p.max_q_len = 64, 64, 100, 8192, 1
+    assert lib.b2a_paged_scores_workspace_bytes(C.byref(p), 148, C.byref(ws)) == 0 and ws.value > 0
+    small = ws.value
+    p.max_context_len = 32768
+    assert lib.b2a_paged_scores_workspace_bytes(C.byref(p), 148, C.byref(ws)) == 0 and ws.value >= small
+    assert lib.b2a_paged_scores_workspace_bytes(C.byref(p), 148, None) == 1                     # NULL
+    p.D = p.Dv = 64
+    assert lib.b2a_paged_scores_workspace_bytes(C.byref(p), 148, C.byref(ws)) == 7              # head size
+    p.D = p.Dv = 128
+    p.Hq = 128                                                                                  # 16 query heads per KV head
+    assert lib.b2a_paged_scores_workspace_bytes(C.byref(p), 148, C.byref(ws)) == 7
+    p.Hq = 32
+    p.kv_dtype = _lib.F16
+    assert lib.b2a_paged_scores_workspace_bytes(C.byref(p), 148, C.byref(ws)) == 7              # only u8 caches
+    p.kv_dtype = _lib.U8
+    assert lib.b2a_paged_last_token_scores(C.byref(p), None, None, None, None, None, None, None, 0, None, None, 0,
+                                           None, None) == 1                                      # NULL operands
+    assert lib.b2a_paged_last_token_scores(C.byref(p), 16, 16, 16, 16, 16, 16, 16, -1, 16, 16, 1 << 30, None, None) == 2
+
+
 def test_kv_block_manager_tables():
     from openvino_contrib_b200 import KvBlockManager
     from openvino_contrib_b200._lib import B2AError
